@@ -1,0 +1,45 @@
+// Host-side helpers shared by the launchers: tensor-map encoding through the
+// driver entry point (no link-time dependency on libcuda), status word access,
+// and the C error codes of the library.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define GF_API extern "C" __attribute__((visibility("default")))
+
+namespace gf {
+
+enum HostErr : int {
+  GFH_OK = 0,
+  GFH_BAD_ARG = -1,
+  GFH_CUDA = -2,
+  GFH_TMAP = -3,
+  GFH_TOO_LARGE = -4,
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn();
+
+// Encode a 2-D tiled map over a row-major [rows, cols] view with `row_stride_bytes` pitch.
+// Box = box_cols x box_rows elements, 128-byte swizzle (box_cols * elem_size must be 128 or less).
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_size, uint64_t rows,
+                 uint64_t cols, uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                 CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);
+
+// 3-D map: [d2, rows, cols] with byte strides for rows and d2.
+int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_size, uint64_t d2,
+                 uint64_t rows, uint64_t cols, uint64_t row_stride_bytes, uint64_t d2_stride_bytes,
+                 uint32_t box_d2, uint32_t box_rows, uint32_t box_cols,
+                 CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);
+
+int sm_count();
+
+// Binds the calling thread to the device selected with gf_set_device (see gf_host.cu).
+void enter();
+
+}  // namespace gf

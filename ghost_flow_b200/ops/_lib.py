@@ -1,0 +1,172 @@
+"""ctypes binding of ``libgfb200.so`` (the sm_100a kernels) and ``libghostflow.so`` (host C++).
+
+The CUDA library is mandatory on a machine with a GPU: :func:`cuda_lib` raises instead of
+silently falling back, so a missing or stale build can never hide behind PyTorch ops.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+_CUDA_LIB = None
+_HOST_LIB = None
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+
+# name -> argtypes (restype is always int unless listed in _RESTYPES)
+_SIGS = {
+    "gf_sm_count": [],
+    "gf_device_count": [],
+    "gf_version": [],
+    "gf_set_device": [I],
+    "gf_gemm_bf16": [P, P, P, I, I, I, I, L, I, L, L, I, I, P, P, L, F, P, I, I, P, I, I, P],
+    "gf_norm_bwd_grid": [I],
+    "gf_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "gf_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
+    "gf_layernorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "gf_layernorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, P],
+    "gf_rope": [P, P, P, I, I, I, L, L, I, I, I, I, P],
+    "gf_swiglu_fwd": [P, P, L, I, P],
+    "gf_swiglu_bwd": [P, P, P, L, I, P],
+    "gf_unary_fwd": [P, P, L, I, I, P],
+    "gf_unary_bwd_bf16": [P, P, P, L, I, P],
+    "gf_op_chain": [P, P, L, P, I, I, P],
+    "gf_binary": [P, P, P, L, I, F, I, P],
+    "gf_reduce": [P, P, P, L, I, I, P],
+    "gf_softmax_rows": [P, P, I, I, I, I, P],
+    "gf_xent_fused": [P, P, P, P, I, I, L, F, L, P],
+    "gf_adam_flat": [P, P, P, P, P, L, F, F, F, F, F, I, F, I, I, P, P],
+    "gf_sgd_flat": [P, P, P, P, L, F, F, F, F, I, I, F, I, P],
+    "gf_grad_sumsq": [P, L, P, I, P],
+    "gf_flash_attn_fwd": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
+    "gf_flash_attn_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
+    "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
+    "gf_cast_f32_to_bf16_2d": [P, P, L, I, L, L, F, P],
+}
+
+
+def _bind(lib, sigs):
+    for name, args in sigs.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+    return lib
+
+
+def lib_path() -> Path:
+    return _PKG / "lib" / "libgfb200.so"
+
+
+def host_lib_path() -> Path:
+    return _PKG / "lib" / "libghostflow.so"
+
+
+def cuda_lib():
+    """Returns the loaded CUDA kernel library; builds it first if the .so is missing."""
+    global _CUDA_LIB
+    if _CUDA_LIB is None:
+        path = lib_path()
+        if not path.exists():
+            from ..csrc.build import build
+
+            build()
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} is missing: run `python -m ghost_flow_b200.csrc.build` (needs nvcc). "
+                "CUDA tensors are never routed to a fallback."
+            )
+        _CUDA_LIB = _bind(ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL), _SIGS)
+    return _CUDA_LIB
+
+
+def has_cuda_lib() -> bool:
+    return lib_path().exists()
+
+
+def host_lib():
+    """Returns the host-only C++ library (checkpoint formats, C ABI, CPU reference math)."""
+    global _HOST_LIB
+    if _HOST_LIB is None:
+        path = host_lib_path()
+        if not path.exists():
+            from ..csrc.build import build
+
+            build()
+        _HOST_LIB = ctypes.CDLL(str(path))
+    return _HOST_LIB
+
+
+_BOUND_DEVICE = -1
+
+
+def stream_ptr() -> int:
+    """Current CUDA stream handle; also keeps the kernel library's device in step with PyTorch's
+    (the library carries its own copy of the CUDA runtime, with its own current-device state)."""
+    global _BOUND_DEVICE
+    dev = torch.cuda.current_device()
+    if dev != _BOUND_DEVICE:
+        cuda_lib().gf_set_device(dev)
+        _BOUND_DEVICE = dev
+    return torch.cuda.current_stream().cuda_stream
+
+
+_STATUS = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 word that kernels write a bounded-wait error code into (0 = ok)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _STATUS[key] = t
+    return t
+
+
+_ERR_NAMES = {
+    1: "consumer timed out waiting for a TMA stage",
+    2: "producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for the accumulator",
+    4: "MMA issuer timed out waiting for a drained accumulator",
+    5: "timed out waiting for a peer flag",
+    6: "timed out in the softmax hand-off",
+    7: "bad argument seen on the device",
+}
+
+
+class KernelStatusError(RuntimeError):
+    pass
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Synchronises and raises if any kernel since the last check recorded an error code."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        if reset:
+            w.zero_()
+        raise KernelStatusError(f"ghost_flow_b200 kernel status {code}: {_ERR_NAMES.get(code, 'unknown')}")
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        names = {-1: "bad argument", -2: "CUDA launch error", -3: "tensor-map encode failed", -4: "size too large"}
+        extra = ""
+        if rc == -2:
+            extra = f" ({torch.cuda.is_available() and 'see cudaGetLastError' or 'no GPU'})"
+        raise RuntimeError(f"{what} failed: {names.get(rc, rc)}{extra}")
+
+
+DEBUG_SYNC = os.environ.get("GF_DEBUG_SYNC", "0") == "1"

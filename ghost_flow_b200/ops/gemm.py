@@ -1,0 +1,155 @@
+"""bf16 GEMM on the hand-written tcgen05 kernel, plus the ``linear`` autograd function.
+
+On CUDA bf16 tensors every product (forward, dgrad, wgrad) runs ``gf_gemm_bf16``; CPU tensors
+(the CPU configs and the CPU-only tests) use ``torch.matmul``. Other CUDA dtypes go to the
+vendor GEMM as a plain library call.
+
+Reference counterparts: ``ghostflow-core/src/ops/matmul.rs:13-170`` (CPU blocked matmul),
+``ghostflow-cuda/src/blas.rs:278-313`` (cuBLAS row-major trick), ``ghostflow-nn/src/linear.rs:56-69``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _is_dense_2d(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.size(1)
+
+
+def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bfloat16, bias=None, residual=None,
+             accumulate=False, alpha=1.0, bn_hint=0, max_ctas=0, b_ready=None, b_rows_per_flag=0, b_epoch=0):
+    """Launches the kernel on 2-D row-major views.
+
+    ``a`` is stored ``[M, K]`` (K-major) or ``[K, M]`` when ``a_mn_major``; ``b`` is stored
+    ``[N, K]`` or ``[K, N]`` when ``b_mn_major``. Row pitches may exceed the row length.
+    """
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert _is_dense_2d(a) and _is_dense_2d(b), "operands must be 2-D with unit inner stride"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert _is_dense_2d(out)
+    lib = _lib.cuda_lib()
+    rc = lib.gf_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+        1 if a_mn_major else 0, a.stride(0), 1 if b_mn_major else 0, b.stride(0), out.stride(0),
+        1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+        bias.data_ptr() if bias is not None else None,
+        residual.data_ptr() if residual is not None else None,
+        residual.stride(0) if residual is not None else 0,
+        float(alpha), _lib.status_word(a.device).data_ptr(), bn_hint, max_ctas,
+        b_ready.data_ptr() if b_ready is not None else None, b_rows_per_flag, b_epoch,
+        _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "gf_gemm_bf16")
+    if _lib.DEBUG_SYNC:
+        _lib.check_status(a.device)
+    return out
+
+
+def _kernel_ok(*ts) -> bool:
+    """bf16 CUDA operands whose 2-D view satisfies the TMA rules (16-byte base and row pitch)."""
+    for t in ts:
+        if not (t.is_cuda and t.dtype == torch.bfloat16):
+            return False
+        if t.dim() >= 2 and (t.stride(-1) != 1 or (t.stride(-2) % 8) or (t.data_ptr() % 16)):
+            return False
+    return True
+
+
+def matmul_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T``."""
+    if not _kernel_ok(x, w):
+        y = x @ w.t()
+        if kw.get("bias") is not None:
+            y = y + kw["bias"]
+        if kw.get("residual") is not None:
+            y = y + kw["residual"]
+        return y
+    M, K = x.shape
+    N = w.shape[0]
+    return gemm_raw(x, False, w, False, M, N, K, **kw)
+
+
+def matmul_nn(a: torch.Tensor, b: torch.Tensor, **kw) -> torch.Tensor:
+    """``a[M,K] @ b[K,N]``."""
+    if not _kernel_ok(a, b):
+        return a @ b
+    M, K = a.shape
+    N = b.shape[1]
+    return gemm_raw(a, False, b, True, M, N, K, **kw)
+
+
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, **kw) -> torch.Tensor:
+    """``a[K,M]^T @ b[K,N]`` (the weight-gradient product ``dy^T x``)."""
+    if not _kernel_ok(a, b):
+        return a.t() @ b
+    K, M = a.shape
+    N = b.shape[1]
+    return gemm_raw(a, True, b, True, M, N, K, **kw)
+
+
+def matmul_tt(a: torch.Tensor, b: torch.Tensor, **kw) -> torch.Tensor:
+    """``a[K,M]^T @ b[N,K]^T``."""
+    if not _kernel_ok(a, b):
+        return a.t() @ b.t()
+    K, M = a.shape
+    N = b.shape[0]
+    return gemm_raw(a, True, b, False, M, N, K, **kw)
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = _as_2d(x)
+        r2 = _as_2d(residual) if residual is not None else None
+        y = matmul_nt(x2, w, bias=bias, residual=r2)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_nn(dy2, w).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = matmul_tn(dy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w^T (+ bias) (+ residual)`` with the bias/residual adds fused into the GEMM epilogue."""
+    if _kernel_ok(x, w):
+        return _LinearFn.apply(x, w, bias, residual)
+    y = torch.nn.functional.linear(x, w, bias)
+    if residual is not None:
+        y = y + residual
+    return y
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """General matmul for the tensor API: 2-D bf16 CUDA operands use the tcgen05 kernel."""
+    if a.dim() == 2 and b.dim() == 2 and _kernel_ok(a, b) and not (a.requires_grad or b.requires_grad):
+        if a.stride(1) == 1 and b.stride(1) == 1:
+            return matmul_nn(a, b)
+        if a.stride(1) == 1 and b.stride(0) == 1:
+            return matmul_nt(a, b.t())
+    return torch.matmul(a, b)

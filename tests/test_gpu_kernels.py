@@ -1,0 +1,261 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _ops():
+    from ghost_flow_b200 import ops
+
+    return ops
+
+
+# ----------------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (384, 256, 192), (200, 136, 72),
+                                   (1024, 4096, 1024), (4096, 1024, 512)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn", "tt"])
+def test_gemm_layouts(M, N, K, layout, kernel_status):
+    ops = _ops()
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float()
+    if layout == "nt":
+        out = ops.matmul_nt(a, b.t().contiguous())
+    elif layout == "nn":
+        out = ops.matmul_nn(a, b)
+    elif layout == "tn":
+        out = ops.matmul_tn(a.t().contiguous(), b)
+    else:
+        out = ops.matmul_tt(a.t().contiguous(), b.t().contiguous())
+    torch.cuda.synchronize()
+    assert out.shape == (M, N)
+    assert _rel_err(out, ref) < 1e-2, f"{layout} {M}x{N}x{K}"
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_tile_widths_and_epilogue(bn, kernel_status):
+    ops = _ops()
+    M, N, K = 512, 768, 320
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t() + bias.float() + res.float()
+    out = ops.gemm_raw(a, False, w, False, M, N, K, bias=bias, residual=res, bn_hint=bn)
+    assert _rel_err(out, ref) < 1e-2
+    # fp32 output with accumulation
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref2 = acc + 0.5 * (a.float() @ w.float().t())
+    out2 = ops.gemm_raw(a, False, w, False, M, N, K, out=acc.clone(), accumulate=True, alpha=0.5, bn_hint=bn)
+    assert _rel_err(out2, ref2) < 1e-2
+
+
+def test_gemm_persistent_many_tiles(kernel_status):
+    """More tiles than SMs: exercises the accumulator double-buffering and stage phase wrap."""
+    ops = _ops()
+    M, N, K = 4096, 4096, 256
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    out = ops.matmul_nt(a, w)
+    ref = a.float() @ w.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_linear_autograd(kernel_status):
+    ops = _ops()
+    x = torch.randn(4, 64, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(384, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(384, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+# ----------------------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("T,D", [(64, 256), (300, 4096), (17, 1024)])
+def test_rmsnorm_fwd_bwd(T, D, kernel_status):
+    ops = _ops()
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+def test_rmsnorm_fused_residual(kernel_status):
+    ops = _ops()
+    T, D = 96, 512
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y, h = ops.rms_norm(x, w, 1e-6, residual=r)
+    (y.float().sum() + 2 * h.float().sum()).backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = xr + rr
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    (yr.sum() + 2 * hr.sum()).backward()
+    assert _rel_err(h, hr) < 1e-2 and _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(r.grad, rr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("T,D", [(64, 768), (33, 128)])
+def test_layernorm_fwd_bwd(T, D, kernel_status):
+    ops = _ops()
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    b = (0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = ops.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (D,), wr, br, 1e-5)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+# ----------------------------------------------------------------------------------------- rope / activations
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_fwd_bwd(interleaved, kernel_status):
+    ops = _ops()
+    B, S, H, D = 2, 128, 4, 128
+    cos, sin = ops.rope_tables(S, D, 1e4, DEV)
+    qkv = torch.randn(B, S, 3 * H, D, device=DEV, dtype=torch.bfloat16)
+    x = qkv[:, :, :H].detach().clone().requires_grad_()          # contiguous copy
+    y = ops.rope(x, cos, sin, interleaved=interleaved)
+    ref = ops.rope_ref(x.detach().float(), cos, sin, interleaved)
+    assert _rel_err(y, ref) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    ops.rope_ref(xr, cos, sin, interleaved).backward(g.float())
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    # strided in-place on a packed view
+    packed = qkv.clone()
+    ops.rope(packed[:, :, :H], cos, sin, interleaved=interleaved, inplace=True)
+    assert _rel_err(packed[:, :, :H], ops.rope_ref(qkv[:, :, :H].float(), cos, sin, interleaved)) < 1e-2
+    assert torch.equal(packed[:, :, H:], qkv[:, :, H:])
+
+
+def test_swiglu_and_unary(kernel_status):
+    ops = _ops()
+    gu = torch.randn(64, 2 * 352, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = ops.swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    a, b = gr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(gu.grad, gr.grad) < 1e-2
+    for name in ["relu", "gelu", "sigmoid", "tanh", "silu"]:
+        x = torch.randn(1000, 8, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        y = ops.unary(x, name)
+        gg = torch.randn_like(y)
+        y.backward(gg)
+        xr = x.detach().float().requires_grad_()
+        from ghost_flow_b200.ops.fused import _unary_ref
+
+        yr = _unary_ref(xr, name)
+        yr.backward(gg.float())
+        assert _rel_err(y, yr) < 1e-2, name
+        assert _rel_err(x.grad, xr.grad) < 1.5e-2, name
+    z = ops.op_chain(torch.randn(999, device=DEV), ["gelu", "tanh", "relu"])
+    assert z.shape == (999,)
+
+
+# ----------------------------------------------------------------------------------------- loss / optimizer
+@pytest.mark.parametrize("T,V", [(64, 1000), (37, 32000), (8, 50264)])
+def test_xent_fused(T, V, kernel_status):
+    ops = _ops()
+    logits = (2 * torch.randn(T, V, device=DEV)).to(torch.bfloat16).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    loss = ops.cross_entropy(logits, tgt)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, tgt)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    assert _rel_err(logits.grad, lr.grad) < 2e-2
+
+
+def test_adamw_flat_matches_reference_formula(kernel_status):
+    from ghost_flow_b200.ops import optim_kernels as ok
+
+    n = 100003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(torch.bfloat16)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    lp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    lr, b1, b2, eps, wd = 3e-4, 0.9, 0.999, 1e-8, 0.01
+    for step in (1, 2, 3):
+        ok.adam_flat(p, m, v, g, lp, lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=step, decoupled=True)
+        gf = g.float()
+        mr = b1 * mr + (1 - b1) * gf
+        vr = b2 * vr + (1 - b2) * gf * gf
+        mh, vh = mr / (1 - b1 ** step), vr / (1 - b2 ** step)
+        pr = pr * (1 - lr * wd) - lr * mh / (vh.sqrt() + eps)
+    assert torch.allclose(p, pr, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(lp.float(), pr, rtol=1e-2, atol=1e-2)
+
+
+# ----------------------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [
+    (1, 128, 1, 1, 128, True), (1, 256, 2, 2, 128, True), (2, 512, 4, 2, 128, True), (1, 384, 2, 2, 64, True),
+    (1, 256, 2, 1, 128, False), (1, 200, 2, 2, 128, True), (1, 1024, 2, 2, 128, True)])
+def test_flash_attention_fwd(B, S, Hq, Hkv, D, causal, kernel_status):
+    ops = _ops()
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    ref = ops.attention_ref(q, k, v, causal=causal)
+    torch.cuda.synchronize()
+    assert _rel_err(o, ref) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [
+    (1, 128, 1, 1, 128, True), (1, 256, 2, 2, 128, True), (2, 512, 4, 2, 128, True), (1, 256, 2, 2, 64, True),
+    (1, 256, 2, 1, 128, False)])
+def test_flash_attention_bwd(B, S, Hq, Hkv, D, causal, kernel_status):
+    ops = _ops()
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    g = torch.randn_like(o)
+    o.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    qr, kr, vr = ref_in[:, :, :Hq], ref_in[:, :, Hq:Hq + Hkv], ref_in[:, :, Hq + Hkv:]
+    ops.attention_ref(qr, kr, vr, causal=causal).backward(g.float())
+    torch.cuda.synchronize()
+    gq, gk, gv = qkv.grad[:, :, :Hq], qkv.grad[:, :, Hq:Hq + Hkv], qkv.grad[:, :, Hq + Hkv:]
+    rq, rk, rv = ref_in.grad[:, :, :Hq], ref_in.grad[:, :, Hq:Hq + Hkv], ref_in.grad[:, :, Hq + Hkv:]
+    assert _rel_err(gv, rv) < 3e-2, "dV"
+    assert _rel_err(gk, rk) < 3e-2, "dK"
+    assert _rel_err(gq, rq) < 3e-2, "dQ"
