@@ -63,10 +63,14 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
 }
 
 static std::atomic<int> g_device{-1};
+static std::atomic<long long> g_launches{0};
+
+void note_extra_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // Every exported launcher calls this first: it binds the calling thread to the process's device in
 // this library's copy of the CUDA runtime (PyTorch keeps its own copy, with its own per-thread state).
 void enter() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   thread_local int bound = -2;
   const int d = g_device.load(std::memory_order_relaxed);
   if (d < 0) {
@@ -100,10 +104,10 @@ int sm_count() {
 // ------------------------------------------------------------------ C surface
 GF_API void gf_set_device(int dev) { gf::g_device.store(dev); }
 
-GF_API int gf_sm_count() {
-  gf::enter();
-  return gf::sm_count();
-}
+// Kernels launched by this library since load (every launcher counts its own kernels).
+GF_API long long gf_launch_count() { return gf::g_launches.load(); }
+
+GF_API int gf_sm_count() { return gf::sm_count(); }
 
 GF_API int gf_device_count() {
   int n = 0;

@@ -41,5 +41,7 @@ int sm_count();
 
 // Binds the calling thread to the device selected with gf_set_device (see gf_host.cu).
 void enter();
+// Launchers that start more than one kernel report the extra ones here (enter() counts one).
+void note_extra_launches(int n);
 
 }  // namespace gf

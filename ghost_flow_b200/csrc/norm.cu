@@ -323,6 +323,7 @@ GF_API int gf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const fl
       (__nv_bfloat16*)dx, scratch, T, D);
   fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
                                                                           accumulate);
+  gf::note_extra_launches(1);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
 
@@ -349,6 +350,7 @@ GF_API int gf_layernorm_bwd(const void* x, const void* w, const void* dy, const 
       scratch, s2, T, D);
   fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
                                                                           accumulate);
+  gf::note_extra_launches(db ? 2 : 1);
   if (db)
     fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(s2, (__nv_bfloat16*)db, g, D,
                                                                             accumulate);

@@ -430,6 +430,7 @@ GF_API int gf_reduce(const void* x, float* partial, float* out, long long n, int
   else
     reduce_stage1_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)x, partial, n, mode);
   reduce_stage2_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(partial, out, g, mode);
+  gf::note_extra_launches(1);
   GF_RET();
 }
 GF_API int gf_softmax_rows(const void* x, void* y, int rows, int cols, int log_mode, int dtype, void* stream) {

@@ -90,6 +90,14 @@ def cuda_lib():
     return _CUDA_LIB
 
 
+def launch_count() -> int:
+    """Kernels launched by the library so far in this process."""
+    fn = cuda_lib().gf_launch_count
+    fn.restype = ctypes.c_longlong
+    fn.argtypes = []
+    return int(fn())
+
+
 def has_cuda_lib() -> bool:
     return lib_path().exists()
 

@@ -1,0 +1,412 @@
+"""Hand-scheduled ZeRO-3 training engine for LLaMA-family decoders.
+
+One process per GPU. Every unit (the embedding, each decoder layer, the head) is ONE flat bf16
+buffer cut into equal shards across the ranks; each rank also holds the fp32 master weights and
+Adam moments of its shard only. A step walks the layers with explicit forward and backward
+kernels (no autograd graph):
+
+    forward : all-gather(layer i+1) runs on the communication stream while layer i computes
+    backward: all-gather(layer i-1) is prefetched; layer i's weight gradients are written by the
+              wgrad GEMMs straight into a flat gradient buffer, which is reduce-scattered and fed
+              to the fused AdamW on the shard while layer i-1 is already computing
+
+so parameters, gradients and optimizer state are all partitioned (stage 3), at most two gathered
+layers and two gradient buffers exist at any time, and the optimizer never sees a full model.
+
+Replaces the reference's in-process simulation: whole-tensor "ownership", reduce-scatter = divide
+by world size, all-gather = clone, Adam without bias correction
+(ghostflow-nn/src/zero_optimizer.rs:149-195,220-259,262-309).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..models.configs import LLaMAConfig
+from ..ops import raw as K
+from ..ops.fused import rope_tables
+
+
+@dataclass
+class OptimConfig:
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+
+
+class _Unit:
+    """One flat parameter unit and this rank's shard of it."""
+
+    def __init__(self, name, specs, world, rank, device, dtype, align=8):
+        self.name = name
+        self.specs = []  # (pname, offset, shape)
+        off = 0
+        for pname, shape in specs:
+            n = math.prod(shape)
+            self.specs.append((pname, off, tuple(shape)))
+            off += (n + align - 1) // align * align
+        self.numel = off
+        quantum = world * 16
+        self.padded = (off + quantum - 1) // quantum * quantum
+        self.shard_numel = self.padded // world
+        self.lo = rank * self.shard_numel
+        self.shard = torch.zeros(self.shard_numel, dtype=dtype, device=device)
+        self.master = None
+        self.m = None
+        self.v = None
+
+    def views(self, flat):
+        return {p: flat[o:o + math.prod(s)].view(s) for p, o, s in self.specs}
+
+
+class Comm:
+    """Collective plumbing for the engine: NCCL/gloo baseline. ``world == 1`` is a no-op."""
+
+    def __init__(self, group=None):
+        self.group = group
+        if dist.is_available() and dist.is_initialized():
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
+            self.backend = dist.get_backend(group)
+        else:
+            self.world, self.rank, self.backend = 1, 0, "none"
+
+    def all_gather(self, shard, full):
+        if self.world == 1:
+            return
+        dist.all_gather_into_tensor(full, shard, group=self.group)
+
+    def reduce_scatter(self, full, shard_out):
+        """Sum over ranks of ``full`` cut into world pieces; piece ``rank`` lands in ``shard_out``."""
+        if self.world == 1:
+            return
+        if self.backend == "nccl":
+            dist.reduce_scatter_tensor(shard_out, full, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            tmp = full.float()
+            dist.all_reduce(tmp, group=self.group)
+            n = shard_out.numel()
+            shard_out.copy_(tmp[self.rank * n:(self.rank + 1) * n].to(shard_out.dtype))
+
+    def all_reduce_scalar(self, t):
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+
+class _Streams:
+    """Compute / communication / optimizer streams (all None on CPU, where everything is serial)."""
+
+    def __init__(self, device):
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            self.comm = torch.cuda.Stream(device)
+            self.opt = torch.cuda.Stream(device)
+
+    def event(self):
+        return torch.cuda.Event() if self.cuda else None
+
+
+class Zero3LlamaEngine:
+    """ZeRO-3 trainer for :class:`LLaMAConfig` models (dense decoder, GQA allowed)."""
+
+    def __init__(self, cfg: LLaMAConfig, device, optim: OptimConfig | None = None, group=None, seed: int = 0,
+                 dtype=torch.bfloat16, comm: Comm | None = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.opt = optim or OptimConfig()
+        self.comm = comm or Comm(group)
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.streams = _Streams(self.device)
+        self.step_count = 0
+        d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+        hd = cfg.head_dim
+        self.qkv_out = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * hd
+        layer_specs = [("attn_norm", (d,)), ("wqkv", (self.qkv_out, d)), ("wo", (d, cfg.num_attention_heads * hd)),
+                       ("ffn_norm", (d,)), ("w_gate_up", (2 * f, d)), ("w_down", (d, f))]
+        mk = lambda name, specs: _Unit(name, specs, self.world, self.rank, self.device, dtype)
+        self.embed = mk("embed", [("tok_emb", (v, d))])
+        self.layers = [mk(f"layer{i}", layer_specs) for i in range(cfg.num_hidden_layers)]
+        self.head = mk("head", [("final_norm", (d,)), ("lm_head", (v, d))])
+        self.units = [self.embed, *self.layers, self.head]
+        self._init_params(seed)
+        max_padded = max(u.padded for u in self.units)
+        if self.world > 1:
+            self.full = [torch.empty(max_padded, dtype=dtype, device=self.device) for _ in range(2)]
+            self.gshard = torch.empty(max(u.shard_numel for u in self.units), dtype=dtype, device=self.device)
+        self.gfull = [torch.zeros(max_padded, dtype=dtype, device=self.device) for _ in range(2)]
+        self._rope = None
+        self.last_stats = {}
+
+    # ------------------------------------------------------------------ init
+    def _init_params(self, seed):
+        """N(0, std) weights, unit norm gains; each unit is generated whole from its own seed (so every
+        world size sees the same model) and only this rank's slice is kept."""
+        std = self.cfg.initializer_range
+        for ui, u in enumerate(self.units):
+            gen = torch.Generator(device=self.device)
+            gen.manual_seed(seed * 100003 + ui)
+            flat = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
+            for pname, off, shape in u.specs:
+                n = math.prod(shape)
+                if pname.endswith("norm"):
+                    flat[off:off + n] = 1.0
+                else:
+                    flat[off:off + n].normal_(0.0, std, generator=gen)
+            sl = flat[u.lo:u.lo + u.shard_numel]
+            u.master = sl.clone()
+            u.shard.copy_(sl.to(self.dtype))
+            u.m = torch.zeros_like(u.master)
+            u.v = torch.zeros_like(u.master)
+            del flat
+
+    def load_unit(self, unit: _Unit, named: dict):
+        """Overwrites a unit from full named tensors (used by tests and checkpoint loading)."""
+        flat = torch.zeros(unit.padded, dtype=torch.float32, device=self.device)
+        for pname, off, shape in unit.specs:
+            flat[off:off + math.prod(shape)] = named[pname].to(self.device, torch.float32).reshape(-1)
+        sl = flat[unit.lo:unit.lo + unit.shard_numel]
+        unit.master.copy_(sl)
+        unit.shard.copy_(sl.to(self.dtype))
+
+    def gather_unit(self, unit: _Unit, master: bool = False) -> dict:
+        """Full named tensors of a unit on every rank (fp32 master copy or the bf16 weights)."""
+        src = unit.master if master else unit.shard
+        if self.world == 1:
+            flat = src
+        else:
+            flat = torch.empty(unit.padded, dtype=src.dtype, device=self.device)
+            self.comm.all_gather(src.contiguous(), flat)
+        return {k: v.clone() for k, v in unit.views(flat).items()}
+
+    # ------------------------------------------------------------------ gather / scatter scheduling
+    def _gather_async(self, unit, slot):
+        """Starts the all-gather of ``unit`` into buffer ``slot``; returns (flat_full, event)."""
+        if self.world == 1:
+            return unit.shard, None
+        st = self.streams
+        full = self.full[slot][:unit.padded]
+        if st.cuda:
+            st.comm.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st.comm):
+                self.comm.all_gather(unit.shard, full)
+                ev = st.event()
+                ev.record(st.comm)
+            return full, ev
+        self.comm.all_gather(unit.shard, full)
+        return full, None
+
+    def _wait(self, ev):
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _reduce_and_update(self, unit, slot):
+        """Gradient reduce-scatter + AdamW on this rank's shard, off the compute stream.
+        Returns an event that marks when gradient buffer ``slot`` may be overwritten."""
+        st = self.streams
+        g_full = self.gfull[slot][:unit.padded]
+        o = self.opt
+        kw = dict(lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay,
+                  step=self.step_count)
+
+        def run():
+            if self.world == 1:
+                g = g_full
+            else:
+                g = self.gshard[:unit.shard_numel]
+                self.comm.reduce_scatter(g_full, g)
+            K.adamw_flat(unit.master, unit.m, unit.v, g, unit.shard, **kw)
+
+        if st.cuda:
+            side = st.opt if self.world == 1 else st.comm
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()
+                ev = st.event()
+                ev.record(side)
+            return ev
+        run()
+        return None
+
+    # ------------------------------------------------------------------ layer math
+    def _rope_tables(self, S):
+        if self._rope is None or self._rope[0].shape[0] < S:
+            self._rope = rope_tables(S, self.cfg.head_dim, self.cfg.rope_theta, self.device)
+        return self._rope
+
+    def _layer_fwd(self, w, x, B, S):
+        c = self.cfg
+        Hq, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        cos, sin = self._rope_tables(S)
+        h1, rstd1, _ = K.rmsnorm_fwd(x, w["attn_norm"], c.rms_norm_eps)
+        qkv = K.gemm(h1, False, w["wqkv"], True)
+        T = x.shape[0]
+        K.rope_(qkv.view(T, Hq + 2 * Hkv, hd)[:, :Hq + Hkv], cos, sin, S, c.rope_interleaved)
+        q, k, v = qkv[:, :Hq * hd], qkv[:, Hq * hd:(Hq + Hkv) * hd], qkv[:, (Hq + Hkv) * hd:]
+        attn, lse = K.attn_fwd(q, k, v, B, S, Hq, Hkv, hd, causal=True)
+        x2 = K.gemm(attn, False, w["wo"], True, residual=x)
+        h2, rstd2, _ = K.rmsnorm_fwd(x2, w["ffn_norm"], c.rms_norm_eps)
+        gu = K.gemm(h2, False, w["w_gate_up"], True)
+        act = K.swiglu_fwd(gu)
+        out = K.gemm(act, False, w["w_down"], True, residual=x2)
+        saved = (x, rstd1, h1, qkv, attn, lse, x2, rstd2, h2, gu, act)
+        return out, saved
+
+    def _layer_bwd(self, w, g, saved, dout, B, S):
+        c = self.cfg
+        Hq, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        cos, sin = self._rope_tables(S)
+        x, rstd1, h1, qkv, attn, lse, x2, rstd2, h2, gu, act = saved
+        T = x.shape[0]
+        # MLP
+        dact = K.gemm(dout, False, w["w_down"], False)
+        K.gemm(dout, True, act, False, out=g["w_down"])
+        dgu = K.swiglu_bwd(gu, dact)
+        del dact
+        dh2 = K.gemm(dgu, False, w["w_gate_up"], False)
+        K.gemm(dgu, True, h2, False, out=g["w_gate_up"])
+        del dgu
+        dx2, _ = K.rmsnorm_bwd(x2, w["ffn_norm"], dh2, rstd2, dres=dout, dw_out=g["ffn_norm"])
+        # attention
+        dattn = K.gemm(dx2, False, w["wo"], False)
+        K.gemm(dx2, True, attn, False, out=g["wo"])
+        dqkv = torch.empty_like(qkv)
+        q, k, v = qkv[:, :Hq * hd], qkv[:, Hq * hd:(Hq + Hkv) * hd], qkv[:, (Hq + Hkv) * hd:]
+        dq, dk, dv = dqkv[:, :Hq * hd], dqkv[:, Hq * hd:(Hq + Hkv) * hd], dqkv[:, (Hq + Hkv) * hd:]
+        K.attn_bwd(q, k, v, attn, dattn, lse, dq, dk, dv, B, S, Hq, Hkv, hd, causal=True)
+        K.rope_(dqkv.view(T, Hq + 2 * Hkv, hd)[:, :Hq + Hkv], cos, sin, S, c.rope_interleaved, backward=True)
+        dh1 = K.gemm(dqkv, False, w["wqkv"], False)
+        K.gemm(dqkv, True, h1, False, out=g["wqkv"])
+        dx, _ = K.rmsnorm_bwd(x, w["attn_norm"], dh1, rstd1, dres=dx2, dw_out=g["attn_norm"])
+        return dx
+
+    # ------------------------------------------------------------------ one training step
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One optimizer step on this rank's micro-batch ``tokens/targets [B, S]`` (int64, on device).
+        Returns the global mean loss as a 0-d fp32 tensor on the device."""
+        c = self.cfg
+        B, S = tokens.shape
+        T = B * S
+        self.step_count += 1
+        L = len(self.layers)
+        tok = tokens.reshape(-1)
+        tgt = targets.reshape(-1)
+
+        # ---------------- forward
+        # Gathered-weight slots: embedding -> 0, layer i -> (i + 1) % 2, head -> (L - 1) % 2 (or 1 when L == 0).
+        # _gather_async makes the communication stream wait for everything already submitted on the
+        # compute stream, i.e. for the previous user of the slot, and no more.
+        emb_full, ev = self._gather_async(self.embed, 0)
+        nxt = self._gather_async(self.layers[0] if L else self.head, 1)
+        self._wait(ev)
+        x = self.embed.views(emb_full)["tok_emb"].index_select(0, tok)
+        saved = []
+        w_full = None
+        for i, unit in enumerate(self.layers):
+            w_full, ev = nxt
+            nxt = self._gather_async(self.layers[i + 1] if i + 1 < L else self.head, i % 2)
+            self._wait(ev)
+            x, sv = self._layer_fwd(unit.views(w_full), x, B, S)
+            saved.append(sv)
+        head_full, ev = nxt
+        self._wait(ev)
+        hw = self.head.views(head_full)
+        hF, rstdF, _ = K.rmsnorm_fwd(x, hw["final_norm"], c.rms_norm_eps)
+        logits = K.gemm(hF, False, hw["lm_head"], True)
+        loss = K.xent_fwd_bwd(logits, tgt, grad_scale=1.0 / (T * self.world)) * self.world  # local mean
+
+        # ---------------- backward
+        grad_free = [None, None]   # events: gradient buffer slot may be overwritten
+        gslot = 0
+        gh = self.head.views(self.gfull[gslot][:self.head.padded])
+        dhF = K.gemm(logits, False, hw["lm_head"], False)
+        K.gemm(logits, True, hF, False, out=gh["lm_head"])
+        del logits
+        dx, _ = K.rmsnorm_bwd(x, hw["final_norm"], dhF, rstdF, dw_out=gh["final_norm"])
+        grad_free[gslot] = self._reduce_and_update(self.head, gslot)
+        # the last layer's weights are still gathered in their slot from the forward pass
+        nxt = (w_full, None)
+        for i in range(L - 1, -1, -1):
+            unit = self.layers[i]
+            gslot = 1 - gslot
+            w_full, ev = nxt
+            if i > 0:
+                nxt = self._gather_async(self.layers[i - 1], i % 2)
+            self._wait(ev)
+            self._wait(grad_free[gslot])
+            g = unit.views(self.gfull[gslot][:unit.padded])
+            dx = self._layer_bwd(unit.views(w_full), g, saved.pop(), dx, B, S)
+            grad_free[gslot] = self._reduce_and_update(unit, gslot)
+        # embedding gradient: scatter-add of dx rows
+        gslot = 1 - gslot
+        self._wait(grad_free[gslot])
+        ge = self.embed.views(self.gfull[gslot][:self.embed.padded])["tok_emb"]
+        ge.zero_()
+        ge.index_add_(0, tok, dx)
+        grad_free[gslot] = self._reduce_and_update(self.embed, gslot)
+        for e in grad_free:
+            self._wait(e)
+        if self.world > 1:
+            loss = self.comm.all_reduce_scalar(loss.clone()) / self.world
+        return loss
+
+    # ------------------------------------------------------------------ inference-style forward (no grad state)
+    @torch.no_grad()
+    def forward_logits(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Logits ``[B, S, vocab]`` with the current weights (gathers one unit at a time, no prefetch)."""
+        B, S = tokens.shape
+        emb_full, ev = self._gather_async(self.embed, 0)
+        self._wait(ev)
+        x = self.embed.views(emb_full)["tok_emb"].index_select(0, tokens.reshape(-1))
+        slot = 1
+        for unit in self.layers:
+            w_full, ev = self._gather_async(unit, slot)
+            self._wait(ev)
+            x, _ = self._layer_fwd(unit.views(w_full), x, B, S)
+            slot = 1 - slot
+        head_full, ev = self._gather_async(self.head, slot)
+        self._wait(ev)
+        hw = self.head.views(head_full)
+        hF, _, _ = K.rmsnorm_fwd(x, hw["final_norm"], self.cfg.rms_norm_eps)
+        return K.gemm(hF, False, hw["lm_head"], True).view(B, S, -1)
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self, master: bool = True) -> dict:
+        """Full (gathered) named tensors with PyTorch-style dotted names."""
+        out = {}
+        out["embed_tokens.weight"] = self.gather_unit(self.embed, master)["tok_emb"]
+        for i, u in enumerate(self.layers):
+            for k, v in self.gather_unit(u, master).items():
+                out[f"layers.{i}.{k}"] = v
+        h = self.gather_unit(self.head, master)
+        out["norm.weight"] = h["final_norm"]
+        out["lm_head.weight"] = h["lm_head"]
+        return out
+
+    def shard_state(self) -> dict:
+        """This rank's shards (weights, master, moments) for sharded checkpoints."""
+        st = {"step": self.step_count, "world": self.world, "rank": self.rank}
+        for u in self.units:
+            st[f"{u.name}.master"] = u.master
+            st[f"{u.name}.exp_avg"] = u.m
+            st[f"{u.name}.exp_avg_sq"] = u.v
+        return st
+
+    def load_shard_state(self, st: dict) -> None:
+        self.step_count = int(st["step"])
+        for u in self.units:
+            u.master.copy_(st[f"{u.name}.master"])
+            u.m.copy_(st[f"{u.name}.exp_avg"])
+            u.v.copy_(st[f"{u.name}.exp_avg_sq"])
+            u.shard.copy_(u.master.to(self.dtype))
+
+    def memory_summary(self) -> dict:
+        per_rank = sum(u.shard_numel for u in self.units)
+        return {"params_total": sum(u.numel for u in self.units), "shard_elems": per_rank,
+                "bytes_weights_bf16": per_rank * 2, "bytes_optimizer_fp32": per_rank * 12}
