@@ -86,6 +86,8 @@ void enter() {
   }
 }
 
+int process_device() { return g_device.load(std::memory_order_relaxed); }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -43,5 +43,7 @@ int sm_count();
 void enter();
 // Launchers that start more than one kernel report the extra ones here (enter() counts one).
 void note_extra_launches(int n);
+// Device index selected with gf_set_device, or -1 when none was selected.
+int process_device();
 
 }  // namespace gf
