@@ -180,7 +180,8 @@ def main():
     _lib.check_status(device)
 
     # ---- device-timed region: exactly K steps
-    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid) if rank == 0 else None)
+    uuid = str(torch.cuda.get_device_properties(device).uuid)
+    sampler = ClockSampler((uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None)
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()

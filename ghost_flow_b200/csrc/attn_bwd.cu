@@ -19,7 +19,7 @@ namespace gf {
 
 constexpr int FB_KV = 128;  // kv rows per CTA
 constexpr int FB_Q = 64;    // query rows per step
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;  // TMA warp, MMA warp, 2 x 4 compute warps (each group owns 32 of the 64 query columns)
 
 struct FaBwdParams {
   int B, S, Hq, Hkv;
@@ -112,12 +112,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       mbar_init(&q_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 4);
-    mbar_init(pds_full, 4);
+    mbar_init(s_empty, 8);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&dq_full[i], 1);
-      mbar_init(&dq_empty[i], 4);
+      mbar_init(&dq_empty[i], 8);
     }
     mbar_init(acc_full, 1);
     mbar_fence_init();
@@ -236,13 +236,17 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (ok) umma_commit(acc_full);
     }
   } else {
-    // ---------------------------------------------------------------- compute warps (2..5)
+    // ---------------------------------------------------------------- compute warps (2..9)
+    // Warps 2..5 own query columns 0..31 of S^T / dP^T / dQ^T, warps 6..9 own columns 32..63; within a
+    // group, warp w owns TMEM lanes 32 * (w % 4) .. +31, one kv row (or one head-dim row of dQ^T) per thread.
+    const int hf = (warp - 2) >> 2;
     const int lane_grp = warp & 3;
-    const int r = lane_grp * 32 + lane;        // kv row inside the tile == hd index when draining dQ^T
+    const int r = lane_grp * 32 + lane;
     const int kv_idx = j * FB_KV + r;
     const uint32_t tlane = (uint32_t)(lane_grp * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     const float l2e = 1.4426950408889634f;
+    const long long dq_ld = (long long)p.Hq * HD;
     bool ok = true;
 
     auto drain_dq = [&](int it) -> bool {
@@ -253,21 +257,17 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc_fence_after();
       const int h = hk * G + it / per_head;
       const int i = i_start + it % per_head;
-      float* dst = p.dq_acc + (long long)(row_base + i * FB_Q) * ((long long)p.Hq * HD) + h * HD + r;
-#pragma unroll
-      for (int c = 0; c < FB_Q / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_base + Cfg::TM_DQ + (it & 1) * FB_Q + c * 32 + tlane, rr);
-        tmem_ld_wait();
-        if (r < HD) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            atomicAdd(dst + (long long)(c * 32 + e) * ((long long)p.Hq * HD), __uint_as_float(rr[e]));
-        }
-      }
+      float* dst = p.dq_acc + (long long)(row_base + i * FB_Q + hf * 32) * dq_ld + h * HD + r;
+      uint32_t rr[32];
+      tmem_ld32(tmem_base + Cfg::TM_DQ + (it & 1) * FB_Q + hf * 32 + tlane, rr);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_empty[it & 1]);
+      if (r < HD) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) atomicAdd(dst + (long long)e * dq_ld, __uint_as_float(rr[e]));
+      }
       return true;
     };
 
@@ -280,35 +280,41 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         break;
       }
       tc_fence_after();
-      const float* lse_s = sStat + st * 2 * FB_Q;
+      const float* lse_s = sStat + st * 2 * FB_Q + hf * 32;
       const float* del_s = lse_s + FB_Q;
-      const int q0 = i * FB_Q;
-      const bool diag = p.causal && (q0 < j * FB_KV + FB_KV);  // tile touches the diagonal
-      uint32_t pp[32], dd[32];
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
+      const int q0 = i * FB_Q + hf * 32;
+      const bool diag = p.causal && (q0 < j * FB_KV + FB_KV);  // these columns touch the diagonal
+      uint32_t pp[16], dd[16];
+      {
         uint32_t sv[32], dpv[32];
         tmem_ld32(tmem_base + Cfg::TM_S + hf * 32 + tlane, sv);
         tmem_ld32(tmem_base + Cfg::TM_DP + hf * 32 + tlane, dpv);
         tmem_ld_wait();
-        if (hf == 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(s_empty);
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);
+        if (!diag) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const int c = hf * 32 + e;
-          float p0 = exp2f(__uint_as_float(sv[e]) * sl2 - lse_s[c] * l2e);
-          float p1 = exp2f(__uint_as_float(sv[e + 1]) * sl2 - lse_s[c + 1] * l2e);
-          if (diag) {
-            if (q0 + c < kv_idx) p0 = 0.f;
-            if (q0 + c + 1 < kv_idx) p1 = 0.f;
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), sl2, -lse_s[e] * l2e));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), sl2, -lse_s[e + 1] * l2e));
+            const float d0 = p0 * (__uint_as_float(dpv[e]) - del_s[e]) * p.scale;
+            const float d1 = p1 * (__uint_as_float(dpv[e + 1]) - del_s[e + 1]) * p.scale;
+            pp[e >> 1] = pack_bf16x2(p0, p1);
+            dd[e >> 1] = pack_bf16x2(d0, d1);
           }
-          const float d0 = p0 * (__uint_as_float(dpv[e]) - del_s[c]) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dpv[e + 1]) - del_s[c + 1]) * p.scale;
-          pp[c >> 1] = pack_bf16x2(p0, p1);
-          dd[c >> 1] = pack_bf16x2(d0, d1);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), sl2, -lse_s[e] * l2e));
+            float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), sl2, -lse_s[e + 1] * l2e));
+            if (q0 + e < kv_idx) p0 = 0.f;
+            if (q0 + e + 1 < kv_idx) p1 = 0.f;
+            const float d0 = p0 * (__uint_as_float(dpv[e]) - del_s[e]) * p.scale;
+            const float d1 = p1 * (__uint_as_float(dpv[e + 1]) - del_s[e + 1]) * p.scale;
+            pp[e >> 1] = pack_bf16x2(p0, p1);
+            dd[e >> 1] = pack_bf16x2(d0, d1);
+          }
         }
       }
       if (!mbar_wait_warp(pds_empty, (it & 1) ^ 1)) {
@@ -317,10 +323,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         break;
       }
 #pragma unroll
-      for (int c16 = 0; c16 < 8; ++c16) {
-        const uint32_t off = sw128_offset((uint32_t)r, (uint32_t)c16);
-        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c16 * 4], pp[c16 * 4 + 1], pp[c16 * 4 + 2], pp[c16 * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[c16 * 4], dd[c16 * 4 + 1], dd[c16 * 4 + 2], dd[c16 * 4 + 3]);
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint32_t off = sw128_offset((uint32_t)r, (uint32_t)(hf * 4 + c4));
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c4 * 4], pp[c4 * 4 + 1], pp[c4 * 4 + 2], pp[c4 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[c4 * 4], dd[c4 * 4 + 1], dd[c4 * 4 + 2], dd[c4 * 4 + 3]);
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -335,8 +341,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         tc_fence_after();
         __nv_bfloat16* dkr = p.dK + (long long)(row_base + kv_idx) * p.lddk + hk * HD;
         __nv_bfloat16* dvr = p.dV + (long long)(row_base + kv_idx) * p.lddv + hk * HD;
+        // each group writes half of the head dimension
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int cc = 0; cc < HD / 64; ++cc) {
+          const int c = hf * (HD / 64) + cc;
           uint32_t rk[32], rv[32];
           tmem_ld32(tmem_base + Cfg::TM_DK + c * 32 + tlane, rk);
           tmem_ld32(tmem_base + Cfg::TM_DV + c * 32 + tlane, rv);

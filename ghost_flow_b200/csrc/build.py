@@ -36,6 +36,7 @@ CUDA_SOURCES = [
     "pointwise.cu",
     "xent_adamw.cu",
     "attn_fwd.cu",
+    "attn_fwd2.cu",
     "attn_bwd.cu",
     "comm_kernels.cu",
     "moe_kernels.cu",

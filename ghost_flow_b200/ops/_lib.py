@@ -47,6 +47,7 @@ _SIGS = {
     "gf_sgd_flat": [P, P, P, P, L, F, F, F, F, I, I, F, I, P],
     "gf_grad_sumsq": [P, L, P, I, P],
     "gf_flash_attn_fwd": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
+    "gf_flash_attn_fwd2": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
     "gf_flash_attn_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
     "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
     "gf_cast_f32_to_bf16_2d": [P, P, L, I, L, L, F, P],
@@ -178,3 +179,9 @@ def check_rc(rc: int, what: str) -> None:
 
 
 DEBUG_SYNC = os.environ.get("GF_DEBUG_SYNC", "0") == "1"
+
+
+def flash_fwd_fn():
+    """Forward attention launcher: the two-tile ping-pong kernel unless GF_FA_FWD=1 selects the first one."""
+    lib = cuda_lib()
+    return lib.gf_flash_attn_fwd if os.environ.get("GF_FA_FWD", "2") == "1" else lib.gf_flash_attn_fwd2

@@ -402,7 +402,7 @@ class _FlashAttnFn(torch.autograd.Function):
         o = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
         lib = _lib.cuda_lib()
-        _rc(lib.gf_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, Hq,
+        _rc(_lib.flash_fwd_fn()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, Hq,
                                   Hkv, D, ldq, ldk, ldv, Hq * D, float(scale), 1 if causal else 0,
                                   _lib.status_word(q.device).data_ptr(), _lib.stream_ptr()), "gf_flash_attn_fwd")
         ctx.save_for_backward(q, k, v, o, lse)

@@ -144,7 +144,7 @@ def attn_fwd(q, k, v, B, S, Hq, Hkv, D, causal=True, scale=None):
     if _k(q):
         o = torch.empty((B * S, Hq * D), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
-        _rc(_lib.cuda_lib().gf_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+        _rc(_lib.flash_fwd_fn()(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                               B, S, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), Hq * D,
                                               float(scale), 1 if causal else 0,
                                               _lib.status_word(q.device).data_ptr(), _lib.stream_ptr()),

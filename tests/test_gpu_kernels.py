@@ -259,3 +259,29 @@ def test_flash_attention_bwd(B, S, Hq, Hkv, D, causal, kernel_status):
     assert _rel_err(gv, rv) < 3e-2, "dV"
     assert _rel_err(gk, rk) < 3e-2, "dK"
     assert _rel_err(gq, rq) < 3e-2, "dQ"
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 256, 2, 2, 128, True), (1, 384, 2, 1, 64, False)])
+def test_flash_attention_fwd_first_generation_kernel(B, S, Hq, Hkv, D, causal, kernel_status, monkeypatch):
+    """The single-tile forward kernel stays available (GF_FA_FWD=1) and must agree with the reference too."""
+    monkeypatch.setenv("GF_FA_FWD", "1")
+    ops = _ops()
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    assert _rel_err(o, ops.attention_ref(q, k, v, causal=causal)) < 2e-2
+
+
+def test_flash_attention_fwd_large_scores_rescale(kernel_status):
+    """Scores that keep growing along the sequence force the in-TMEM output rescale path many times."""
+    ops = _ops()
+    B, S, H, D = 1, 1024, 2, 128
+    q = torch.randn(B, S, H, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, S, H, D, device=DEV, dtype=torch.bfloat16)
+    ramp = torch.linspace(0.2, 6.0, S, device=DEV).view(1, S, 1, 1)
+    k = (k * ramp).to(torch.bfloat16)
+    v = torch.randn(B, S, H, D, device=DEV, dtype=torch.bfloat16)
+    o = ops.flash_attention(q, k, v, causal=True)
+    assert _rel_err(o, ops.attention_ref(q, k, v, causal=True)) < 2e-2
+    o2 = ops.flash_attention(q, k, v, causal=False)
+    assert _rel_err(o2, ops.attention_ref(q, k, v, causal=False)) < 2e-2
