@@ -1,0 +1,347 @@
+// Collectives written as kernels over peer-mapped (symmetric) memory on one NVSwitch box.
+//
+//  * gf_signal_peers / gf_wait_flags : system-scope release/acquire flags in each rank's signal pad.
+//  * gf_rs_adamw_fused : gradient reduce-scatter fused with the sharded AdamW update. Each rank reads its
+//      slice of EVERY rank's bf16 gradient buffer straight over NVLink (plain peer loads, or one
+//      multimem.ld_reduce through the switch when a multicast mapping is given), sums in fp32, and
+//      applies AdamW to its fp32 master/moment shard, writing the bf16 weight shard in the same pass.
+//      The reduced gradient never exists in memory.
+//  * gf_allgather_pull : parameter all-gather; each rank copies the peers' bf16 shards into its local
+//      gathered buffer and raises one local flag per source shard, which the GEMM producer
+//      (gemm_bf16.cu, b_ready) can wait on tile by tile.
+//
+// Every wait is bounded and reports through the status word; nothing here uses TMA, let alone
+// cluster multicast, on peer memory.
+//
+// The reference only simulates these collectives in-process (reduce-scatter = divide by world size,
+// all-gather = clone: ghostflow-nn/src/zero_optimizer.rs:220-259) and its optimizer step has no bias
+// correction or weight decay (zero_optimizer.rs:262-309); the update here is the AdamW of
+// ghostflow-optim/src/adam.rs:162-197.
+#include "gf_host.h"
+#include "gf_ptx.cuh"
+
+namespace gf {
+
+constexpr int MAX_RANKS = 8;
+
+struct PeerPtrs {
+  const void* p[MAX_RANKS];
+};
+struct PeerFlagPtrs {
+  int* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until *flag >= value. Returns false when the limit ran out.
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int value, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (ld_acquire_sys(flag) >= value) return true;
+    __nanosleep(100);
+  }
+  return false;
+}
+
+// ------------------------------------------------------------------ flags
+// Thread r writes `value` into rank r's pad at index idx_base + my_rank.
+__global__ void signal_peers_kernel(PeerFlagPtrs pads, int idx_base, int my_rank, int world, int value) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(pads.p[r] + idx_base + my_rank, value);
+  }
+}
+
+// Thread r waits for local_pad[idx_base + r] >= value.
+__global__ void wait_flags_kernel(const int* local_pad, int idx_base, int world, int value, uint32_t limit,
+                                  int* status) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    if (!wait_flag_ge(local_pad + idx_base + r, value, limit) && status) atomicCAS(status, 0, GF_ERR_WAIT_PEER);
+  }
+}
+
+// ------------------------------------------------------------------ reduce-scatter + AdamW
+struct RsAdamArgs {
+  PeerPtrs grads;           // each rank's full bf16 gradient buffer (same layout everywhere)
+  const void* mc_grads;     // multicast mapping of the same buffer, or null
+  long long shard_lo;       // first element of this rank's shard inside the full buffer
+  long long n;              // shard elements (multiple of 8)
+  float* master;
+  float* m;
+  float* v;
+  __nv_bfloat16* p_lp;      // bf16 weight shard (may be null)
+  float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale;
+  int world, my_rank;
+  // flags
+  const int* local_pad;     // this rank's pad
+  PeerFlagPtrs pads;        // every rank's pad
+  int ready_idx;            // wait: local_pad[ready_idx + r] >= ready_val for all r
+  int ready_val;
+  int consumed_idx;         // afterwards: pads[r][consumed_idx + my_rank] = consumed_val
+  int consumed_val;
+  int version_idx;          // afterwards: pads[r][version_idx + my_rank] = version_val (weights updated)
+  int version_val;
+  int* done_counter;        // local int, zero before launch; reset by the last block
+  uint32_t wait_limit;
+  int* status;
+};
+
+template <bool USE_MC>
+__global__ void __launch_bounds__(256)
+rs_adamw_kernel(const RsAdamArgs a) {
+  __shared__ int s_ok;
+  if (threadIdx.x < 32) {
+    bool ok = true;
+    if (threadIdx.x < a.world) ok = wait_flag_ge(a.local_pad + a.ready_idx + threadIdx.x, a.ready_val, a.wait_limit);
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0) {
+      s_ok = ok ? 1 : 0;
+      if (!ok && a.status) atomicCAS(a.status, 0, GF_ERR_WAIT_PEER);
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long long nvec = a.n >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+      float g[8];
+      if (USE_MC) {
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.mc_grads) + a.shard_lo + i * 8;
+        uint32_t r0, r1, r2, r3;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                     : "l"(src)
+                     : "memory");
+        float2 f0 = unpack_bf16x2(r0), f1 = unpack_bf16x2(r1), f2 = unpack_bf16x2(r2), f3 = unpack_bf16x2(r3);
+        g[0] = f0.x; g[1] = f0.y; g[2] = f1.x; g[3] = f1.y; g[4] = f2.x; g[5] = f2.y; g[6] = f3.x; g[7] = f3.y;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 0.f;
+        uint4 u[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r < a.world) {
+            // start with the next rank after mine so the eight ranks do not all hit the same peer at once
+            int src_rank = a.my_rank + 1 + r;
+            if (src_rank >= a.world) src_rank -= a.world;
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.grads.p[src_rank]) + a.shard_lo + i * 8;
+            u[r] = *reinterpret_cast<const uint4*>(src);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r < a.world) {
+            float2 f0 = unpack_bf16x2(u[r].x), f1 = unpack_bf16x2(u[r].y), f2 = unpack_bf16x2(u[r].z),
+                   f3 = unpack_bf16x2(u[r].w);
+            g[0] += f0.x; g[1] += f0.y; g[2] += f1.x; g[3] += f1.y;
+            g[4] += f2.x; g[5] += f2.y; g[6] += f3.x; g[7] += f3.y;
+          }
+        }
+      }
+      float pv[8], mv[8], vv[8];
+      *reinterpret_cast<float4*>(pv) = reinterpret_cast<const float4*>(a.master)[i * 2];
+      *reinterpret_cast<float4*>(pv + 4) = reinterpret_cast<const float4*>(a.master)[i * 2 + 1];
+      *reinterpret_cast<float4*>(mv) = reinterpret_cast<const float4*>(a.m)[i * 2];
+      *reinterpret_cast<float4*>(mv + 4) = reinterpret_cast<const float4*>(a.m)[i * 2 + 1];
+      *reinterpret_cast<float4*>(vv) = reinterpret_cast<const float4*>(a.v)[i * 2];
+      *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<const float4*>(a.v)[i * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gj = g[j] * a.grad_scale;
+        mv[j] = a.beta1 * mv[j] + (1.f - a.beta1) * gj;
+        vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
+        const float mh = mv[j] / a.bc1, vh = vv[j] / a.bc2;
+        pv[j] = pv[j] * (1.f - a.lr * a.wd) - a.lr * mh / (sqrtf(vh) + a.eps);
+      }
+      reinterpret_cast<float4*>(a.master)[i * 2] = *reinterpret_cast<float4*>(pv);
+      reinterpret_cast<float4*>(a.master)[i * 2 + 1] = *reinterpret_cast<float4*>(pv + 4);
+      reinterpret_cast<float4*>(a.m)[i * 2] = *reinterpret_cast<float4*>(mv);
+      reinterpret_cast<float4*>(a.m)[i * 2 + 1] = *reinterpret_cast<float4*>(mv + 4);
+      reinterpret_cast<float4*>(a.v)[i * 2] = *reinterpret_cast<float4*>(vv);
+      reinterpret_cast<float4*>(a.v)[i * 2 + 1] = *reinterpret_cast<float4*>(vv + 4);
+      if (a.p_lp) {
+        uint4 o;
+        o.x = pack_bf16x2(pv[0], pv[1]); o.y = pack_bf16x2(pv[2], pv[3]);
+        o.z = pack_bf16x2(pv[4], pv[5]); o.w = pack_bf16x2(pv[6], pv[7]);
+        reinterpret_cast<uint4*>(a.p_lp)[i] = o;
+      }
+    }
+  }
+  // last block to finish tells every rank that their gradient buffer has been consumed by this rank and
+  // that this rank's weight shard now holds the new version
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(a.done_counter, 1);
+    s_ok = (prev == (int)gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok && threadIdx.x < a.world) {
+    __threadfence_system();
+    st_release_sys(a.pads.p[threadIdx.x] + a.consumed_idx + a.my_rank, a.consumed_val);
+    if (a.version_idx >= 0) st_release_sys(a.pads.p[threadIdx.x] + a.version_idx + a.my_rank, a.version_val);
+    if (threadIdx.x == 0) *a.done_counter = 0;
+  }
+}
+
+// ------------------------------------------------------------------ all-gather (pull)
+struct AgArgs {
+  PeerPtrs shards;          // every rank's bf16 shard (symmetric)
+  __nv_bfloat16* full;      // local gathered buffer [world * shard_elems]
+  long long shard_elems;    // multiple of 8
+  int world, my_rank;
+  const int* local_pad;
+  int version_idx;          // wait: local_pad[version_idx + r] >= version_val before copying rank r's shard
+  int version_val;
+  int* ready_flags;         // local int[world]: set to ready_val once shard r has landed (gpu scope)
+  int ready_val;
+  int* block_counters;      // local int[world], zero before launch; reset when a shard completes
+  int blocks_per_shard;
+  uint32_t wait_limit;
+  int* status;
+};
+
+// grid = world * blocks_per_shard; block b copies a slice of shard (my_rank + 1 + b / blocks_per_shard) % world,
+// so the local shard (cheap) comes last and remote traffic starts at once, staggered across ranks.
+__global__ void __launch_bounds__(512)
+allgather_pull_kernel(const AgArgs a) {
+  __shared__ int s_ok;
+  const int order = blockIdx.x / a.blocks_per_shard;
+  const int slice = blockIdx.x % a.blocks_per_shard;
+  int src = a.my_rank + 1 + order;
+  if (src >= a.world) src -= a.world;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    if (src != a.my_rank) ok = wait_flag_ge(a.local_pad + a.version_idx + src, a.version_val, a.wait_limit);
+    s_ok = ok ? 1 : 0;
+    if (!ok && a.status) atomicCAS(a.status, 0, GF_ERR_WAIT_PEER);
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long long nvec = a.shard_elems >> 3;
+    const long long per = (nvec + a.blocks_per_shard - 1) / a.blocks_per_shard;
+    const long long lo = slice * per;
+    long long hi = lo + per;
+    if (hi > nvec) hi = nvec;
+    const uint4* s = reinterpret_cast<const uint4*>(a.shards.p[src]);
+    uint4* d = reinterpret_cast<uint4*>(a.full + (long long)src * a.shard_elems);
+    long long i = lo + threadIdx.x;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3LL * blockDim.x < hi; i += 4LL * blockDim.x) {
+      uint4 v0 = s[i], v1 = s[i + blockDim.x], v2 = s[i + 2LL * blockDim.x], v3 = s[i + 3LL * blockDim.x];
+      d[i] = v0; d[i + blockDim.x] = v1; d[i + 2LL * blockDim.x] = v2; d[i + 3LL * blockDim.x] = v3;
+    }
+    for (; i < hi; i += blockDim.x) d[i] = s[i];
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(a.block_counters + src, 1);
+    if (prev == a.blocks_per_shard - 1) {
+      a.block_counters[src] = 0;
+      __threadfence();
+      if (s_ok) st_release_gpu(a.ready_flags + src, a.ready_val);
+    }
+  }
+}
+
+__global__ void fill_int_kernel(int* p, int n, int v) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+static inline uint32_t limit_or_default(long long wait_limit) {
+  return wait_limit > 0 ? (uint32_t)wait_limit : (uint32_t)(1u << 24);  // x 100 ns sleeps: about 2 s
+}
+
+// pads: device pointers (as uint64) of every rank's signal pad, world entries.
+GF_API int gf_signal_peers(const unsigned long long* pads, int world, int my_rank, int idx_base, int value,
+                           void* stream) {
+  gf::enter();
+  if (world < 1 || world > MAX_RANKS) return GFH_BAD_ARG;
+  PeerFlagPtrs pp;
+  for (int r = 0; r < MAX_RANKS; ++r) pp.p[r] = r < world ? reinterpret_cast<int*>(pads[r]) : nullptr;
+  signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pp, idx_base, my_rank, world, value);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_wait_flags(const int* local_pad, int idx_base, int world, int value, long long wait_limit, int* status,
+                         void* stream) {
+  gf::enter();
+  if (world < 1 || world > 32) return GFH_BAD_ARG;
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_pad, idx_base, world, value,
+                                                        limit_or_default(wait_limit), status);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_fill_int(int* p, int n, int v, void* stream) {
+  gf::enter();
+  fill_int_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(p, n, v);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+// grad_ptrs / pads: world device pointers each. mc_grads: multicast pointer of the gradient buffer or 0.
+GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long long mc_grads,
+                             const unsigned long long* pads, int world, int my_rank, long long shard_lo, long long n,
+                             float* master, float* m, float* v, void* p_lp, float lr, float beta1, float beta2,
+                             float eps, float wd, int step, float grad_scale, int ready_idx, int ready_val,
+                             int consumed_idx, int consumed_val, int version_idx, int version_val, int* done_counter,
+                             int max_ctas, long long wait_limit, int* status, void* stream) {
+  gf::enter();
+  if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_lo & 7)) return GFH_BAD_ARG;
+  RsAdamArgs a;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    a.grads.p[r] = r < world ? reinterpret_cast<const void*>(grad_ptrs[r]) : nullptr;
+    a.pads.p[r] = r < world ? reinterpret_cast<int*>(pads[r]) : nullptr;
+  }
+  a.mc_grads = reinterpret_cast<const void*>(mc_grads);
+  a.shard_lo = shard_lo; a.n = n; a.master = master; a.m = m; a.v = v; a.p_lp = (__nv_bfloat16*)p_lp;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.grad_scale = grad_scale;
+  a.bc1 = 1.f - powf(beta1, (float)step);
+  a.bc2 = 1.f - powf(beta2, (float)step);
+  a.world = world; a.my_rank = my_rank;
+  a.local_pad = a.pads.p[my_rank];
+  a.ready_idx = ready_idx; a.ready_val = ready_val; a.consumed_idx = consumed_idx; a.consumed_val = consumed_val;
+  a.version_idx = version_idx; a.version_val = version_val;
+  a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
+  long long want = ((n >> 3) + 255) / 256;
+  int grid = max_ctas > 0 ? max_ctas : sm_count() * 2;
+  if (want < grid) grid = (int)(want > 0 ? want : 1);
+  if (mc_grads)
+    rs_adamw_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  else
+    rs_adamw_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+// shard_ptrs: every rank's shard (world pointers). ready_flags / block_counters: local int[world].
+GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, long long shard_elems, int world,
+                             int my_rank, const int* local_pad, int version_idx, int version_val, int* ready_flags,
+                             int ready_val, int* block_counters, int blocks_per_shard, long long wait_limit,
+                             int* status, void* stream) {
+  gf::enter();
+  if (world < 1 || world > MAX_RANKS || (shard_elems & 7) || blocks_per_shard < 1) return GFH_BAD_ARG;
+  AgArgs a;
+  for (int r = 0; r < MAX_RANKS; ++r) a.shards.p[r] = r < world ? reinterpret_cast<const void*>(shard_ptrs[r]) : nullptr;
+  a.full = (__nv_bfloat16*)full; a.shard_elems = shard_elems; a.world = world; a.my_rank = my_rank;
+  a.local_pad = local_pad; a.version_idx = version_idx; a.version_val = version_val;
+  a.ready_flags = ready_flags; a.ready_val = ready_val; a.block_counters = block_counters;
+  a.blocks_per_shard = blocks_per_shard; a.wait_limit = limit_or_default(wait_limit); a.status = status;
+  allgather_pull_kernel<<<world * blocks_per_shard, 512, 0, (cudaStream_t)stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}

@@ -42,8 +42,9 @@ class OptimConfig:
 class _Unit:
     """One flat parameter unit and this rank's shard of it."""
 
-    def __init__(self, name, specs, world, rank, device, dtype, align=8):
+    def __init__(self, name, specs, world, rank, device, dtype, align=8, index=0):
         self.name = name
+        self.index = index
         self.specs = []  # (pname, offset, shape)
         off = 0
         for pname, shape in specs:
@@ -55,7 +56,7 @@ class _Unit:
         self.padded = (off + quantum - 1) // quantum * quantum
         self.shard_numel = self.padded // world
         self.lo = rank * self.shard_numel
-        self.shard = torch.zeros(self.shard_numel, dtype=dtype, device=device)
+        self.shard = None   # allocated by the engine (from the communicator's arena when it has one)
         self.master = None
         self.m = None
         self.v = None
@@ -75,6 +76,14 @@ class Comm:
             self.backend = dist.get_backend(group)
         else:
             self.world, self.rank, self.backend = 1, 0, "none"
+
+    fused = False
+
+    def reserve(self, nbytes: int) -> None:
+        """Hook for communicators that keep weights and gradient buffers in a symmetric arena."""
+
+    def alloc(self, numel: int, dtype, device=None) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=device)
 
     def all_gather(self, shard, full):
         if self.world == 1:
@@ -130,17 +139,24 @@ class Zero3LlamaEngine:
         self.qkv_out = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * hd
         layer_specs = [("attn_norm", (d,)), ("wqkv", (self.qkv_out, d)), ("wo", (d, cfg.num_attention_heads * hd)),
                        ("ffn_norm", (d,)), ("w_gate_up", (2 * f, d)), ("w_down", (d, f))]
-        mk = lambda name, specs: _Unit(name, specs, self.world, self.rank, self.device, dtype)
-        self.embed = mk("embed", [("tok_emb", (v, d))])
-        self.layers = [mk(f"layer{i}", layer_specs) for i in range(cfg.num_hidden_layers)]
-        self.head = mk("head", [("final_norm", (d,)), ("lm_head", (v, d))])
+        mk = lambda name, specs, idx: _Unit(name, specs, self.world, self.rank, self.device, dtype, index=idx)
+        self.embed = mk("embed", [("tok_emb", (v, d))], 0)
+        self.layers = [mk(f"layer{i}", layer_specs, i + 1) for i in range(cfg.num_hidden_layers)]
+        self.head = mk("head", [("final_norm", (d,)), ("lm_head", (v, d))], cfg.num_hidden_layers + 1)
         self.units = [self.embed, *self.layers, self.head]
-        self._init_params(seed)
         max_padded = max(u.padded for u in self.units)
+        esz = torch.empty((), dtype=dtype).element_size()
+        # weights shards and the two gradient staging buffers come from the communicator (a symmetric,
+        # peer-mapped arena for the fused path; plain device memory otherwise)
+        self.comm.reserve(sum((u.shard_numel * esz + 255) // 256 * 256 for u in self.units)
+                          + 2 * ((max_padded * esz + 255) // 256 * 256) + 4096)
+        for u in self.units:
+            u.shard = self.comm.alloc(u.shard_numel, dtype, self.device)
+        self.gfull = [self.comm.alloc(max_padded, dtype, self.device) for _ in range(2)]
+        self._init_params(seed)
         if self.world > 1:
             self.full = [torch.empty(max_padded, dtype=dtype, device=self.device) for _ in range(2)]
             self.gshard = torch.empty(max(u.shard_numel for u in self.units), dtype=dtype, device=self.device)
-        self.gfull = [torch.zeros(max_padded, dtype=dtype, device=self.device) for _ in range(2)]
         self._rope = None
         self.last_stats = {}
 
@@ -195,7 +211,10 @@ class Zero3LlamaEngine:
         if st.cuda:
             st.comm.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(st.comm):
-                self.comm.all_gather(unit.shard, full)
+                if self.comm.fused:
+                    self.comm.all_gather_unit(unit, unit.index, full, self.step_count - 1)
+                else:
+                    self.comm.all_gather(unit.shard, full)
                 ev = st.event()
                 ev.record(st.comm)
             return full, ev
@@ -205,6 +224,13 @@ class Zero3LlamaEngine:
     def _wait(self, ev):
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
+
+    def _acquire_grad_slot(self, slot, local_event):
+        """Before the first write into gradient buffer ``slot``: this rank's previous reduce/update of it is
+        done (event) and, on the peer-memory path, every peer has finished reading it (flags)."""
+        self._wait(local_event)
+        if self.comm.fused:
+            self.comm.wait_grad_slot_free(slot)
 
     def _reduce_and_update(self, unit, slot):
         """Gradient reduce-scatter + AdamW on this rank's shard, off the compute stream.
@@ -216,6 +242,9 @@ class Zero3LlamaEngine:
                   step=self.step_count)
 
         def run():
+            if self.comm.fused:
+                self.comm.reduce_scatter_adamw(unit, unit.index, g_full, slot, **kw)
+                return
             if self.world == 1:
                 g = g_full
             else:
@@ -223,8 +252,10 @@ class Zero3LlamaEngine:
                 self.comm.reduce_scatter(g_full, g)
             K.adamw_flat(unit.master, unit.m, unit.v, g, unit.shard, **kw)
 
+        if self.comm.fused:
+            self.comm.grads_ready(slot)   # compute stream: my gradients for this buffer are complete
         if st.cuda:
-            side = st.opt if self.world == 1 else st.comm
+            side = st.opt if (self.world == 1 or self.comm.fused) else st.comm
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 run()
@@ -324,6 +355,7 @@ class Zero3LlamaEngine:
         # ---------------- backward
         grad_free = [None, None]   # events: gradient buffer slot may be overwritten
         gslot = 0
+        self._acquire_grad_slot(gslot, None)
         gh = self.head.views(self.gfull[gslot][:self.head.padded])
         dhF = K.gemm(logits, False, hw["lm_head"], False)
         K.gemm(logits, True, hF, False, out=gh["lm_head"])
@@ -339,13 +371,13 @@ class Zero3LlamaEngine:
             if i > 0:
                 nxt = self._gather_async(self.layers[i - 1], i % 2)
             self._wait(ev)
-            self._wait(grad_free[gslot])
+            self._acquire_grad_slot(gslot, grad_free[gslot])
             g = unit.views(self.gfull[gslot][:unit.padded])
             dx = self._layer_bwd(unit.views(w_full), g, saved.pop(), dx, B, S)
             grad_free[gslot] = self._reduce_and_update(unit, gslot)
         # embedding gradient: scatter-add of dx rows
         gslot = 1 - gslot
-        self._wait(grad_free[gslot])
+        self._acquire_grad_slot(gslot, grad_free[gslot])
         ge = self.embed.views(self.gfull[gslot][:self.embed.padded])["tok_emb"]
         ge.zero_()
         ge.index_add_(0, tok, dx)

@@ -1,0 +1,55 @@
+"""ZeRO-3 engine partitioning logic on CPU ranks (gloo): two ranks with one sequence each must follow the same
+loss curve and reach the same weights as one rank with both sequences."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import torch
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import os, sys, json, torch
+    import torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    from ghost_flow_b200.models.configs import LLaMAConfig
+    from ghost_flow_b200.parallel.zero3 import Zero3LlamaEngine, OptimConfig, Comm
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = LLaMAConfig.llama_tiny()
+    eng = Zero3LlamaEngine(cfg, "cpu", optim=OptimConfig(lr=1e-2), dtype=torch.float32, seed=7, comm=Comm())
+    g = torch.Generator().manual_seed(11)
+    tok = torch.randint(0, cfg.vocab_size, (world, 33), generator=g)
+    mine = tok[rank:rank + 1]
+    losses = [float(eng.step(mine[:, :-1], mine[:, 1:])) for _ in range(3)]
+    w = eng.gather_unit(eng.layers[1], master=True)["w_down"]
+    if rank == 0:
+        torch.save({{"losses": losses, "w": w}}, {out!r})
+    dist.barrier()
+    dist.destroy_process_group()
+""")
+
+
+def test_two_cpu_ranks_match_single_rank(tmp_path):
+    from ghost_flow_b200.models.configs import LLaMAConfig
+    from ghost_flow_b200.parallel.zero3 import OptimConfig, Zero3LlamaEngine
+
+    out = str(tmp_path / "r0.pt")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(repo=REPO, out=out))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29731", str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = torch.load(out)
+    cfg = LLaMAConfig.llama_tiny()
+    eng = Zero3LlamaEngine(cfg, "cpu", optim=OptimConfig(lr=1e-2), dtype=torch.float32, seed=7)
+    g = torch.Generator().manual_seed(11)
+    tok = torch.randint(0, cfg.vocab_size, (2, 33), generator=g)
+    ref = [float(eng.step(tok[:, :-1], tok[:, 1:])) for _ in range(3)]
+    for a, b in zip(got["losses"], ref):
+        assert abs(a - b) < 1e-4, (got["losses"], ref)
+    w = eng.gather_unit(eng.layers[1], master=True)["w_down"]
+    assert torch.allclose(got["w"], w, atol=1e-5)
