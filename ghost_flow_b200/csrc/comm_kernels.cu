@@ -237,10 +237,15 @@ allgather_pull_kernel(const AgArgs a) {
     const uint4* s = reinterpret_cast<const uint4*>(a.shards.p[src]);
     uint4* d = reinterpret_cast<uint4*>(a.full + (long long)src * a.shard_elems);
     long long i = lo + threadIdx.x;
-    // four independent 16-byte loads in flight per thread
-    for (; i + 3LL * blockDim.x < hi; i += 4LL * blockDim.x) {
-      uint4 v0 = s[i], v1 = s[i + blockDim.x], v2 = s[i + 2LL * blockDim.x], v3 = s[i + 3LL * blockDim.x];
-      d[i] = v0; d[i + blockDim.x] = v1; d[i + 2LL * blockDim.x] = v2; d[i + 3LL * blockDim.x] = v3;
+    // eight independent 16-byte loads in flight per thread (NVLink latency is a few microseconds, so the
+    // kernel needs megabytes in flight to fill the links)
+    const long long bd = blockDim.x;
+    for (; i + 7 * bd < hi; i += 8 * bd) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = s[i + k * bd];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) d[i + k * bd] = v[k];
     }
     for (; i < hi; i += blockDim.x) d[i] = s[i];
   }
@@ -265,6 +270,18 @@ __global__ void fill_int_kernel(int* p, int n, int v) {
 
 using namespace gf;
 
+static void configure_comm_kernels() {
+  static bool done = false;
+  if (done) return;
+  prefer_max_smem(signal_peers_kernel);
+  prefer_max_smem(wait_flags_kernel);
+  prefer_max_smem(rs_adamw_kernel<true>);
+  prefer_max_smem(rs_adamw_kernel<false>);
+  prefer_max_smem(allgather_pull_kernel);
+  prefer_max_smem(fill_int_kernel);
+  done = true;
+}
+
 static inline uint32_t limit_or_default(long long wait_limit) {
   return wait_limit > 0 ? (uint32_t)wait_limit : (uint32_t)(1u << 24);  // x 100 ns sleeps: about 2 s
 }
@@ -273,6 +290,7 @@ static inline uint32_t limit_or_default(long long wait_limit) {
 GF_API int gf_signal_peers(const unsigned long long* pads, int world, int my_rank, int idx_base, int value,
                            void* stream) {
   gf::enter();
+  configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS) return GFH_BAD_ARG;
   PeerFlagPtrs pp;
   for (int r = 0; r < MAX_RANKS; ++r) pp.p[r] = r < world ? reinterpret_cast<int*>(pads[r]) : nullptr;
@@ -283,6 +301,7 @@ GF_API int gf_signal_peers(const unsigned long long* pads, int world, int my_ran
 GF_API int gf_wait_flags(const int* local_pad, int idx_base, int world, int value, long long wait_limit, int* status,
                          void* stream) {
   gf::enter();
+  configure_comm_kernels();
   if (world < 1 || world > 32) return GFH_BAD_ARG;
   wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_pad, idx_base, world, value,
                                                         limit_or_default(wait_limit), status);
@@ -291,6 +310,7 @@ GF_API int gf_wait_flags(const int* local_pad, int idx_base, int world, int valu
 
 GF_API int gf_fill_int(int* p, int n, int v, void* stream) {
   gf::enter();
+  configure_comm_kernels();
   fill_int_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(p, n, v);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
@@ -303,6 +323,7 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
                              int consumed_idx, int consumed_val, int version_idx, int version_val, int* done_counter,
                              int max_ctas, long long wait_limit, int* status, void* stream) {
   gf::enter();
+  configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_lo & 7)) return GFH_BAD_ARG;
   RsAdamArgs a;
   for (int r = 0; r < MAX_RANKS; ++r) {
@@ -335,6 +356,7 @@ GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, l
                              int ready_val, int* block_counters, int blocks_per_shard, long long wait_limit,
                              int* status, void* stream) {
   gf::enter();
+  configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS || (shard_elems & 7) || blocks_per_shard < 1) return GFH_BAD_ARG;
   AgArgs a;
   for (int r = 0; r < MAX_RANKS; ++r) a.shards.p[r] = r < world ? reinterpret_cast<const void*>(shard_ptrs[r]) : nullptr;

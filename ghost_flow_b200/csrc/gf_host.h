@@ -46,4 +46,13 @@ void note_extra_launches(int n);
 // Device index selected with gf_set_device, or -1 when none was selected.
 int process_device();
 
+// Asks for the largest shared-memory carve-out for a kernel that itself needs little shared memory. An SM
+// cannot change its L1/shared split while CTAs are resident, so a side-stream kernel running with the
+// default split keeps the big-shared-memory GEMM / attention CTAs of the compute stream off every SM it
+// occupies until it drains; with the same split they share the SM.
+template <typename K>
+inline void prefer_max_smem(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 }  // namespace gf

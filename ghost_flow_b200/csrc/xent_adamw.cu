@@ -209,7 +209,9 @@ __global__ void sumsq_kernel(const G* __restrict__ g, long long n, float* __rest
 
 static inline int flat_grid(long long n) {
   long long g = (n + 1023) / 1024;
-  const long long cap = (long long)sm_count() * 8;
+  // four CTAs (1024 threads) per SM at most: these kernels are HBM-bound and usually run beside compute kernels of another
+  // stream, which must still find free thread slots and registers on every SM
+  const long long cap = (long long)sm_count() * 4;
   return (int)(g < cap ? (g > 0 ? g : 1) : cap);
 }
 
@@ -243,6 +245,12 @@ GF_API int gf_adam_flat(float* p, float* m, float* v, const void* g, void* p_lp,
                         const int* skip, void* stream) {
   gf::enter();
   if (n <= 0) return GFH_OK;
+  static bool configured = false;
+  if (!configured) {
+    prefer_max_smem(adam_flat_kernel<__nv_bfloat16>);
+    prefer_max_smem(adam_flat_kernel<float>);
+    configured = true;
+  }
   AdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.grad_scale = grad_scale;
   a.bc1 = 1.f - powf(beta1, (float)step);
