@@ -97,8 +97,11 @@ struct RsAdamArgs {
   int* status;
 };
 
+// Register budget: at most 64 per thread (4 CTAs of 256 threads per SM) and one CTA per SM in the launch, so
+// that the persistent GEMM / all-gather CTAs of the other streams always find room beside it. With a larger
+// footprint those kernels cannot start until this one has drained, and the "overlapped" update serialises.
 template <bool USE_MC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 rs_adamw_kernel(const RsAdamArgs a) {
   __shared__ int s_ok;
   if (threadIdx.x < 32) {
@@ -128,24 +131,30 @@ rs_adamw_kernel(const RsAdamArgs a) {
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) g[j] = 0.f;
-        uint4 u[MAX_RANKS];
+        // two batches of four peers: four 16-byte loads in flight, then accumulate
 #pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r) {
-          if (r < a.world) {
-            // start with the next rank after mine so the eight ranks do not all hit the same peer at once
-            int src_rank = a.my_rank + 1 + r;
-            if (src_rank >= a.world) src_rank -= a.world;
-            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.grads.p[src_rank]) + a.shard_lo + i * 8;
-            u[r] = *reinterpret_cast<const uint4*>(src);
+        for (int half = 0; half < 2; ++half) {
+          uint4 u[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int r = half * 4 + q;
+            if (r < a.world) {
+              // start with the next rank after mine so the ranks do not all hit the same peer at once
+              int src_rank = a.my_rank + 1 + r;
+              if (src_rank >= a.world) src_rank -= a.world;
+              const __nv_bfloat16* src =
+                  reinterpret_cast<const __nv_bfloat16*>(a.grads.p[src_rank]) + a.shard_lo + i * 8;
+              u[q] = *reinterpret_cast<const uint4*>(src);
+            }
           }
-        }
 #pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r) {
-          if (r < a.world) {
-            float2 f0 = unpack_bf16x2(u[r].x), f1 = unpack_bf16x2(u[r].y), f2 = unpack_bf16x2(u[r].z),
-                   f3 = unpack_bf16x2(u[r].w);
-            g[0] += f0.x; g[1] += f0.y; g[2] += f1.x; g[3] += f1.y;
-            g[4] += f2.x; g[5] += f2.y; g[6] += f3.x; g[7] += f3.y;
+          for (int q = 0; q < 4; ++q) {
+            if (half * 4 + q < a.world) {
+              float2 f0 = unpack_bf16x2(u[q].x), f1 = unpack_bf16x2(u[q].y), f2 = unpack_bf16x2(u[q].z),
+                     f3 = unpack_bf16x2(u[q].w);
+              g[0] += f0.x; g[1] += f0.y; g[2] += f1.x; g[3] += f1.y;
+              g[4] += f2.x; g[5] += f2.y; g[6] += f3.x; g[7] += f3.y;
+            }
           }
         }
       }
@@ -214,7 +223,7 @@ struct AgArgs {
 
 // grid = world * blocks_per_shard; block b copies a slice of shard (my_rank + 1 + b / blocks_per_shard) % world,
 // so the local shard (cheap) comes last and remote traffic starts at once, staggered across ranks.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256, 4)
 allgather_pull_kernel(const AgArgs a) {
   __shared__ int s_ok;
   const int order = blockIdx.x / a.blocks_per_shard;
@@ -341,7 +350,7 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
   a.version_idx = version_idx; a.version_val = version_val;
   a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
   long long want = ((n >> 3) + 255) / 256;
-  int grid = max_ctas > 0 ? max_ctas : sm_count() * 2;
+  int grid = max_ctas > 0 ? max_ctas : sm_count();
   if (want < grid) grid = (int)(want > 0 ? want : 1);
   if (mc_grads)
     rs_adamw_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
@@ -364,6 +373,6 @@ GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, l
   a.local_pad = local_pad; a.version_idx = version_idx; a.version_val = version_val;
   a.ready_flags = ready_flags; a.ready_val = ready_val; a.block_counters = block_counters;
   a.blocks_per_shard = blocks_per_shard; a.wait_limit = limit_or_default(wait_limit); a.status = status;
-  allgather_pull_kernel<<<world * blocks_per_shard, 512, 0, (cudaStream_t)stream>>>(a);
+  allgather_pull_kernel<<<world * blocks_per_shard, 256, 0, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }

@@ -125,7 +125,7 @@ class FusedComm(Comm):
         rc = self.lib.gf_allgather_pull(
             self.peer_ptrs(unit.shard), full.data_ptr(), unit.shard_numel, self.world, self.rank,
             self.pad.data_ptr(), PAD_VERSION + unit_index * 8, need_version, self.ag_ready.data_ptr(),
-            self.ag_epoch, self.ag_counters.data_ptr(), max(8, 128 // self.world), 0, _lib.status_word(self.device).data_ptr(),
+            self.ag_epoch, self.ag_counters.data_ptr(), max(8, 256 // self.world), 0, _lib.status_word(self.device).data_ptr(),
             _lib.stream_ptr())
         _lib.check_rc(rc, "gf_allgather_pull")
 
