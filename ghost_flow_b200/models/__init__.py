@@ -2,3 +2,17 @@
 from .configs import BertConfig, GPTConfig, LLaMAConfig, MixtralConfig, T5Config, ViTConfig  # noqa: F401
 from .gpt import GPTForCausalLM, GPTForSequenceClassification, GPTModel  # noqa: F401
 from .llama import LLaMAForCausalLM, LLaMAModel  # noqa: F401
+from .encoders import (  # noqa: F401
+    BertForMaskedLM, BertForSequenceClassification, BertForTokenClassification, BertModel, BertOutput,
+    MixtralForCausalLM, PatchEmbedding, T5ForConditionalGeneration, T5ForSequenceClassification, T5Model,
+    VisionTransformer,
+)
+from .multimodal import (  # noqa: F401
+    CLIP, CLIPConfig, DDPM, BetaSchedule, DiffusionConfig, NeRF, NeRFConfig, NeRFMLP, NoiseScheduler,
+    PositionalEncoder, RaySampler, ResidualBlock, UNet, VolumeRenderer,
+)
+from .geometry import (  # noqa: F401
+    ActorCriticAgent, DQNAgent, FarthestPointSampler, GATLayer, GCNLayer, Graph, GraphSAGELayer, KNNGrouper, Mesh,
+    MeshConv, MeshEncoder, MeshPool, MeshUtils, MPNNLayer, PointNet, PointNetBackbone, PointNetConfig, PolicyNetwork,
+    PPOAgent, QNetwork, REINFORCEAgent, ReplayBuffer, SAGEAggregator, STN3d, ValueNetwork,
+)

@@ -23,3 +23,26 @@ from .transformer import (  # noqa: F401
     TransformerEncoder, TransformerEncoderLayer,
 )
 from .rnn import GRU, GRUCell, LSTM, LSTMCell  # noqa: F401
+from .mixed_precision import (  # noqa: F401
+    AutocastContext, GradScaler, MixedPrecisionConfig, PrecisionMode, autocast, dequantize_fp8_blockwise,
+    quantize_fp8_blockwise, to_full_precision, to_half_precision,
+)
+from .techniques import (  # noqa: F401
+    CheckpointConfig, CheckpointedLayer, CheckpointedSequential, CheckpointManager, CheckpointStats,
+    CheckpointStrategy, CurriculumConfig, CurriculumLearning, CurriculumStats, CurriculumStrategy,
+    DifficultyScorer, DistillationConfig, DistillationMethod, DistillationStats, DynamicQuantization,
+    KnowledgeDistillation, LoRAConfig, LoRALinear, PacingFunction, PrefixTuning, PrefixTuningConfig, PromptInit,
+    PromptTuning, PromptTuningConfig, PTuningV2, QLoRAConfig, QLoRALinear, QuantizationAwareTraining,
+    QuantizationConfig, QuantizationScheme, QuantizedTensor, estimate_memory_savings,
+)
+from .moe import Expert, MixtureOfExperts, MoEConfig, MoEStats, Router, RoutingStrategy  # noqa: F401
+from .ring_attention import RingAttention, RingAttentionConfig, StripedRingAttention  # noqa: F401
+from .privacy import (  # noqa: F401
+    AdversarialAttack, AdversarialTrainer, AdversarialTrainingConfig, AggregationStrategy, AttackConfig, AttackType,
+    DPConfig, DPSGDOptimizer, FederatedClient, FederatedServer, LocalDP, PATEEnsemble, PrivacyAccountant,
+    RandomizedSmoothing, SecureAggregation,
+)
+from .inference import (  # noqa: F401
+    BatchInference, InferenceConfig, InferenceOptimizer, InferenceSession, ONNXAttribute, ONNXGraph, ONNXModel,
+    ONNXNode, ONNXTensor, onnx_to_tensor, tensor_to_onnx, warmup_model,
+)

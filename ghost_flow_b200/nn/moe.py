@@ -183,5 +183,5 @@ class MixtureOfExperts(Module):
         return float(u.min() / u.max().clamp(min=1.0)) if u.numel() else 1.0
 
     def get_stats(self) -> MoEStats:
-        return MoEStats(self.get_expert_usage(), self.load_balance_factor(), float(self.get_aux_loss()),
+        return MoEStats(self.get_expert_usage(), self.load_balance_factor(), float(self.get_aux_loss().detach()),
                         float(self._cv) if self._cv is not None else 0.0, self._dropped)

@@ -70,8 +70,12 @@ class CheckpointManager:
             self.stats.memory_saved_bytes += sum(a.numel() * a.element_size() for a in args
                                                  if isinstance(a, torch.Tensor))
 
+            calls = [0]
+
             def counted(*a):
-                self.stats.num_recomputations += 1
+                calls[0] += 1
+                if calls[0] > 1:   # the first call is the forward pass, later ones are recomputations
+                    self.stats.num_recomputations += 1
                 return fn(*a)
 
             return _torch_checkpoint(counted, *args, use_reentrant=False)

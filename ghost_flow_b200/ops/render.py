@@ -1,0 +1,253 @@
+"""NeRF rendering arithmetic, point-cloud sampling, mesh normals, INT8 quantisation and the fused inference
+Conv+BN+ReLU: CUDA kernels (``csrc/misc_kernels.cu``) for fp32 GPU tensors outside autograd, PyTorch formulas
+otherwise (those formulas are also the test oracles, restating the reference's CPU loops:
+ghostflow-nn/src/nerf.rs:111-147,353-408; point_cloud.rs:326-470; mesh.rs:55-113; quantization.rs:77-240;
+ops/conv.rs + norm.rs)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_BOUND = False
+
+
+def _lib_misc():
+    global _BOUND
+    lib = _lib.cuda_lib()
+    if not _BOUND:
+        P, I, L, Fl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.gf_posenc.argtypes = [P, P, L, I, I, I, P]
+        lib.gf_volume_render.argtypes = [P, P, P, P, P, P, P, P, I, I, I, P]
+        lib.gf_fps.argtypes = [P, P, P, I, I, I, I, P]
+        lib.gf_knn.argtypes = [P, P, P, I, I, I, I, P]
+        lib.gf_face_normals.argtypes = [P, P, P, P, I, P]
+        lib.gf_quantize_i8.argtypes = [P, P, P, P, L, L, I, I, I, P]
+        lib.gf_dequantize_i8.argtypes = [P, P, P, P, L, L, I, P]
+        lib.gf_fake_quant.argtypes = [P, P, P, P, L, L, I, I, I, P]
+        lib.gf_conv_bn_relu.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, Fl, I, P]
+        lib.gf_batchnorm_train.argtypes = [P, P, P, P, P, P, P, P, I, I, I, Fl, Fl, P]
+        _BOUND = True
+    return lib
+
+
+def _gpu_plain(*ts) -> bool:
+    """fp32 CUDA tensors with no autograd graph to maintain."""
+    for t in ts:
+        if t is None:
+            continue
+        if not (t.is_cuda and t.dtype == torch.float32) or (torch.is_grad_enabled() and t.requires_grad):
+            return False
+    return True
+
+
+def _p(t):
+    return t.data_ptr() if t is not None else None
+
+
+# ------------------------------------------------------------------ NeRF
+def positional_encoding_ref(x, num_freqs: int, include_input: bool = True):
+    outs = [x] if include_input else []
+    for k in range(num_freqs):
+        outs += [torch.sin(x * 2.0 ** k), torch.cos(x * 2.0 ** k)]
+    # per input dimension: [x, sin(2^0 x), cos(2^0 x), sin(2^1 x), ...]
+    return torch.stack(outs, dim=-1).flatten(-2)
+
+
+def positional_encoding(x, num_freqs: int, include_input: bool = True):
+    if _gpu_plain(x):
+        xc = x.contiguous()
+        d = xc.shape[-1]
+        per = 2 * num_freqs + (1 if include_input else 0)
+        out = torch.empty(*xc.shape[:-1], d * per, device=x.device, dtype=torch.float32)
+        _lib.check_rc(_lib_misc().gf_posenc(xc.data_ptr(), out.data_ptr(), xc.numel() // d, d, num_freqs,
+                                            1 if include_input else 0, _lib.stream_ptr()), "gf_posenc")
+        return out
+    return positional_encoding_ref(x, num_freqs, include_input)
+
+
+def volume_render_ref(rgb, sigma, z, ray_norm=None, white_background=False):
+    delta = torch.cat((z[:, 1:] - z[:, :-1], torch.full_like(z[:, :1], 1e10)), -1)
+    if ray_norm is not None:
+        delta = delta * ray_norm[:, None]
+    alpha = 1.0 - torch.exp(-sigma * delta)
+    T = torch.cumprod(torch.cat((torch.ones_like(alpha[:, :1]), 1.0 - alpha + 1e-10), -1), -1)[:, :-1]
+    w = T * alpha
+    color = (w[..., None] * rgb).sum(1)
+    acc = w.sum(1)
+    if white_background:
+        color = color + (1.0 - acc)[:, None]
+    return color, (w * z).sum(1), acc, w
+
+
+def volume_render(rgb, sigma, z, ray_norm=None, white_background=False):
+    """(color [R,3], depth [R], acc [R], weights [R,S])."""
+    if _gpu_plain(rgb, sigma, z, ray_norm):
+        R, S = sigma.shape
+        rgb, sigma, z = rgb.contiguous(), sigma.contiguous(), z.contiguous()
+        color = torch.empty(R, 3, device=rgb.device)
+        depth = torch.empty(R, device=rgb.device)
+        acc = torch.empty(R, device=rgb.device)
+        w = torch.empty(R, S, device=rgb.device)
+        rn = ray_norm.contiguous() if ray_norm is not None else None
+        _lib.check_rc(_lib_misc().gf_volume_render(rgb.data_ptr(), sigma.data_ptr(), z.data_ptr(), _p(rn),
+                                                   color.data_ptr(), depth.data_ptr(), acc.data_ptr(), w.data_ptr(),
+                                                   R, S, 1 if white_background else 0, _lib.stream_ptr()),
+                      "gf_volume_render")
+        return color, depth, acc, w
+    return volume_render_ref(rgb, sigma, z, ray_norm, white_background)
+
+
+# ------------------------------------------------------------------ point clouds / meshes
+def farthest_point_sample_ref(pts, m: int, start: int = 0):
+    B, N, _ = pts.shape
+    idx = torch.zeros(B, m, dtype=torch.long, device=pts.device)
+    dist = torch.full((B, N), 1e30, device=pts.device)
+    cur = torch.full((B,), start % N, dtype=torch.long, device=pts.device)
+    ar = torch.arange(B, device=pts.device)
+    for i in range(m):
+        idx[:, i] = cur
+        d = (pts - pts[ar, cur][:, None, :]).pow(2).sum(-1)
+        dist = torch.minimum(dist, d)
+        cur = dist.argmax(-1)
+    return idx
+
+
+def farthest_point_sample(pts, m: int, start: int = 0):
+    """Indices ``[B, m]`` of an iterative farthest-point subset of ``pts [B, N, 3]``."""
+    if _gpu_plain(pts):
+        B, N, _ = pts.shape
+        p = pts.contiguous()
+        idx = torch.empty(B, m, dtype=torch.int32, device=pts.device)
+        scratch = torch.empty(B, N, device=pts.device)
+        _lib.check_rc(_lib_misc().gf_fps(p.data_ptr(), idx.data_ptr(), scratch.data_ptr(), B, N, m, start,
+                                         _lib.stream_ptr()), "gf_fps")
+        return idx.long()
+    return farthest_point_sample_ref(pts, m, start)
+
+
+def knn_ref(pts, queries, k: int):
+    d = torch.cdist(queries, pts)
+    return d.topk(k, dim=-1, largest=False).indices
+
+
+def knn(pts, queries, k: int):
+    """Indices ``[B, Q, k]`` of the k nearest ``pts [B, N, 3]`` of every query ``[B, Q, 3]`` (nearest first)."""
+    if _gpu_plain(pts, queries) and k <= 64:
+        B, N, _ = pts.shape
+        Q = queries.shape[1]
+        out = torch.empty(B, Q, k, dtype=torch.int32, device=pts.device)
+        _lib.check_rc(_lib_misc().gf_knn(pts.contiguous().data_ptr(), queries.contiguous().data_ptr(), out.data_ptr(),
+                                         B, N, Q, k, _lib.stream_ptr()), "gf_knn")
+        return out.long()
+    return knn_ref(pts, queries, k)
+
+
+def face_normals(verts, faces):
+    """(unit normals ``[F,3]``, areas ``[F]``) of triangles ``faces [F,3]`` over ``verts [V,3]``."""
+    if _gpu_plain(verts) and faces.is_cuda:
+        Fn = faces.shape[0]
+        n = torch.empty(Fn, 3, device=verts.device)
+        a = torch.empty(Fn, device=verts.device)
+        _lib.check_rc(_lib_misc().gf_face_normals(verts.contiguous().data_ptr(), faces.int().contiguous().data_ptr(),
+                                                  n.data_ptr(), a.data_ptr(), Fn, _lib.stream_ptr()),
+                      "gf_face_normals")
+        return n, a
+    v0, v1, v2 = verts[faces[:, 0]], verts[faces[:, 1]], verts[faces[:, 2]]
+    c = torch.cross(v1 - v0, v2 - v0, dim=-1)
+    ln = c.norm(dim=-1)
+    return c / ln.clamp(min=1e-20)[:, None], 0.5 * ln
+
+
+# ------------------------------------------------------------------ INT8
+def _chan_layout(x, channel_dim, channels):
+    if channels == 1:
+        return 1
+    inner = 1
+    for d in x.shape[channel_dim + 1:]:
+        inner *= d
+    return inner
+
+
+def quantize_int8(x, scale, zero_point, channel_dim: int = 0, qmin: int = -128, qmax: int = 127):
+    channels = scale.numel()
+    if _gpu_plain(x):
+        xc = x.contiguous()
+        q = torch.empty(xc.shape, dtype=torch.int8, device=x.device)
+        _lib.check_rc(_lib_misc().gf_quantize_i8(xc.data_ptr(), q.data_ptr(), scale.float().contiguous().data_ptr(),
+                                                 zero_point.float().contiguous().data_ptr(), xc.numel(),
+                                                 _chan_layout(xc, channel_dim, channels), channels, qmin, qmax,
+                                                 _lib.stream_ptr()), "gf_quantize_i8")
+        return q
+    shape = [1] * x.dim()
+    if channels > 1:
+        shape[channel_dim] = channels
+    return (torch.round(x / scale.view(shape)) + zero_point.view(shape)).clamp(qmin, qmax).to(torch.int8)
+
+
+def dequantize_int8(q, scale, zero_point, channel_dim: int = 0):
+    channels = scale.numel()
+    if q.is_cuda:
+        qc = q.contiguous()
+        x = torch.empty(qc.shape, dtype=torch.float32, device=q.device)
+        _lib.check_rc(_lib_misc().gf_dequantize_i8(qc.data_ptr(), x.data_ptr(), scale.float().contiguous().data_ptr(),
+                                                   zero_point.float().contiguous().data_ptr(), qc.numel(),
+                                                   _chan_layout(qc, channel_dim, channels), channels,
+                                                   _lib.stream_ptr()), "gf_dequantize_i8")
+        return x
+    shape = [1] * q.dim()
+    if channels > 1:
+        shape[channel_dim] = channels
+    return (q.float() - zero_point.view(shape)) * scale.view(shape)
+
+
+def fake_quantize(x, scale, zero_point, channel_dim: int = 0, qmin: int = -128, qmax: int = 127):
+    if _gpu_plain(x):
+        channels = scale.numel()
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _lib.check_rc(_lib_misc().gf_fake_quant(xc.data_ptr(), y.data_ptr(), scale.float().contiguous().data_ptr(),
+                                                zero_point.float().contiguous().data_ptr(), xc.numel(),
+                                                _chan_layout(xc, channel_dim, channels), channels, qmin, qmax,
+                                                _lib.stream_ptr()), "gf_fake_quant")
+        return y
+    return dequantize_int8(quantize_int8(x, scale, zero_point, channel_dim, qmin, qmax), scale, zero_point, channel_dim)
+
+
+# ------------------------------------------------------------------ conv + BN + ReLU (inference)
+def conv_bn_relu(x, weight, bias, bn_weight, bn_bias, running_mean, running_var, stride: int = 1, padding: int = 0,
+                 eps: float = 1e-5, relu: bool = True):
+    """Inference-time ``relu(batchnorm(conv2d(x)))`` in one pass over the output."""
+    if _gpu_plain(x, weight) and x.dim() == 4:
+        N, Cin, H, W = x.shape
+        Cout, _, KH, KW = weight.shape
+        OH, OW = (H + 2 * padding - KH) // stride + 1, (W + 2 * padding - KW) // stride + 1
+        y = torch.empty(N, Cout, OH, OW, device=x.device)
+        rc = _lib_misc().gf_conv_bn_relu(x.contiguous().data_ptr(), weight.contiguous().data_ptr(), _p(bias),
+                                         _p(bn_weight), _p(bn_bias), _p(running_mean), _p(running_var), y.data_ptr(),
+                                         N, Cin, H, W, Cout, KH, KW, stride, padding, float(eps), 1 if relu else 0,
+                                         _lib.stream_ptr())
+        _lib.check_rc(rc, "gf_conv_bn_relu")
+        return y
+    y = F.conv2d(x, weight, bias, stride, padding)
+    if bn_weight is not None:
+        y = F.batch_norm(y, running_mean, running_var, bn_weight, bn_bias, False, 0.0, eps)
+    return torch.relu(y) if relu else y
+
+
+def batch_norm_train(x, weight, bias, running_mean, running_var, momentum: float = 0.1, eps: float = 1e-5):
+    """Training-mode batch norm over ``[N, C, *]`` that also updates the running statistics."""
+    if _gpu_plain(x, weight, bias):
+        xc = x.contiguous()
+        N, C = xc.shape[0], xc.shape[1]
+        HW = xc.numel() // (N * C)
+        y = torch.empty_like(xc)
+        _lib.check_rc(_lib_misc().gf_batchnorm_train(xc.data_ptr(), y.data_ptr(), _p(weight), _p(bias),
+                                                     _p(running_mean), _p(running_var), None, None, N, C, HW,
+                                                     float(eps), float(momentum), _lib.stream_ptr()),
+                      "gf_batchnorm_train")
+        return y
+    return F.batch_norm(x, running_mean, running_var, weight, bias, True, momentum, eps)
