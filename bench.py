@@ -205,10 +205,25 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     _lib.check_status(device)
 
-    t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+    # ---- exposed communication: the same K steps with every kernel kept except the traffic between ranks
+    # (weights and gradients stay local, so the numbers computed are meaningless; this runs last on purpose).
+    ms_dry = ms
+    if world > 1 and getattr(eng.comm, "fused", False):
+        eng.comm.dry_run = True
+        run_steps(1, 0, False)
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        run_steps(args.steps, args.warmup, False)
+        g1.record()
+        sync_all()
+        ms_dry = g0.elapsed_time(g1) / args.steps
+        eng.comm.dry_run = False
+
+    t = torch.tensor([ms, ms_e2e, ms_dry], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
+    ms, ms_e2e, ms_dry = float(t[0]), float(t[1]), float(t[2])
     tokens_per_step = B * S * world
     value = tokens_per_step / (ms / 1e3)
     e2e_value = tokens_per_step / (ms_e2e / 1e3)
@@ -234,6 +249,8 @@ def main():
                     "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4,
                     "loss": loss_e2e},
             "gpu_launches": int(launches),
+            "exposed_comm_ms": max(0.0, ms - ms_dry) if world > 1 else 0.0,
+            "compute_only_ms_per_step": ms_dry,
         }
         print(json.dumps(out))
     if world > 1:

@@ -72,6 +72,10 @@ class FusedComm(Comm):
         self.rs_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.slot_use = [0, 0]
         self.ag_epoch = 0
+        # dry_run = True keeps every kernel of the step except the traffic between ranks (local shard copy, local
+        # AdamW on the unreduced gradient slice). The numbers it produces are wrong on purpose: it exists only to
+        # time the compute-only step, so that exposed communication = full step - dry step can be reported.
+        self.dry_run = False
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
@@ -121,6 +125,9 @@ class FusedComm(Comm):
     # ------------------------------------------------------------------ collectives
     def all_gather_unit(self, unit, unit_index: int, full: torch.Tensor, need_version: int) -> None:
         """Pulls every rank's shard of ``unit`` into ``full`` on the current stream."""
+        if self.dry_run:
+            full[self.rank * unit.shard_numel:(self.rank + 1) * unit.shard_numel].copy_(unit.shard)
+            return
         self.ag_epoch += 1
         rc = self.lib.gf_allgather_pull(
             self.peer_ptrs(unit.shard), full.data_ptr(), unit.shard_numel, self.world, self.rank,
@@ -131,6 +138,8 @@ class FusedComm(Comm):
 
     def grads_ready(self, slot: int) -> None:
         """Called on the compute stream after the last gradient write into buffer ``slot``."""
+        if self.dry_run:
+            return
         self.slot_use[slot] += 1
         rc = self.lib.gf_signal_peers(self.pad_ptrs, self.world, self.rank, PAD_READY + slot * 8,
                                       self.slot_use[slot], _lib.stream_ptr())
@@ -139,7 +148,7 @@ class FusedComm(Comm):
     def wait_grad_slot_free(self, slot: int) -> None:
         """Called on the compute stream before the first gradient write of a new use of buffer ``slot``:
         every peer must have finished reading the previous contents."""
-        if self.slot_use[slot] == 0:
+        if self.slot_use[slot] == 0 or self.dry_run:
             return
         rc = self.lib.gf_wait_flags(self.pad.data_ptr(), PAD_CONSUMED + slot * 8, self.world, self.slot_use[slot],
                                     0, _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
@@ -148,6 +157,13 @@ class FusedComm(Comm):
     def reduce_scatter_adamw(self, unit, unit_index: int, g_full: torch.Tensor, slot: int, *, lr, beta1, beta2, eps,
                              weight_decay, step, grad_scale=1.0) -> None:
         """Fused reduce-scatter + AdamW for this rank's shard of ``unit`` on the current stream."""
+        if self.dry_run:
+            from ..ops import raw as K
+
+            K.adamw_flat(unit.master, unit.m, unit.v, g_full[unit.lo:unit.lo + unit.shard_numel], unit.shard, lr=lr,
+                         beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, step=step,
+                         grad_scale=grad_scale)
+            return
         use = self.slot_use[slot]
         rc = self.lib.gf_rs_adamw_fused(
             self.peer_ptrs(g_full), self.mc_ptr(g_full), self.pad_ptrs, self.world, self.rank, unit.lo,

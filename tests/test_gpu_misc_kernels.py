@@ -1,0 +1,75 @@
+"""CUDA kernels off the transformer path against their PyTorch fp32 formulas."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_posenc_and_volume_render(kernel_status):
+    from ghost_flow_b200.ops import render
+
+    x = torch.randn(1000, 3, device=DEV)
+    assert torch.allclose(render.positional_encoding(x, 6), render.positional_encoding_ref(x, 6), atol=1e-4)
+    R, S = 513, 96
+    rgb, sigma = torch.rand(R, S, 3, device=DEV), torch.rand(R, S, device=DEV) * 3
+    z = torch.sort(torch.rand(R, S, device=DEV) * 4 + 2, -1).values
+    nrm = torch.rand(R, device=DEV) + 0.5
+    for wb in (False, True):
+        got = render.volume_render(rgb, sigma, z, nrm, wb)
+        ref = render.volume_render_ref(rgb, sigma, z, nrm, wb)
+        for a, b in zip(got, ref):
+            assert torch.allclose(a, b, atol=2e-4, rtol=1e-3)
+
+
+def test_fps_knn_normals(kernel_status):
+    from ghost_flow_b200.ops import render
+
+    pts = torch.randn(3, 500, 3, device=DEV)
+    idx = render.farthest_point_sample(pts, 32, start=7)
+    assert torch.equal(idx.cpu(), render.farthest_point_sample_ref(pts.cpu(), 32, 7))
+    q = torch.randn(3, 40, 3, device=DEV)
+    got = render.knn(pts, q, 8)
+    ref = render.knn_ref(pts, q, 8)
+    d = torch.cdist(q, pts)
+    assert torch.allclose(d.gather(-1, got), d.gather(-1, ref), atol=1e-5)
+    verts = torch.randn(100, 3, device=DEV)
+    faces = torch.randint(0, 100, (200, 3), device=DEV)
+    n, a = render.face_normals(verts, faces)
+    nr, ar = render.face_normals(verts.cpu(), faces.cpu())
+    assert torch.allclose(a.cpu(), ar, atol=1e-5) and torch.allclose(n.cpu(), nr, atol=1e-4)
+
+
+def test_int8_quant_kernels(kernel_status):
+    from ghost_flow_b200.ops import render
+
+    x = torch.randn(16, 8, 5, device=DEV)
+    scale = (x.abs().amax((0, 2)) / 127).clamp(min=1e-8)
+    zp = torch.zeros(8, device=DEV)
+    q = render.quantize_int8(x, scale, zp, channel_dim=1, qmin=-127)
+    qr = render.quantize_int8(x.cpu(), scale.cpu(), zp.cpu(), channel_dim=1, qmin=-127)
+    assert (q.cpu().int() - qr.int()).abs().max() <= 1
+    assert (render.dequantize_int8(q, scale, zp, 1) - x).abs().max() < scale.max() * 0.51
+    s1, z1 = torch.tensor([0.05], device=DEV), torch.tensor([3.0], device=DEV)
+    fq = render.fake_quantize(x, s1, z1)
+    assert torch.allclose(fq.cpu(), render.fake_quantize(x.cpu(), s1.cpu(), z1.cpu()), atol=0.051)
+
+
+def test_conv_bn_relu_and_batchnorm(kernel_status):
+    from ghost_flow_b200.ops import render
+
+    x = torch.randn(2, 5, 37, 41, device=DEV)          # output wider than 32 columns
+    w, b = torch.randn(7, 5, 3, 3, device=DEV) * 0.2, torch.randn(7, device=DEV)
+    g, be = torch.rand(7, device=DEV) + 0.5, torch.randn(7, device=DEV)
+    mu, var = torch.randn(7, device=DEV), torch.rand(7, device=DEV) + 0.5
+    for stride, pad in ((1, 1), (2, 0)):
+        got = render.conv_bn_relu(x, w, b, g, be, mu, var, stride, pad)
+        ref = torch.relu(F.batch_norm(F.conv2d(x, w, b, stride, pad), mu, var, g, be, False, 0.0, 1e-5))
+        assert torch.allclose(got, ref, atol=2e-3, rtol=1e-3)
+    rm, rv = torch.zeros(5, device=DEV), torch.ones(5, device=DEV)
+    rm2, rv2 = rm.clone(), rv.clone()
+    wt, bs = torch.rand(5, device=DEV) + 0.5, torch.randn(5, device=DEV)
+    y = render.batch_norm_train(x, wt, bs, rm, rv, 0.1, 1e-5)
+    yr = F.batch_norm(x, rm2, rv2, wt, bs, True, 0.1, 1e-5)
+    assert torch.allclose(y, yr, atol=1e-3) and torch.allclose(rm, rm2, atol=1e-4) and torch.allclose(rv, rv2, atol=1e-3)
