@@ -28,11 +28,39 @@ struct GemmParams {
   float alpha;
   int* status;
   int tiles_m, tiles_n;
-  // Optional readiness flags for operand B (used by the fused all-gather + GEMM path):
-  // tile column block n waits until b_ready[n_to_flag(n)] >= b_epoch. Null = no waiting.
-  const int* b_ready;
-  int b_rows_per_flag;
-  int b_epoch;
+  // Fused all-gather (optional). The first g_copy_ctas CTAs pull every rank's shard of a flat bf16 buffer
+  // into this GPU's memory (own shard first, then rank+1, rank+2, ...) and raise one flag per shard; the compute
+  // CTAs walk the tiles in the same order and wait (bounded) only for the shards that hold their tile's rows
+  // of the gathered operand, so the GEMM starts on local data while remote shards are still in flight.
+  int g_operand;            // -1 none, 0 = the rows of A are gathered, 1 = the rows of B (K-major operands only)
+  int g_copy_ctas;
+  int g_world, g_rank;
+  int g_first_shard;        // copy order: g_first_shard, g_first_shard + 1, ... (mod world)
+  const void* g_src[8];     // every rank's shard (peer-mapped)
+  __nv_bfloat16* g_dst;     // local gathered buffer: shard r lands at g_dst + r * g_shard_elems
+  long long g_shard_elems;  // multiple of 8
+  long long g_operand_off;  // element offset of the operand's first row inside the gathered buffer
+  long long g_operand_ld;   // row pitch of the gathered operand, elements
+  int* g_ready;             // local int[world]: epoch value once shard r is complete
+  int* g_counters;          // local int[world], zero before launch (reset by the kernel)
+  int g_epoch;
+  const int* g_version_pad; // this rank's signal pad: wait pad[g_version_idx + r] >= g_version_val before reading rank r
+  int g_version_idx, g_version_val;
+  // Fused reduce-scatter (optional, row-parallel linear): every rank holds a partial C; rows are owned in
+  // contiguous blocks of rs_rows_per_rank. The epilogue stores each partial tile straight into the OWNER rank's
+  // staging buffer over NVLink and bumps the owner's arrival counter for that column block; after its own tiles a
+  // CTA turns to the reduce phase: it waits (bounded) until all ranks' partials of a column block have arrived
+  // and sums them into the local output shard.
+  int rs_world, rs_rank;            // rs_world = 0: off
+  __nv_bfloat16* rs_stage[8];       // every rank's staging buffer [world][rows_per_rank][N] (peer-mapped)
+  int* rs_counters[8];              // every rank's arrival counters int[tiles_n] (peer-mapped, start at zero)
+  int rs_rows_per_rank;
+  int rs_call;                      // number of earlier calls that used these counters with the same shape
+  __nv_bfloat16* rs_out;            // local output [rows_per_rank, N]
+  long long rs_ldo;
+  int order_n_fast;         // 1: consecutive tiles share the A row block (used when A is the gathered operand)
+  int rs_interleave;        // > 0: row blocks per owner; the walk then alternates between owners block by block
+  int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
 };
 
 constexpr int BM = 128;
@@ -53,6 +81,116 @@ __device__ __forceinline__ void set_status(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
+// Tile walk: by default consecutive tiles share the B column block (tm fastest); with order_n_fast they share
+// the A row block. The slow index is rotated by tile_rot.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  if (p.rs_interleave > 0) {
+    // fused reduce-scatter: consecutive row blocks go to different owners (the next rank first, this rank last),
+    // which spreads the NVLink stores of the epilogue evenly over the run of the kernel
+    tn = tile % p.tiles_n;
+    const int s = tile / p.tiles_n;
+    int owner = s % p.rs_world + p.rs_rank + 1;
+    if (owner >= p.rs_world) owner -= p.rs_world;
+    tm = owner * p.rs_interleave + s / p.rs_world;
+  } else if (p.order_n_fast) {
+    tn = tile % p.tiles_n;
+    tm = tile / p.tiles_n + p.tile_rot;
+    if (tm >= p.tiles_m) tm -= p.tiles_m;
+  } else {
+    tm = tile % p.tiles_m;
+    tn = tile / p.tiles_m + p.tile_rot;
+    if (tn >= p.tiles_n) tn -= p.tiles_n;
+  }
+}
+
+// Copy CTAs of the fused all-gather. One thread per copy CTA drives the bulk-copy engine: peer shard ->
+// shared-memory ring (cp.async.bulk, completion on an mbarrier; plain bulk loads, no multicast) -> local gathered
+// buffer (cp.async.bulk store). The ring keeps (G_CHUNKS - 2) x 16 KB in flight per CTA without using
+// registers or issue slots, so a handful of copy CTAs fills the NVLink ports. Every copy CTA takes a slice of
+// each shard, shard by shard in arrival order (own shard first), so the whole copy bandwidth goes to the shard
+// the compute CTAs need next.
+constexpr int G_CHUNK = 16384;
+constexpr int G_CHUNKS = 8;
+
+__device__ __forceinline__ void gather_role(const GemmParams& p, uint8_t* smem) {
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + G_CHUNKS * G_CHUNK);
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < G_CHUNKS; ++i) mbar_init(&bar[i], 1);
+  mbar_fence_init();
+  const long long shard_bytes = p.g_shard_elems * 2;
+  long long per = (shard_bytes + p.g_copy_ctas - 1) / p.g_copy_ctas;
+  per = (per + 255) / 256 * 256;
+  const long long lo = (long long)blockIdx.x * per;
+  long long hi = lo + per;
+  if (hi > shard_bytes) hi = shard_bytes;
+  const int nchunks = hi > lo ? (int)((hi - lo + G_CHUNK - 1) / G_CHUNK) : 0;
+  uint32_t issued = 0;  // chunks loaded so far over all shards: stage = issued % G_CHUNKS, phase = (issued / G_CHUNKS) & 1
+  for (int order = 0; order < p.g_world; ++order) {
+    int src = p.g_first_shard + order;
+    if (src >= p.g_world) src -= p.g_world;
+    bool ok = true;
+    if (src != p.g_rank && p.g_version_pad) {
+      ok = false;
+      for (uint32_t it = 0; it < GF_WAIT_LIMIT; ++it) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_version_pad + p.g_version_idx + src) : "memory");
+        if (v >= p.g_version_val) { ok = true; break; }
+        __nanosleep(100);
+      }
+      if (!ok) set_status(p.status, GF_ERR_WAIT_PEER);
+    }
+    if (ok && nchunks > 0) {
+      const char* sbase = reinterpret_cast<const char*>(p.g_src[src]) + lo;
+      char* dbase = reinterpret_cast<char*>(p.g_dst) + (long long)src * shard_bytes + lo;
+      constexpr int LAG = G_CHUNKS - 2;
+      const uint32_t first = issued;
+      for (int c = 0; c < nchunks + LAG; ++c) {
+        if (c < nchunks) {
+          // the store that last read this stage must be done with shared memory (all but the newest store group)
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          const uint32_t n = first + c;
+          const int st = n % G_CHUNKS;
+          const long long off = (long long)c * G_CHUNK;
+          const uint32_t bytes = (uint32_t)((hi - lo - off) < G_CHUNK ? (hi - lo - off) : G_CHUNK);
+          mbar_expect_tx(&bar[st], bytes);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(smem + st * G_CHUNK)), "l"(sbase + off), "r"(bytes), "r"(smem_u32(&bar[st]))
+                       : "memory");
+        }
+        const int d = c - LAG;
+        if (d >= 0) {
+          const uint32_t n = first + d;
+          const int st = n % G_CHUNKS;
+          if (!mbar_wait(&bar[st], (n / G_CHUNKS) & 1)) {
+            set_status(p.status, GF_ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          const long long off = (long long)d * G_CHUNK;
+          const uint32_t bytes = (uint32_t)((hi - lo - off) < G_CHUNK ? (hi - lo - off) : G_CHUNK);
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dbase + off), "r"(smem_u32(smem + st * G_CHUNK)), "r"(bytes)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      issued = first + nchunks;
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    __threadfence();
+    const int prev = atomicAdd(p.g_counters + src, 1);
+    if (prev == p.g_copy_ctas - 1) {
+      p.g_counters[src] = 0;
+      __threadfence();
+      if (ok) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.g_ready + src), "r"(p.g_epoch) : "memory");
+    }
+    if (!ok) {
+      error_drain_pause();
+      return;
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -70,6 +208,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
+  if ((int)blockIdx.x < n_copy) {
+    gather_role(p, smem);
+    return;
+  }
+  const int cta = (int)blockIdx.x - n_copy;
+  const int nctas = (int)gridDim.x - n_copy;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -99,23 +244,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % p.tiles_m;
-        const int tn = tile / p.tiles_m;
+      for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        if (p.b_ready) {
-          // Wait (bounded) until every row block of B that this tile reads has landed in local memory.
-          const int f0 = n0 / p.b_rows_per_flag;
-          int n_hi = n0 + BN - 1;
-          if (n_hi > p.N - 1) n_hi = p.N - 1;
-          const int f1 = n_hi / p.b_rows_per_flag;
-          for (int f = f0; f <= f1 && ok; ++f) {
-            uint32_t it = 0;
+        if (p.g_operand >= 0) {
+          // shards that hold the rows of the gathered operand read by this tile
+          const long long r0 = p.g_operand == 0 ? m0 : n0;
+          const long long rmax = p.g_operand == 0 ? p.M : p.N;
+          long long r1 = r0 + (p.g_operand == 0 ? BM : BN);
+          if (r1 > rmax) r1 = rmax;
+          const long long e0 = p.g_operand_off + r0 * p.g_operand_ld;
+          const long long e1 = p.g_operand_off + (r1 - 1) * p.g_operand_ld + p.K - 1;
+          const int s0 = (int)(e0 / p.g_shard_elems), s1 = (int)(e1 / p.g_shard_elems);
+          for (int sh = s0; sh <= s1 && ok; ++sh) {
+            uint32_t spins = 0;
             while (true) {
               int v;
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + f) : "memory");
-              if (v >= p.b_epoch) break;
-              if (++it > GF_WAIT_LIMIT) {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + sh) : "memory");
+              if (v >= p.g_epoch) break;
+              if (++spins > GF_WAIT_LIMIT) {
                 ok = false;
                 break;
               }
@@ -165,7 +313,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = cta; tile < num_tiles && ok; tile += nctas, ++it) {
         const int buf = it & 1;
         const uint32_t bphase = (it >> 1) & 1;
         if (!mbar_wait(&tempty_bar[buf], bphase ^ 1)) {
@@ -204,11 +352,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int lane_grp = warp & 3;  // TMEM lanes [32*lane_grp, +32) belong to this warp
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = cta; tile < num_tiles; tile += nctas, ++it) {
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
-      const int tm = tile % p.tiles_m;
-      const int tn = tile / p.tiles_m;
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
       const int row = tm * BM + lane_grp * 32 + lane;
       const int n0 = tn * BN;
       if (!mbar_wait_warp(&tfull_bar[buf], bphase)) {
@@ -228,12 +376,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
           const bool full = (col0 + 32 <= p.N);
-          if (p.bias) {
+          if (p.bias && p.rs_world == 0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
           }
-          if (p.residual) {
+          if (p.residual && p.rs_world == 0) {
             const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
             if (full && ((p.ldr & 7) == 0)) {
 #pragma unroll
@@ -250,7 +398,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
           }
-          if (p.out_fp32) {
+          if (p.rs_world > 0) {
+            // partial result -> owner's staging slot [my rank][local row]
+            const int owner = row / p.rs_rows_per_rank;
+            const int lrow = row - owner * p.rs_rows_per_rank;
+            __nv_bfloat16* cp = p.rs_stage[owner] + ((long long)p.rs_rank * p.rs_rows_per_rank + lrow) * p.N + col0;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(cp + q * 8) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
+            }
+          } else if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
             if (full && ((p.ldc & 3) == 0)) {
 #pragma unroll
@@ -301,6 +469,75 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (p.rs_world > 0) {
+        // all 128 epilogue threads have stored their rows: publish the tile to the owners of those rows
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int m0 = tm * BM;
+          int m1 = m0 + BM - 1;
+          if (m1 > p.M - 1) m1 = p.M - 1;
+          for (int o = m0 / p.rs_rows_per_rank; o <= m1 / p.rs_rows_per_rank; ++o)
+            asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p.rs_counters[o] + tn), "r"(1) : "memory");
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ reduce phase of the fused reduce-scatter
+  if (p.rs_world > 0) {
+    __shared__ int s_go;
+    __syncthreads();
+    const int Mr = p.rs_rows_per_rank, o = p.rs_rank;
+    const int cnt = ((o + 1) * Mr - 1) / BM - (o * Mr) / BM + 1;   // row tiles that touch my rows
+    const int target = (p.rs_call + 1) * p.rs_world * cnt;
+    const int row_chunks = (Mr + 31) / 32;
+    const __nv_bfloat16* stage = p.rs_stage[o];
+    const int* counters = p.rs_counters[o];
+    for (int item = cta; item < p.tiles_n * row_chunks; item += nctas) {
+      const int tn = item / row_chunks, rc = item % row_chunks;
+      if (threadIdx.x == 0) {
+        int ok = 0;
+        for (uint32_t it = 0; it < GF_WAIT_LIMIT; ++it) {
+          int v;
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(counters + tn) : "memory");
+          if (v >= target) { ok = 1; break; }
+          __nanosleep(100);
+        }
+        if (!ok) set_status(p.status, GF_ERR_WAIT_PEER);
+        s_go = ok;
+      }
+      __syncthreads();
+      if (s_go) {
+        const int r0 = rc * 32, r1 = min(Mr, r0 + 32);
+        const int c0 = tn * BN, c1 = min(p.N, c0 + BN);
+        const int vpr = (c1 - c0) >> 3;
+        for (int v = threadIdx.x; v < (r1 - r0) * vpr; v += blockDim.x) {
+          const int lrow = r0 + v / vpr, col = c0 + (v % vpr) * 8;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int src = 0; src < p.rs_world; ++src) {
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + ((long long)src * Mr + lrow) * p.N + col);
+            float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+            acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+            acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          }
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(p.bias[col + j]);
+          }
+          if (p.residual) {
+            const uint4 u = *reinterpret_cast<const uint4*>(p.residual + (long long)lrow * p.ldr + col);
+            float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+            acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+            acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          }
+          uint4 ov;
+          ov.x = pack_bf16x2(acc[0], acc[1]); ov.y = pack_bf16x2(acc[2], acc[3]);
+          ov.z = pack_bf16x2(acc[4], acc[5]); ov.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(p.rs_out + (long long)lrow * p.rs_ldo + col) = ov;
+        }
+      }
+      __syncthreads();
     }
   }
 
@@ -331,7 +568,27 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (tiles < grid) grid = tiles;
+  const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
+  if (tiles < grid - n_copy) grid = tiles + n_copy;
+  if (p.rs_world > 0) {
+    // walk the row blocks starting with the next rank's rows and ending with this rank's own
+    p.order_n_fast = 1;
+    const int next = (p.rs_rank + 1) % p.rs_world;
+    p.tile_rot = (int)(((long long)next * p.rs_rows_per_rank / BM) % p.tiles_m);
+    p.rs_interleave = (p.rs_rows_per_rank % BM == 0) ? p.rs_rows_per_rank / BM : 0;
+  }
+  if (p.g_operand >= 0) {
+    // start the tile walk in the tiles whose rows live in the shard that is copied first
+    const long long first = p.g_first_shard * p.g_shard_elems - p.g_operand_off;
+    long long row = first > 0 ? (first + p.g_operand_ld - 1) / p.g_operand_ld : 0;
+    if (p.g_operand == 0) {
+      p.order_n_fast = 1;
+      p.tile_rot = (int)((row / BM) % p.tiles_m);
+    } else {
+      p.order_n_fast = 0;
+      p.tile_rot = (int)((row / BN) % p.tiles_n);
+    }
+  }
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
@@ -353,18 +610,12 @@ static int pick_bn(int M, int N, int hint) {
 
 }  // namespace gf
 
-// lda/ldb: row pitch in elements of the matrix as stored.
-//   a_mn_major = 0: A stored [M, K] (K contiguous); 1: A stored [K, M] (M contiguous).
-//   b_mn_major = 0: B stored [N, K] (K contiguous); 1: B stored [K, N] (N contiguous).
-GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
-                        int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate,
-                        const void* bias, const void* residual, long long ldr, float alpha, int* status,
-                        int bn_hint, int max_ctas, const int* b_ready, int b_rows_per_flag, int b_epoch,
-                        void* stream_v) {
-  gf::enter();
+static int gemm_core(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
+                     int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate, const void* bias,
+                     const void* residual, long long ldr, float alpha, int* status, int bn_hint, int max_ctas,
+                     gf::GemmParams& p, cudaStream_t stream) {
   using namespace gf;
   if (M <= 0 || N <= 0 || K <= 0) return GFH_BAD_ARG;
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const int bn = pick_bn(M, N, bn_hint);
   CUtensorMap tmA, tmB;
   int rc;
@@ -378,13 +629,11 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   else
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb * 2, BK, 64);
   if (rc) return rc;
-  GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr; p.alpha = alpha; p.status = status;
-  p.b_ready = b_ready; p.b_rows_per_flag = b_rows_per_flag > 0 ? b_rows_per_flag : 1; p.b_epoch = b_epoch;
 #define GF_DISPATCH(BN_)                                                                  \
   if (!a_mn_major && !b_mn_major) return launch_gemm<BN_, false, false>(tmA, tmB, p, max_ctas, stream); \
   if (!a_mn_major && b_mn_major) return launch_gemm<BN_, false, true>(tmA, tmB, p, max_ctas, stream);   \
@@ -393,4 +642,83 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (bn == 256) { GF_DISPATCH(256) }
   GF_DISPATCH(128)
 #undef GF_DISPATCH
+}
+
+static void no_gather(gf::GemmParams& p) {
+  p.g_operand = -1; p.g_copy_ctas = 0; p.g_world = 1; p.g_rank = 0; p.g_first_shard = 0;
+  for (int i = 0; i < 8; ++i) p.g_src[i] = nullptr;
+  p.g_dst = nullptr; p.g_shard_elems = 8; p.g_operand_off = 0; p.g_operand_ld = 1; p.g_ready = nullptr;
+  p.g_counters = nullptr; p.g_epoch = 0; p.g_version_pad = nullptr; p.g_version_idx = 0; p.g_version_val = 0;
+  p.order_n_fast = 0; p.tile_rot = 0; p.rs_interleave = 0;
+  p.rs_world = 0; p.rs_rank = 0; p.rs_rows_per_rank = 1; p.rs_call = 0; p.rs_out = nullptr; p.rs_ldo = 0;
+  for (int i = 0; i < 8; ++i) { p.rs_stage[i] = nullptr; p.rs_counters[i] = nullptr; }
+}
+
+// lda/ldb: row pitch in elements of the matrix as stored.
+//   a_mn_major = 0: A stored [M, K] (K contiguous); 1: A stored [K, M] (M contiguous).
+//   b_mn_major = 0: B stored [N, K] (K contiguous); 1: B stored [K, N] (N contiguous).
+GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
+                        int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate,
+                        const void* bias, const void* residual, long long ldr, float alpha, int* status,
+                        int bn_hint, int max_ctas, const int* unused_flags, int unused_a, int unused_b,
+                        void* stream_v) {
+  gf::enter();
+  gf::GemmParams p;
+  no_gather(p);
+  return gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias, residual, ldr,
+                   alpha, status, bn_hint, max_ctas, p, reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+// Fused all-gather + GEMM. `operand` = 0: A ([M, K], K-major) is a view into the gathered buffer `g_dst`;
+// 1: B ([N, K], K-major) is. `src_ptrs` are every rank's shard of that buffer (world pointers, peer-mapped);
+// the kernel's first `copy_ctas` CTAs copy them into g_dst while the others compute. `ready` and `counters`
+// are local int[world] (counters zero); `epoch` must grow with every call that reuses `ready`. Shards are copied
+// in the order first_shard, first_shard + 1, ... (first_shard < 0: this rank's own shard first).
+GF_API int gf_gemm_bf16_allgather(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int out_fp32, const void* bias, const void* residual,
+                                  long long ldr, float alpha, int* status, int operand,
+                                  const unsigned long long* src_ptrs, void* g_dst, long long shard_elems, int world,
+                                  int my_rank, int first_shard, int copy_ctas, int* ready, int* counters, int epoch,
+                                  const int* version_pad, int version_idx, int version_val, void* stream_v) {
+  gf::enter();
+  if (world < 1 || world > 8 || (shard_elems & 7) || copy_ctas < 1 || (operand != 0 && operand != 1)) return gf::GFH_BAD_ARG;
+  gf::GemmParams p;
+  no_gather(p);
+  p.g_operand = operand; p.g_copy_ctas = copy_ctas; p.g_world = world; p.g_rank = my_rank;
+  p.g_first_shard = (first_shard >= 0 && first_shard < world) ? first_shard : my_rank;
+  for (int i = 0; i < world; ++i) p.g_src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+  p.g_dst = reinterpret_cast<__nv_bfloat16*>(g_dst);
+  p.g_shard_elems = shard_elems;
+  const char* opnd = reinterpret_cast<const char*>(operand == 0 ? A : B);
+  p.g_operand_off = (opnd - reinterpret_cast<const char*>(g_dst)) / 2;
+  p.g_operand_ld = operand == 0 ? lda : ldb;
+  if (p.g_operand_off < 0) return gf::GFH_BAD_ARG;
+  p.g_ready = ready; p.g_counters = counters; p.g_epoch = epoch;
+  p.g_version_pad = version_pad; p.g_version_idx = version_idx; p.g_version_val = version_val;
+  return gemm_core(A, B, C, M, N, K, 0, lda, 0, ldb, ldc, out_fp32, 0, bias, residual, ldr, alpha, status, 256, 0, p,
+                   reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+// Fused GEMM + reduce-scatter for a row-parallel linear: every rank passes its partial operands
+// (A [M, K_local] K-major, B [N, K_local] K-major). Rows of the result are owned in blocks of M / world; this
+// rank's block (sum over ranks, + bias, + residual [M / world, N]) lands in `out`. `stage_ptrs` / `counter_ptrs`
+// are every rank's staging buffer ([world, M / world, N] bf16) and arrival counters (int[ceil(N / 256)], zeroed
+// once); `call_index` counts earlier calls on the same counters with the same shape.
+GF_API int gf_gemm_bf16_reduce_scatter(const void* A, const void* B, void* out, int M, int N, int K, long long lda,
+                                       long long ldb, long long ldo, const void* bias, const void* residual,
+                                       long long ldr, float alpha, int* status, const unsigned long long* stage_ptrs,
+                                       const unsigned long long* counter_ptrs, int world, int my_rank, int call_index,
+                                       int max_ctas, void* stream_v) {
+  gf::enter();
+  if (world < 1 || world > 8 || (M % world) || (N & 7) || (ldo & 7)) return gf::GFH_BAD_ARG;
+  gf::GemmParams p;
+  no_gather(p);
+  p.rs_world = world; p.rs_rank = my_rank; p.rs_rows_per_rank = M / world; p.rs_call = call_index;
+  p.rs_out = reinterpret_cast<__nv_bfloat16*>(out); p.rs_ldo = ldo;
+  for (int i = 0; i < world; ++i) {
+    p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(stage_ptrs[i]);
+    p.rs_counters[i] = reinterpret_cast<int*>(counter_ptrs[i]);
+  }
+  return gemm_core(A, B, out, M, N, K, 0, lda, 0, ldb, ldo, 0, 0, bias, residual, ldr, alpha, status, 256, max_ctas, p,
+                   reinterpret_cast<cudaStream_t>(stream_v));
 }

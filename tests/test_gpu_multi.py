@@ -45,3 +45,16 @@ def test_fused_collectives_match_nccl_and_single_gpu(tmp_path):
     w1 = eng.gather_unit(eng.layers[2], master=True)["w_gate_up"].cpu()
     assert (fused["w"] - nccl["w"]).norm() / nccl["w"].norm() < 1e-2
     assert (fused["w"] - w1).norm() / w1.norm() < 1e-2
+
+
+def test_fused_tensor_parallel_kernels_match_nccl(tmp_path):
+    """all-gather + GEMM and GEMM + reduce-scatter as single kernels against NCCL followed / preceded by the GEMM."""
+    _need(2)
+    out = str(tmp_path / "tp.pt")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29751",
+                        os.path.join(HERE, "_tp_worker.py"), out], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    res = torch.load(out)
+    assert res and all(v < 1.5e-2 for v in res.values()), res
