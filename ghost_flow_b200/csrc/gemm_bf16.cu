@@ -60,6 +60,7 @@ struct GemmParams {
   long long rs_ldo;
   int order_n_fast;         // 1: consecutive tiles share the A row block (used when A is the gathered operand)
   int rs_interleave;        // > 0: row blocks per owner; the walk then alternates between owners block by block
+  int group_m;              // > 0: plain GEMM walks bands of group_m row blocks (keeps a wave's A and B panels in L2)
   int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
 };
 
@@ -92,6 +93,16 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     int owner = s % p.rs_world + p.rs_rank + 1;
     if (owner >= p.rs_world) owner -= p.rs_world;
     tm = owner * p.rs_interleave + s / p.rs_world;
+  } else if (p.group_m > 0) {
+    // bands of group_m row blocks; inside a band tm runs fastest. One wave of CTAs then touches about
+    // group_m A panels and (CTAs / group_m) B panels instead of every A panel.
+    const int per_band = p.group_m * p.tiles_n;
+    const int band = tile / per_band;
+    const int first = band * p.group_m;
+    const int rows = min(p.group_m, p.tiles_m - first);
+    const int r = tile - band * per_band;
+    tm = first + r % rows;
+    tn = r / rows;
   } else if (p.order_n_fast) {
     tn = tile % p.tiles_n;
     tm = tile / p.tiles_n + p.tile_rot;
@@ -570,6 +581,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if (tiles < grid - n_copy) grid = tiles + n_copy;
+  p.group_m = (p.rs_world == 0 && p.g_operand < 0 && p.tiles_m > 16 && p.tiles_n > 1) ? 16 : 0;
   if (p.rs_world > 0) {
     // walk the row blocks starting with the next rank's rows and ending with this rank's own
     p.order_n_fast = 1;

@@ -97,52 +97,69 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // ------------------------------------------------------------------ RMSNorm backward
 // dx = rstd * g - x * rstd^3 * mean(g * x), g = dy * w ; dw partial = sum_rows dy * x * rstd.
 // If `dres` is given, it is added into dx (gradient arriving through the residual branch).
-__global__ void __launch_bounds__(NORM_THREADS)
+// Operands stay packed (bf16x8 in a uint4) between the two passes over a row and only the dw accumulators are
+// fp32, so for D <= 4096 (MAXV = 2) a thread needs about 64 registers and four CTAs fit on an SM.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+template <int MAXV>
+__global__ void __launch_bounds__(NORM_THREADS, MAXV == 1 ? 4 : (MAXV == 2 ? 3 : 2))
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, int T, int D) {
   __shared__ float red[32];
   const int nv = D >> 3;
-  float dwacc[NORM_MAXV][8];
-  float wv[NORM_MAXV][8];
+  float dwacc[MAXV][8];
+  uint4 wp[MAXV];
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-    if (v < nv) load8(w + v * 8, wv[i]);
+    wp[i] = (v < nv) ? *reinterpret_cast<const uint4*>(w + v * 8) : make_uint4(0, 0, 0, 0);
   }
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const float rstd = rstd_in[row];
-    float xv[NORM_MAXV][8], gv[NORM_MAXV][8];
-    float dot = 0.f;
+    uint4 xp[MAXV], gp[MAXV], rp[MAXV];
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nv) {
-        load8(x + (long long)row * D + v * 8, xv[i]);
-        load8(dy + (long long)row * D + v * 8, gv[i]);
+        xp[i] = *reinterpret_cast<const uint4*>(x + (long long)row * D + v * 8);
+        gp[i] = *reinterpret_cast<const uint4*>(dy + (long long)row * D + v * 8);
+        if (dres) rp[i] = *reinterpret_cast<const uint4*>(dres + (long long)row * D + v * 8);
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nv) {
+        float xv[8], gv[8], wv[8];
+        unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(wp[i], wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          dwacc[i][j] += gv[i][j] * xv[i][j] * rstd;
-          gv[i][j] *= wv[i][j];
-          dot += gv[i][j] * xv[i][j];
+          dwacc[i][j] += gv[j] * xv[j] * rstd;
+          dot += gv[j] * wv[j] * xv[j];
         }
       }
     }
     dot = block_sum(dot, red);
     const float c = dot * rstd * rstd * rstd / (float)D;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nv) {
-        float o[8];
+        float xv[8], gv[8], wv[8], o[8];
+        unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(wp[i], wv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * gv[i][j] - c * xv[i][j];
+        for (int j = 0; j < 8; ++j) o[j] = rstd * gv[j] * wv[j] - c * xv[j];
         if (dres) {
           float rv[8];
-          load8(dres + (long long)row * D + v * 8, rv);
+          unpack8(rp[i], rv);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += rv[j];
         }
@@ -151,7 +168,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nv) {
       float* dst = dw_partial + (long long)blockIdx.x * D + v * 8;
@@ -318,7 +335,9 @@ GF_API int gf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const fl
   gf::enter();
   if (D % 8 || D > NORM_THREADS * NORM_MAXV * 8 || T <= 0) return GFH_BAD_ARG;
   const int g = norm_grid(T);
-  rmsnorm_bwd_kernel<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+  auto kern = D <= NORM_THREADS * 8 ? rmsnorm_bwd_kernel<1>
+              : D <= NORM_THREADS * 16 ? rmsnorm_bwd_kernel<2> : rmsnorm_bwd_kernel<NORM_MAXV>;
+  kern<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, scratch, T, D);
   fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
