@@ -59,7 +59,31 @@ struct GemmParams {
   __nv_bfloat16* rs_out;            // local output [rows_per_rank, N]
   long long rs_ldo;
   int order_n_fast;         // 1: consecutive tiles share the A row block (used when A is the gathered operand)
+  int rs_tma;               // partial tiles leave through shared memory and TMA stores (full NVLink packets)
   int rs_interleave;        // > 0: row blocks per owner; the walk then alternates between owners block by block
+  // ---- grouped GEMM over row segments (experts of a mixture-of-experts layer). grp_offsets[e] is the first row
+  // of segment e in a row-sorted buffer, every entry a multiple of BM, grp_offsets[experts] the total.
+  //  mode 1: C[rows, N] = A[rows, K] x B_e, B_e the e-th matrix of a stacked weight (forward / input gradient)
+  //  mode 2: C_e[M, N] = A[rows_e, M]^T x B[rows_e, N], the contraction runs over the rows of segment e (weight
+  //          gradient); C is stacked [experts, M, N]
+  const int* grp_offsets;
+  int grp_experts, grp_mode;
+  int grp_b_rows;           // rows of one B_e in the stacked tensor map (mode 1)
+  // mode 1 fed by an all-to-all dispatch: rows of segment e that came from rank r are
+  // [grp_src_start[e * (grp_world + 1) + r], ...[r + 1]); rank r's rows are complete once grp_arrived[r] >= grp_epoch.
+  // A tile waits only for the ranks whose rows it reads.
+  const int* grp_src_start;
+  const int* grp_arrived;
+  int grp_world, grp_epoch;
+  // scatter epilogue (all-to-all combine fused into the GEMM): output row r goes to rank sc_ret[r].x, row
+  // sc_ret[r].y of that rank's buffer sc_dst[rank] (pitch sc_ld); rows with sc_ret[r].y < 0 are padding. When the
+  // last CTA is done it stores sc_epoch into sc_flags[peer][sc_rank] of every rank.
+  const int2* sc_ret;
+  __nv_bfloat16* sc_dst[8];
+  int* sc_flags[8];
+  long long sc_ld;
+  int sc_world, sc_rank, sc_epoch;
+  int* sc_counter;
   int group_m;              // > 0: plain GEMM walks bands of group_m row blocks (keeps a wave's A and B panels in L2)
   int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
 };
@@ -76,6 +100,14 @@ struct GemmCfg {
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = (2 * BN >= 512) ? 512 : (2 * BN >= 256 ? 256 : 128);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+// Fused reduce-scatter: every epilogue warp stages 32 rows x 128 columns of a partial tile in shared memory and
+// sends them to the owner rank with one TMA store, so NVLink carries full packets instead of 16-byte stores.
+constexpr int RS_STAGE_COLS = 128;
+constexpr int RS_STAGE_BYTES = 4 * 32 * RS_STAGE_COLS * 2;
+struct RsMaps {
+  CUtensorMap m[8];         // every rank's staging buffer [world * rows_per_rank, N], box 32 x 128, no swizzle
 };
 
 __device__ __forceinline__ void set_status(int* status, int code) {
@@ -112,6 +144,47 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     tn = tile / p.tiles_m + p.tile_rot;
     if (tn >= p.tiles_n) tn -= p.tiles_n;
   }
+}
+
+struct TileInfo {
+  int tm, tn;
+  int a_row;        // row (M) coordinate of the A tile in its tensor map
+  int b_row;        // row (N) coordinate of the B tile in its tensor map (K-major B)
+  int b_k_add;      // added to the k coordinate of an MN-major B (stacked [experts * K, N])
+  int k_begin;      // first k of the contraction
+  int nkb;          // k blocks of the contraction
+  long long c_row_add;  // added to the output row
+};
+
+// Fills `t` for tile index `tile`; false if the tile has nothing to compute (grouped modes).
+__device__ __forceinline__ bool tile_info(const GemmParams& p, int tile, int num_kb, TileInfo& t) {
+  t.b_k_add = 0; t.k_begin = 0; t.nkb = num_kb; t.c_row_add = 0;
+  if (p.grp_mode == 2) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int e = tile / per;
+    const int r = tile - e * per;
+    t.tm = r % p.tiles_m;
+    t.tn = r / p.tiles_m;
+    t.a_row = t.tm * BM;
+    t.b_row = 0;
+    const int k0 = __ldg(p.grp_offsets + e), k1 = __ldg(p.grp_offsets + e + 1);
+    t.k_begin = k0;
+    t.nkb = (k1 - k0) / BK;
+    t.c_row_add = (long long)e * p.M;
+    return true;              // an empty segment still owes zeros (or nothing, when accumulating) to the output
+  }
+  tile_coords(p, tile, t.tm, t.tn);
+  t.a_row = t.tm * BM;
+  t.b_row = 0;
+  if (p.grp_mode == 1) {
+    if (t.a_row >= __ldg(p.grp_offsets + p.grp_experts)) return false;
+    int e = 0;
+    while (e + 1 < p.grp_experts && __ldg(p.grp_offsets + e + 1) <= t.a_row) ++e;
+    t.b_row = e * p.grp_b_rows;
+    t.b_k_add = e * p.grp_b_rows;
+    t.c_row_add = -(long long)(e + 1);      // producer: the segment index, recovered below (outputs add nothing)
+  }
+  return true;
 }
 
 // Copy CTAs of the fused all-gather. One thread per copy CTA drives the bulk-copy engine: peer shard ->
@@ -205,7 +278,7 @@ __device__ __forceinline__ void gather_role(const GemmParams& p, uint8_t* smem) 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const GemmParams p, const __grid_constant__ RsMaps rsm) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -214,11 +287,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull_bar = empty_bar + Cfg::STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint8_t* rs_stage_smem = smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256;    // behind the barriers; only with p.rs_tma
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1);
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if ((int)blockIdx.x < n_copy) {
     gather_role(p, smem);
@@ -256,9 +330,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
-        int tm, tn;
-        tile_coords(p, tile, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        TileInfo ti;
+        if (!tile_info(p, tile, num_kb, ti)) continue;
+        const int m0 = ti.a_row, n0 = ti.tn * BN;
+        if (p.grp_src_start) {
+          const int e = (int)(-ti.c_row_add) - 1;
+          const int* ss = p.grp_src_start + e * (p.grp_world + 1);
+          for (int r = 0; r < p.grp_world && ok; ++r) {
+            if (__ldg(ss + r) >= m0 + BM || __ldg(ss + r + 1) <= m0) continue;
+            uint32_t spins = 0;
+            while (true) {
+              int v;
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.grp_arrived + r) : "memory");
+              if (v >= p.grp_epoch) break;
+              if (++spins > GF_WAIT_LIMIT) { ok = false; break; }
+              __nanosleep(64);
+            }
+          }
+          if (!ok) {
+            set_status(p.status, GF_ERR_WAIT_PEER);
+            break;
+          }
+          fence_proxy_async_all();
+        }
         if (p.g_operand >= 0) {
           // shards that hold the rows of the gathered operand read by this tile
           const long long r0 = p.g_operand == 0 ? m0 : n0;
@@ -287,7 +381,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           fence_proxy_async_all();
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             set_status(p.status, GF_ERR_WAIT_EMPTY);
             ok = false;
@@ -296,7 +390,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = ti.k_begin + kb * BK;
           if (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           } else {
@@ -304,10 +398,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[stage], m0 + c * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, ti.b_row + n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[stage], n0 + c * 64, k0);
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tmB, &full_bar[stage], n0 + c * 64, ti.b_k_add + k0);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -324,16 +419,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += nctas, ++it) {
+      for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
+        TileInfo ti;
+        if (!tile_info(p, tile, num_kb, ti) || ti.nkb == 0) continue;
         const int buf = it & 1;
         const uint32_t bphase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&tempty_bar[buf], bphase ^ 1)) {
           set_status(p.status, GF_ERR_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             set_status(p.status, GF_ERR_WAIT_FULL);
             ok = false;
@@ -363,13 +461,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int lane_grp = warp & 3;  // TMEM lanes [32*lane_grp, +32) belong to this warp
     int it = 0;
-    for (int tile = cta; tile < num_tiles; tile += nctas, ++it) {
-      const int buf = it & 1;
-      const uint32_t bphase = (it >> 1) & 1;
-      int tm, tn;
-      tile_coords(p, tile, tm, tn);
+    for (int tile = cta; tile < num_tiles; tile += nctas) {
+      TileInfo ti;
+      if (!tile_info(p, tile, num_kb, ti)) continue;
+      const int tm = ti.tm, tn = ti.tn;
+      if (p.grp_mode == 1) ti.c_row_add = 0;
       const int row = tm * BM + lane_grp * 32 + lane;
       const int n0 = tn * BN;
+      if (ti.nkb == 0) {
+        // empty segment of a grouped weight gradient: the result is zero
+        if (!p.accumulate && row < p.M) {
+          for (int col = n0; col < min(p.N, n0 + BN); ++col) {
+            if (p.out_fp32) reinterpret_cast<float*>(p.C)[(ti.c_row_add + row) * p.ldc + col] = 0.f;
+            else reinterpret_cast<__nv_bfloat16*>(p.C)[(ti.c_row_add + row) * p.ldc + col] = __float2bfloat16(0.f);
+          }
+        }
+        continue;
+      }
+      const int buf = it & 1;
+      const uint32_t bphase = (it >> 1) & 1;
+      ++it;
       if (!mbar_wait_warp(&tfull_bar[buf], bphase)) {
         set_status(p.status, GF_ERR_WAIT_TMEM_FULL);
         break;
@@ -409,7 +520,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
           }
-          if (p.rs_world > 0) {
+          if (p.rs_tma) {
+            __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(rs_stage_smem) + (warp - 2) * 32 * RS_STAGE_COLS;
+            const int sub = c & 3;
+            if (sub == 0) {
+              if (lane == 0) tma_store_wait_read<0>();     // the previous store has read the staging rows
+              __syncwarp();
+            }
+            __nv_bfloat16* sp = stg + lane * RS_STAGE_COLS + sub * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(sp + q * 8) = o;
+            }
+            if (sub == 3 || col0 + 32 >= p.N) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                const int row0 = tm * BM + lane_grp * 32;
+                const int owner = row0 / p.rs_rows_per_rank;
+                const int srow = p.rs_rank * p.rs_rows_per_rank + (row0 - owner * p.rs_rows_per_rank);
+                tma_store_2d(&rsm.m[owner], stg, n0 + (c >> 2) * RS_STAGE_COLS, srow);
+                tma_store_commit();
+              }
+            }
+          } else if (p.rs_world > 0) {
             // partial result -> owner's staging slot [my rank][local row]
             const int owner = row / p.rs_rows_per_rank;
             const int lrow = row - owner * p.rs_rows_per_rank;
@@ -430,7 +569,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
             }
           } else if (p.out_fp32) {
-            float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+            float* cp = reinterpret_cast<float*>(p.C) + (ti.c_row_add + row) * p.ldc + col0;
             if (full && ((p.ldc & 3) == 0)) {
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
@@ -447,7 +586,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) cp[j] = p.accumulate ? cp[j] + v[j] : v[j];
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (ti.c_row_add + row) * p.ldc + col0;
+            if (p.sc_ret) {
+              const int2 rt = __ldg(p.sc_ret + row);
+              if (rt.y < 0) continue;
+              cp = p.sc_dst[rt.x] + (long long)rt.y * p.sc_ld + col0;
+            }
             if (full && ((p.ldc & 7) == 0)) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -482,6 +626,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       if (p.rs_world > 0) {
         // all 128 epilogue threads have stored their rows: publish the tile to the owners of those rows
+        if (p.rs_tma && lane == 0) tma_store_wait<0>();
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
@@ -554,14 +699,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // ------------------------------------------------------------ teardown
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) error_drain_pause();
+  if (p.sc_ret) __threadfence_system();      // rows stored into peers' buffers by this thread
   tc_fence_before();
   __syncthreads();
+  if (p.sc_ret && threadIdx.x == 0) {
+    const int done = atomicAdd(p.sc_counter, 1);
+    if (done == nctas - 1) {
+      *p.sc_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.sc_world; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.sc_flags[r] + p.sc_rank), "r"(p.sc_epoch) : "memory");
+    }
+  }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
+
+static RsMaps g_no_rs_maps;   // zero-filled; passed when the launch has no reduce-scatter
+static thread_local const RsMaps* g_rs_maps = nullptr;
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_ctas,
@@ -570,18 +728,19 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES + RS_STAGE_BYTES);
     if (e != cudaSuccess) return GFH_CUDA;
     configured = true;
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  int tiles = p.tiles_m * p.tiles_n;
+  int tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if (tiles < grid - n_copy) grid = tiles + n_copy;
-  p.group_m = (p.rs_world == 0 && p.g_operand < 0 && p.tiles_m > 16 && p.tiles_n > 1) ? 16 : 0;
+  p.group_m = (p.rs_world == 0 && p.g_operand < 0 && p.grp_mode != 2 && p.tiles_m > 16 && p.tiles_n > 1) ? 16 : 0;
   if (p.rs_world > 0) {
     // walk the row blocks starting with the next rank's rows and ending with this rank's own
     p.order_n_fast = 1;
@@ -601,7 +760,9 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
       p.tile_rot = (int)((row / BN) % p.tiles_n);
     }
   }
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  const RsMaps* maps = (p.rs_tma && g_rs_maps) ? g_rs_maps : &g_no_rs_maps;
+  if (p.rs_tma && !g_rs_maps) p.rs_tma = 0;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES + (p.rs_tma ? RS_STAGE_BYTES : 0), stream>>>(tmA, tmB, p, *maps);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
 
@@ -636,10 +797,11 @@ static int gemm_core(const void* A, const void* B, void* C, int M, int N, int K,
   else
     rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda * 2, BK, 64);
   if (rc) return rc;
+  const long long stack = p.grp_mode == 1 ? p.grp_experts : 1;   // B is `stack` matrices one after another
   if (!b_mn_major)
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, bn, BK);
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N * stack, K, ldb * 2, bn, BK);
   else
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb * 2, BK, 64);
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K * stack, N, ldb * 2, BK, 64);
   if (rc) return rc;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
@@ -661,7 +823,11 @@ static void no_gather(gf::GemmParams& p) {
   for (int i = 0; i < 8; ++i) p.g_src[i] = nullptr;
   p.g_dst = nullptr; p.g_shard_elems = 8; p.g_operand_off = 0; p.g_operand_ld = 1; p.g_ready = nullptr;
   p.g_counters = nullptr; p.g_epoch = 0; p.g_version_pad = nullptr; p.g_version_idx = 0; p.g_version_val = 0;
-  p.order_n_fast = 0; p.tile_rot = 0; p.rs_interleave = 0;
+  p.order_n_fast = 0; p.tile_rot = 0; p.rs_interleave = 0; p.rs_tma = 0;
+  p.grp_offsets = nullptr; p.grp_experts = 0; p.grp_mode = 0; p.grp_b_rows = 0;
+  p.grp_src_start = nullptr; p.grp_arrived = nullptr; p.grp_world = 1; p.grp_epoch = 0;
+  p.sc_ret = nullptr; p.sc_ld = 0; p.sc_world = 0; p.sc_rank = 0; p.sc_epoch = 0; p.sc_counter = nullptr;
+  for (int i = 0; i < 8; ++i) { p.sc_dst[i] = nullptr; p.sc_flags[i] = nullptr; }
   p.rs_world = 0; p.rs_rank = 0; p.rs_rows_per_rank = 1; p.rs_call = 0; p.rs_out = nullptr; p.rs_ldo = 0;
   for (int i = 0; i < 8; ++i) { p.rs_stage[i] = nullptr; p.rs_counters[i] = nullptr; }
 }
@@ -679,6 +845,51 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   no_gather(p);
   return gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias, residual, ldr,
                    alpha, status, bn_hint, max_ctas, p, reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+// Grouped GEMM over the row segments of a row-sorted buffer (the experts of a mixture-of-experts layer).
+// `offsets` is a DEVICE int[experts + 1]: first row of every segment and the total; every entry must be a multiple
+// of 128 and rows between a segment's last token and the next boundary must hold zeros.
+//   mode 1: C[rows, N] = A[rows, K] * op(B_e) for the rows of segment e. A is K-major with `rows_cap` rows
+//           (an upper bound of offsets[experts]; tiles beyond the total are skipped). B is the stacked weight:
+//           b_mn_major = 0 -> [experts, N, K]; 1 -> [experts, K, N].
+//   mode 2: C_e[M, N] = A[rows_e, M]^T * B[rows_e, N] (both operands row-sorted activations, MN-major), C stacked
+//           [experts, M, N]; `rows_cap` is the row count of A and B.
+GF_API int gf_gemm_bf16_grouped(const void* A, const void* B, void* C, int mode, int rows_cap, int M, int N, int K,
+                                long long lda, int b_mn_major, long long ldb, long long ldc, int out_fp32,
+                                int accumulate, float alpha, int* status, const int* offsets, int experts,
+                                const int* src_start, const int* arrived, int world, int epoch,
+                                const void* scatter_ret, const unsigned long long* scatter_dst,
+                                const unsigned long long* scatter_flags, long long scatter_ld, int my_rank,
+                                int scatter_epoch, int* scatter_counter, void* stream_v) {
+  gf::enter();
+  if (!offsets || experts <= 0 || (mode != 1 && mode != 2) || rows_cap % 128) return gf::GFH_BAD_ARG;
+  if (world < 1 || world > 8) return gf::GFH_BAD_ARG;
+  gf::GemmParams p;
+  no_gather(p);
+  p.grp_offsets = offsets; p.grp_experts = experts; p.grp_mode = mode;
+  if (src_start && arrived) {
+    p.grp_src_start = src_start; p.grp_arrived = arrived; p.grp_world = world; p.grp_epoch = epoch;
+  }
+  if (scatter_ret) {
+    if (mode != 1 || out_fp32 || accumulate || !scatter_dst || !scatter_flags || !scatter_counter)
+      return gf::GFH_BAD_ARG;
+    p.sc_ret = reinterpret_cast<const int2*>(scatter_ret);
+    for (int i = 0; i < world; ++i) {
+      p.sc_dst[i] = reinterpret_cast<__nv_bfloat16*>(scatter_dst[i]);
+      p.sc_flags[i] = reinterpret_cast<int*>(scatter_flags[i]);
+    }
+    p.sc_ld = scatter_ld; p.sc_world = world; p.sc_rank = my_rank; p.sc_epoch = scatter_epoch;
+    p.sc_counter = scatter_counter;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  if (mode == 1) {
+    p.grp_b_rows = b_mn_major ? K : N;
+    return gemm_core(A, B, C, rows_cap, N, K, 0, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, nullptr, nullptr, 0,
+                     alpha, status, 0, 0, p, st);
+  }
+  return gemm_core(A, B, C, M, N, rows_cap, 1, lda, 1, ldb, ldc, out_fp32, accumulate, nullptr, nullptr, 0, alpha,
+                   status, 0, 0, p, st);
 }
 
 // Fused all-gather + GEMM. `operand` = 0: A ([M, K], K-major) is a view into the gathered buffer `g_dst`;
@@ -731,6 +942,21 @@ GF_API int gf_gemm_bf16_reduce_scatter(const void* A, const void* B, void* out, 
     p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(stage_ptrs[i]);
     p.rs_counters[i] = reinterpret_cast<int*>(counter_ptrs[i]);
   }
-  return gemm_core(A, B, out, M, N, K, 0, lda, 0, ldb, ldo, 0, 0, bias, residual, ldr, alpha, status, 256, max_ctas, p,
-                   reinterpret_cast<cudaStream_t>(stream_v));
+  gf::RsMaps maps;
+  if ((M / world) % gf::BM == 0) {
+    // partial tiles go out as TMA stores of 32 x 128 boxes into the owners' staging buffers
+    p.rs_tma = 1;
+    for (int i = 0; i < 8; ++i) {
+      const int src = i < world ? i : 0;
+      int rc = gf::make_tmap_2d(&maps.m[i], reinterpret_cast<const void*>(stage_ptrs[src]),
+                                CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, (long long)N * 2, 32, gf::RS_STAGE_COLS,
+                                CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
+    gf::g_rs_maps = &maps;
+  }
+  int rc = gemm_core(A, B, out, M, N, K, 0, lda, 0, ldb, ldo, 0, 0, bias, residual, ldr, alpha, status, 256, max_ctas,
+                     p, reinterpret_cast<cudaStream_t>(stream_v));
+  gf::g_rs_maps = nullptr;
+  return rc;
 }

@@ -20,6 +20,7 @@ enum : int {
   GF_ERR_WAIT_PEER = 5,      // a flag owned by another rank never arrived
   GF_ERR_WAIT_SOFTMAX = 6,
   GF_ERR_BAD_ARG = 7,
+  GF_ERR_CAPACITY = 8,       // more rows were routed to this rank than its buffers hold
 };
 
 #ifndef GF_WAIT_LIMIT

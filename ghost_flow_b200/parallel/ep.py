@@ -1,0 +1,362 @@
+"""Expert-parallel mixture of experts: router, all-to-all dispatch/combine over peer memory, grouped expert GEMMs.
+
+The reference routes token by token on the CPU and runs every expert in one process
+(ghostflow-nn/src/mixture_of_experts.rs:152-177 router, :212-274 dispatch loop, :289-323 load-balance loss).
+Here ``num_experts`` SwiGLU experts are sharded over the ranks of one NVSwitch box. One forward is
+
+    logits = x Wg^T -> route (softmax, top-k, renormalise) -> publish histogram -> plan segments
+    -> dispatch token rows into the owner ranks' buffers (peer stores) -> grouped GEMM W13 (waits per tile for the
+    source ranks it reads) -> SwiGLU -> grouped GEMM W2 whose epilogue stores every output row straight into the
+    token's home rank -> weighted sum per token
+
+and the backward runs the same machinery in reverse (the gradient of the combine is a dispatch, the gradient of
+the dispatch is a combine) plus grouped weight-gradient GEMMs that contract over each expert's row segment.
+With ``world == 1`` the same kernels run on plain local buffers. ``forward``/``backward`` are explicit (no autograd
+graph), ``ExpertParallelMoE.apply`` wraps them in a ``torch.autograd.Function`` for use inside torch models.
+On CPU tensors a dense PyTorch restatement is used (the test oracle).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib, raw
+
+_BOUND = False
+
+
+def _bind():
+    global _BOUND
+    lib = _lib.cuda_lib()
+    if not _BOUND:
+        P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.gf_moe_route.argtypes = [P, I, I, I, I, I, P, P, P, P, P]
+        lib.gf_moe_publish.argtypes = [P, P, P, I, I, I, I, I, P]
+        lib.gf_moe_plan.argtypes = [P, P, I, I, I, I, I, I, P, P, P, P, P, P]
+        lib.gf_moe_dispatch.argtypes = [P, L, P, P, I, I, I, I, I, I, I, P, P, P, I, P, P, P, I, I, P, P]
+        lib.gf_moe_zero_pad.argtypes = [P, I, P, P, P, I, I, I, P]
+        lib.gf_moe_combine.argtypes = [P, P, P, P, I, I, I, P, I, I, I, P, P, P, P]
+        lib.gf_gemm_bf16_grouped.argtypes = [P, P, P, I, I, I, I, I, L, I, L, L, I, I, F, P, P, I,
+                                             P, P, I, I, P, P, P, L, I, I, P, P]
+        for n in ("gf_moe_route", "gf_moe_publish", "gf_moe_plan", "gf_moe_dispatch", "gf_moe_zero_pad",
+                  "gf_moe_combine", "gf_gemm_bf16_grouped"):
+            getattr(lib, n).restype = I
+        _BOUND = True
+    return lib
+
+
+def _u64(vals):
+    return (ctypes.c_ulonglong * len(vals))(*[int(v) for v in vals])
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+FLAG_COUNTS, FLAG_DISPATCH, FLAG_COMBINE = 0, 1, 2
+
+
+def grouped_gemm(a, b, out, mode, offsets, experts, *, rows_cap, M=0, N, K, b_mn=False, out_fp32=False,
+                 accumulate=False, wait=None, scatter=None):
+    """Thin wrapper over ``gf_gemm_bf16_grouped`` (see the comment above that function for the two modes).
+
+    ``wait = (src_start, arrived, world, epoch)`` makes every tile wait for the source ranks of its rows;
+    ``scatter = (ret, dst_ptrs, flag_ptrs, ld, rank, world, epoch, counter)`` sends the output rows home."""
+    lib = _bind()
+    dev = a.device
+    ws = wait or (None, None, 1, 0)
+    world = ws[2]
+    sc = scatter
+    rc = lib.gf_gemm_bf16_grouped(
+        a.data_ptr(), b.data_ptr(), _ptr(out), mode, rows_cap, M, N, K, a.stride(0),
+        1 if b_mn else 0, b.stride(-2), out.stride(-2) if out is not None else 0, 1 if out_fp32 else 0,
+        1 if accumulate else 0, 1.0, _lib.status_word(dev).data_ptr(), offsets.data_ptr(), experts,
+        _ptr(ws[0]), _ptr(ws[1]), sc[5] if sc else world, ws[3],
+        _ptr(sc[0]) if sc else None, sc[1] if sc else None, sc[2] if sc else None, sc[3] if sc else 0,
+        sc[4] if sc else 0, sc[6] if sc else 0, _ptr(sc[7]) if sc else None, _lib.stream_ptr())
+    _lib.check_rc(rc, "gf_gemm_bf16_grouped")
+    return out
+
+
+@dataclass
+class MoEContext:
+    """What one forward leaves behind for its backward."""
+    x: torch.Tensor
+    idx: torch.Tensor
+    w: torch.Tensor
+    probs: torch.Tensor
+    dest_row: torch.Tensor
+    seg_offsets: torch.Tensor
+    src_start: torch.Tensor
+    h: torch.Tensor
+    a: torch.Tensor
+
+
+class ExpertParallelMoE:
+    """SwiGLU experts sharded over ``group`` (``num_experts % world == 0``), top-``k`` softmax routing with
+    renormalised weights (the Mixtral recipe).
+
+    Parameters (bf16): ``gate [E, d]``, ``w13 [E_local, 2 * d_ff, d]`` (gate rows then up rows), ``w2 [E_local, d, d_ff]``.
+    ``tokens`` is the number of tokens per rank and call; ``capacity_factor`` bounds the rows a rank accepts:
+    ``rows_cap = capacity_factor * tokens * k`` (+ padding); the default ``world`` is the drop-free worst case. If more rows
+    arrive than fit the owner's kernel records status 8 and :func:`ghost_flow_b200.ops._lib.check_status` raises.
+    """
+
+    def __init__(self, d_model, d_ff, num_experts, k, tokens, device, group=None, capacity_factor=None, seed=0):
+        self.group = group
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        assert num_experts % self.world == 0 and d_model % 8 == 0 and d_ff % 8 == 0
+        self.d, self.f, self.E, self.k, self.T = d_model, d_ff, num_experts, k, tokens
+        self.el = num_experts // self.world
+        self.device = torch.device(device)
+        cf = float(capacity_factor if capacity_factor is not None else self.world)
+        self.rows_cap = (int(cf * tokens * k) + self.el * 128 + 127) // 128 * 128
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        bf = torch.bfloat16
+
+        def init(*shape, std):
+            return (torch.randn(*shape, generator=g) * std).to(bf).to(self.device)
+
+        # the router weight is stored padded to a multiple of 128 rows (zeros) so that the router GEMMs have
+        # tile-sized extents; ``gate`` and its gradient are views of the first ``num_experts`` rows
+        ep_rows = (num_experts + 127) // 128 * 128
+        self.gate_pad = torch.zeros(ep_rows, d_model, dtype=bf, device=self.device)
+        self.gate_pad[:num_experts] = init(num_experts, d_model, std=0.02)
+        self.gate = self.gate_pad[:num_experts]
+        all13 = init(num_experts, 2 * d_ff, d_model, std=0.02)
+        all2 = init(num_experts, d_model, d_ff, std=0.02)
+        lo, hi = self.rank * self.el, (self.rank + 1) * self.el
+        self.w13, self.w2 = all13[lo:hi].contiguous(), all2[lo:hi].contiguous()
+        self.gate_grad_pad = torch.zeros_like(self.gate_pad)
+        self.grads = {"gate": self.gate_grad_pad[:num_experts], "w13": torch.zeros_like(self.w13),
+                      "w2": torch.zeros_like(self.w2)}
+        self.epoch = 0
+        self.last_counts = None
+        if self.device.type == "cuda":
+            self._alloc()
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc(self):
+        R, d, T, k, E, W = self.rows_cap, self.d, self.T, self.k, self.E, self.world
+        sizes = {"xs": R * d * 2, "dys": R * d * 2, "ret": R * 8, "comb": T * k * d * 2, "dcomb": T * k * d * 2,
+                 "table": W * E * 4, "flags": 4 * 8 * 4}
+        total = sum((v + 255) // 256 * 256 for v in sizes.values()) + 4096
+        if W > 1:
+            from .tp import SymmetricWorkspace
+            self.ws = SymmetricWorkspace(total, self.device, self.group or dist.group.WORLD)
+            alloc, peers = self.ws.alloc, self.ws.peer_ptrs
+        else:
+            buf = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            self._buf, off = buf, [0]
+
+            def alloc(numel, dtype):
+                esz = torch.empty((), dtype=dtype).element_size()
+                t = buf[off[0]:off[0] + numel * esz].view(dtype)
+                off[0] += (numel * esz + 255) // 256 * 256
+                return t
+
+            def peers(t):
+                return [t.data_ptr()]
+        bf, i32 = torch.bfloat16, torch.int32
+        self.xs = alloc(R * d, bf).view(R, d)
+        self.dys = alloc(R * d, bf).view(R, d)
+        self.ret = alloc(R * 2, i32).view(R, 2)
+        self.comb = alloc(T * k * d, bf).view(T * k, d)
+        self.dcomb = alloc(T * k * d, bf).view(T * k, d)
+        self.table = alloc(W * E, i32).view(W, E)
+        self.flags = alloc(32, i32)
+        self.p = {n: _u64(peers(getattr(self, n))) for n in ("xs", "dys", "ret", "comb", "dcomb", "table", "flags")}
+        dev = self.device
+        self.counts = torch.zeros(E, dtype=i32, device=dev)
+        self.send_base = torch.zeros(E, dtype=i32, device=dev)
+        self.cursor = torch.zeros(E, dtype=i32, device=dev)
+        self.done = torch.zeros(4, dtype=i32, device=dev)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, residual=None):
+        """x [T, d] bf16 -> (y [T, d], ctx)."""
+        if x.device.type != "cuda":
+            return self._forward_ref(x, residual)
+        lib, st = _bind(), _lib.stream_ptr
+        T, k, d, f, E, W, R = self.T, self.k, self.d, self.f, self.E, self.world, self.rows_cap
+        assert x.shape == (T, d) and x.dtype == torch.bfloat16 and x.is_contiguous()
+        dev, status = self.device, _lib.status_word(self.device).data_ptr()
+        logits = raw.gemm(x, False, self.gate_pad, True, out_dtype=torch.float32)[:, :E].contiguous()
+        idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, k, dtype=torch.float32, device=dev)
+        probs = torch.empty(T, E, dtype=torch.float32, device=dev)
+        self.counts.zero_()
+        _lib.check_rc(lib.gf_moe_route(logits.data_ptr(), 1, T, E, k, 1, idx.data_ptr(), w.data_ptr(), probs.data_ptr(),
+                                       self.counts.data_ptr(), st()), "gf_moe_route")
+        self.epoch += 1
+        ep = self.epoch
+        _lib.check_rc(lib.gf_moe_publish(self.p["table"], self.p["flags"], self.counts.data_ptr(), E, W, self.rank,
+                                         FLAG_COUNTS, ep, st()), "gf_moe_publish")
+        seg = torch.empty(self.el + 1, dtype=torch.int32, device=dev)
+        src_start = torch.empty(self.el, W + 1, dtype=torch.int32, device=dev)
+        _lib.check_rc(lib.gf_moe_plan(self.table.data_ptr(), self.flags.data_ptr(), FLAG_COUNTS, ep, E, W, self.rank, R,
+                                      seg.data_ptr(), src_start.data_ptr(), self.send_base.data_ptr(),
+                                      self.cursor.data_ptr(), status, st()), "gf_moe_plan")
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        _lib.check_rc(lib.gf_moe_dispatch(x.data_ptr(), x.stride(0), idx.data_ptr(), None, T, k, d, E, W, self.rank, R,
+                                          self.send_base.data_ptr(), self.cursor.data_ptr(), dest_row.data_ptr(), 0,
+                                          self.p["xs"], self.p["ret"], self.p["flags"], FLAG_DISPATCH, ep,
+                                          self.done.data_ptr(), st()), "gf_moe_dispatch")
+        _lib.check_rc(lib.gf_moe_zero_pad(self.xs.data_ptr(), d, self.ret.data_ptr(), seg.data_ptr(),
+                                          src_start.data_ptr(), self.el, W, R, st()), "gf_moe_zero_pad")
+        h = torch.empty(R, 2 * f, dtype=torch.bfloat16, device=dev)
+        grouped_gemm(self.xs, self.w13, h, 1, seg, self.el, rows_cap=R, N=2 * f, K=d,
+                     wait=(src_start, self.flags[FLAG_DISPATCH * 8:], W, ep))
+        a = raw.swiglu_fwd(h)
+        grouped_gemm(a, self.w2, self.comb, 1, seg, self.el, rows_cap=R, N=d, K=f,
+                     scatter=(self.ret, self.p["comb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
+                              self.done[1:]))
+        y = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
+        _lib.check_rc(lib.gf_moe_combine(self.comb.data_ptr(), w.data_ptr(), _ptr(residual), y.data_ptr(), T, k, d,
+                                         self.flags.data_ptr(), FLAG_COMBINE, ep, W, None, None, status, st()),
+                      "gf_moe_combine")
+        self.last_counts = self.counts.clone()
+        return y, MoEContext(x, idx, w, probs, dest_row, seg, src_start, h, a)
+
+    def _flag_ptrs(self, row):
+        """Every rank's flag row ``row`` (the kernels index it by source rank)."""
+        return _u64([int(v) + row * 8 * 4 for v in self.p["flags"]])
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, ctx: MoEContext, dy: torch.Tensor):
+        """Accumulates into ``self.grads`` and returns dx [T, d] (without the residual branch)."""
+        if dy.device.type != "cuda":
+            return self._backward_ref(ctx, dy)
+        lib, st = _bind(), _lib.stream_ptr
+        T, k, d, f, E, W, R = self.T, self.k, self.d, self.f, self.E, self.world, self.rows_cap
+        dev, status = self.device, _lib.status_word(self.device).data_ptr()
+        seg, src_start = ctx.seg_offsets, ctx.src_start
+        dy = dy.contiguous()
+        # d(weights): <dy[t], expert output of slot s>; the per-slot outputs are still in comb
+        dots = torch.empty(T, k, dtype=torch.float32, device=dev)
+        _lib.check_rc(lib.gf_moe_combine(self.comb.data_ptr(), None, None, None, T, k, d, None, 0, 0, W, dy.data_ptr(),
+                                         dots.data_ptr(), status, st()), "gf_moe_combine(dots)")
+        # gradient of the combine = dispatch of w * dy to the forward rows
+        self.epoch += 1
+        ep = self.epoch
+        _lib.check_rc(lib.gf_moe_dispatch(dy.data_ptr(), dy.stride(0), ctx.idx.data_ptr(), ctx.w.data_ptr(), T, k, d, E, W,
+                                          self.rank, R, self.send_base.data_ptr(), self.cursor.data_ptr(),
+                                          ctx.dest_row.data_ptr(), 1, self.p["dys"], self.p["ret"], self.p["flags"],
+                                          FLAG_DISPATCH, ep, self.done.data_ptr(), st()), "gf_moe_dispatch(bwd)")
+        _lib.check_rc(lib.gf_moe_zero_pad(self.dys.data_ptr(), d, None, seg.data_ptr(), src_start.data_ptr(), self.el, W,
+                                          R, st()), "gf_moe_zero_pad")
+        wait = (src_start, self.flags[FLAG_DISPATCH * 8:], W, ep)
+        da = torch.empty(R, f, dtype=torch.bfloat16, device=dev)
+        grouped_gemm(self.dys, self.w2, da, 1, seg, self.el, rows_cap=R, N=f, K=d, b_mn=True, wait=wait)
+        grouped_gemm(self.dys, ctx.a, self.grads["w2"], 2, seg, self.el, rows_cap=R, M=d, N=f, K=R, accumulate=True)
+        dh = raw.swiglu_bwd(ctx.h, da)
+        # padding rows of h are zero, so dh is zero there as well and the weight gradient ignores them
+        grouped_gemm(dh, self.xs, self.grads["w13"], 2, seg, self.el, rows_cap=R, M=2 * f, N=d, K=R, accumulate=True)
+        grouped_gemm(dh, self.w13, self.dcomb, 1, seg, self.el, rows_cap=R, N=d, K=2 * f, b_mn=True,
+                     scatter=(self.ret, self.p["dcomb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
+                              self.done[1:]))
+        dx = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
+        _lib.check_rc(lib.gf_moe_combine(self.dcomb.data_ptr(), None, None, dx.data_ptr(), T, k, d,
+                                         self.flags.data_ptr(), FLAG_COMBINE, ep, W, None, None, status, st()),
+                      "gf_moe_combine(dx)")
+        # router: weights -> probabilities -> logits (small [T, E] tensors)
+        dlogits = self._router_backward(ctx, dots)
+        dl = torch.zeros(T, self.gate_pad.shape[0], dtype=torch.bfloat16, device=dev)
+        dl[:, :E] = dlogits
+        raw.gemm(dl, False, self.gate_pad, False, out=dx, accumulate=True)
+        raw.gemm(dl, True, ctx.x, False, out=self.gate_grad_pad, accumulate=True)
+        return dx
+
+    @staticmethod
+    def _router_backward(ctx: MoEContext, dw: torch.Tensor) -> torch.Tensor:
+        p = ctx.probs
+        idx = ctx.idx.long()
+        psel = p.gather(1, idx)
+        s = psel.sum(1, keepdim=True)
+        wn = psel / s
+        dpsel = (dw - (dw * wn).sum(1, keepdim=True)) / s
+        dp = torch.zeros_like(p).scatter_(1, idx, dpsel)
+        return p * (dp - (dp * p).sum(1, keepdim=True))
+
+    # ------------------------------------------------------------------ statistics / auxiliary loss
+    def expert_counts(self) -> torch.Tensor:
+        """Tokens routed to every expert by this rank in the last forward."""
+        return self.last_counts
+
+    def aux_loss(self, ctx: MoEContext) -> torch.Tensor:
+        """Switch-style load-balance loss ``E * sum_e f_e * P_e``."""
+        frac = torch.bincount(ctx.idx.flatten().long(), minlength=self.E).float() / ctx.idx.numel()
+        return self.E * (frac * ctx.probs.mean(0)).sum()
+
+    # ------------------------------------------------------------------ CPU / oracle path
+    def full_weights(self):
+        """All experts' weights on every rank (for the dense oracle); all-gathers when sharded."""
+        if self.world == 1:
+            return self.w13, self.w2
+        w13 = torch.empty(self.E, 2 * self.f, self.d, dtype=self.w13.dtype, device=self.w13.device)
+        w2 = torch.empty(self.E, self.d, self.f, dtype=self.w2.dtype, device=self.w2.device)
+        dist.all_gather_into_tensor(w13, self.w13, group=self.group)
+        dist.all_gather_into_tensor(w2, self.w2, group=self.group)
+        return w13, w2
+
+    def dense_reference(self, x, w13=None, w2=None, residual=None):
+        """fp32 PyTorch restatement: every token through its top-k experts, differentiable."""
+        w13 = self.w13 if w13 is None else w13
+        w2 = self.w2 if w2 is None else w2
+        xf = x.float()
+        probs = torch.softmax(xf @ self.gate.float().t(), -1)
+        top, idx = probs.topk(self.k, -1)
+        wts = top / top.sum(-1, keepdim=True)
+        y = torch.zeros_like(xf)
+        for e in range(w13.shape[0]):
+            tok, slot = (idx == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            hh = xf[tok] @ w13[e].float().t()
+            g, u = hh.chunk(2, -1)
+            out = (torch.nn.functional.silu(g) * u) @ w2[e].float().t()
+            y.index_add_(0, tok, out * wts[tok, slot, None])
+        if residual is not None:
+            y = y + residual.float()
+        return y
+
+    def _forward_ref(self, x, residual):
+        assert self.world == 1, "the CPU path holds all experts in one process"
+        xr = x.detach().clone().requires_grad_(True)
+        leaves = [self.gate, self.w13, self.w2]
+        for t in leaves:
+            t.requires_grad_(True)
+        y = self.dense_reference(xr, residual=residual)
+        return y.to(x.dtype).detach(), (xr, y)
+
+    def _backward_ref(self, ctx, dy):
+        xr, y = ctx
+        gx, gg, g13, g2 = torch.autograd.grad(y, [xr, self.gate, self.w13, self.w2], dy.float())
+        self.grads["gate"] += gg.to(self.gate.dtype)
+        self.grads["w13"] += g13.to(self.w13.dtype)
+        self.grads["w2"] += g2.to(self.w2.dtype)
+        for t in (self.gate, self.w13, self.w2):
+            t.requires_grad_(False)
+        return gx.to(dy.dtype)
+
+    # ------------------------------------------------------------------ autograd wrapper
+    def apply(self, x: torch.Tensor) -> torch.Tensor:
+        """Differentiable call for use inside a torch model (weight gradients land in ``self.grads``)."""
+        return _MoEFn.apply(x, self)
+
+
+class _MoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, layer):
+        y, c = layer.forward(x)
+        ctx.layer, ctx.c = layer, c
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        return ctx.layer.backward(ctx.c, dy), None
