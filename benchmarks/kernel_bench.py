@@ -53,6 +53,20 @@ def build(args, dev):
         b = torch.randn(N, K, device=dev, dtype=bf)
         out = torch.empty(M, N, device=dev, dtype=bf)
         return (lambda: torch.matmul(a, b.t(), out=out)), 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    if k in ("gemm_fp8_rowcol", "gemm_fp8_block"):
+        from ghost_flow_b200.ops import fp8
+        M, N, K = args.m, args.n, args.k
+        mode = 0 if k == "gemm_fp8_rowcol" else 1
+        a = torch.randn(M, K, device=dev, dtype=bf)
+        b = torch.randn(N, K, device=dev, dtype=bf)
+        aq, sa = fp8.quantize_rows(a, mode)
+        bq, sb = fp8.quantize_rows(b, 0) if mode == 0 else fp8.quantize_block128(b)
+        out = torch.empty(M, N, device=dev, dtype=bf)
+        return (lambda: fp8.gemm_fp8(aq, sa, bq, sb, mode, out=out)), 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    if k == "quant_fp8_rows":
+        from ghost_flow_b200.ops import fp8
+        x = torch.randn(args.rows, args.cols, device=dev, dtype=bf)
+        return (lambda: fp8.quantize_rows(x, 1)), 0.0, 3.0 * args.rows * args.cols
     if k in ("attn_fwd", "attn_bwd"):
         B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads or args.heads, args.dim
         q = torch.randn(B * S, H * D, device=dev, dtype=bf)
