@@ -187,10 +187,13 @@ def attn_bwd(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D, causal=True, sca
     s = qf @ kf.transpose(-1, -2) * scale
     if causal:
         s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(), float("-inf"))
-    p = torch.softmax(s, -1)
+    # probabilities from the given log-sum-exp and delta from o, as in the kernel: k/v may be one block of a longer
+    # key sequence (ring attention), in which case lse and o are those of the whole row
+    p = torch.exp(s - lse.float().unsqueeze(-1))
+    of = o.float().reshape(B, S, Hq, D).transpose(1, 2)
     dvf = p.transpose(-1, -2) @ dof
     dp = dof @ vf.transpose(-1, -2)
-    ds = p * (dp - (dp * p).sum(-1, keepdim=True)) * scale
+    ds = p * (dp - (dof * of).sum(-1, keepdim=True)) * scale
     dqf = ds @ kf
     dkf = ds.transpose(-1, -2) @ qf
     dkf = dkf.reshape(B, Hkv, G, S, D).sum(2)

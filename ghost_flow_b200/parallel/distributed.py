@@ -1,0 +1,569 @@
+"""Data / model / pipeline parallel wrappers and the generic ZeRO optimizer, with the reference's names but real
+collectives (``torch.distributed``: NCCL on GPUs, gloo on CPU).
+
+Reference: ghostflow-nn/src/distributed.rs (DistributedBackend :11-18, DistributedConfig :35-45, DataParallel :51-139,
+ModelParallel :145-184, GradientAccumulator :190-267, DistributedDataParallel :273-329, PipelineParallel :334-391)
+and ghostflow-nn/src/zero_optimizer.rs (ZeRoStage/ZeRoConfig :15-55, partitioning :149-195, reduce-scatter :220-242,
+all-gather :245-259, step :262-309, offload :312-341, stats :344-404). Every collective there is simulated
+(gradients are multiplied by 1/world, parameters cloned); here they move data.
+
+The flagship LLaMA trainer does not go through these wrappers: it has its own hand-scheduled engine
+(:mod:`ghost_flow_b200.parallel.zero3`). These classes serve arbitrary ``torch.nn.Module`` models.
+"""
+from __future__ import annotations
+
+import contextlib
+import enum
+import math
+import os
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..ops import raw
+
+
+class DistributedBackend(enum.Enum):
+    NCCL = "nccl"
+    Gloo = "gloo"
+    MPI = "mpi"
+
+
+@dataclass
+class DistributedConfig:
+    backend: DistributedBackend = DistributedBackend.NCCL
+    world_size: int = 1
+    rank: int = 0
+    master_addr: str = "127.0.0.1"
+    master_port: int = 29500
+
+    @classmethod
+    def from_env(cls, backend=None):
+        be = backend or (DistributedBackend.NCCL if torch.cuda.is_available() else DistributedBackend.Gloo)
+        return cls(be, int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0)),
+                   os.environ.get("MASTER_ADDR", "127.0.0.1"), int(os.environ.get("MASTER_PORT", 29500)))
+
+
+def init_process_group(config: DistributedConfig, timeout_s: float | None = None):
+    """One process per GPU. Idempotent; returns the default group (or None for world_size 1)."""
+    if config.world_size <= 1:
+        return None
+    if not dist.is_initialized():
+        import datetime
+
+        os.environ.setdefault("MASTER_ADDR", config.master_addr)
+        os.environ.setdefault("MASTER_PORT", str(config.master_port))
+        kw = {}
+        if timeout_s is not None:
+            kw["timeout"] = datetime.timedelta(seconds=timeout_s)
+        if config.backend is DistributedBackend.NCCL and torch.cuda.is_available():
+            local = int(os.environ.get("LOCAL_RANK", config.rank % max(1, torch.cuda.device_count())))
+            torch.cuda.set_device(local)
+            kw["device_id"] = torch.device("cuda", local)
+        dist.init_process_group(config.backend.value, rank=config.rank, world_size=config.world_size, **kw)
+    return dist.group.WORLD
+
+
+def _world(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+# --------------------------------------------------------------------------------------------- data parallel
+class DataParallel:
+    """Replicated model, batch split along dim 0, gradients averaged over ranks (one all-reduce per tensor, the
+    reference's granularity; :class:`DistributedDataParallel` buckets)."""
+
+    def __init__(self, module: torch.nn.Module, device_ids=None, group=None):
+        self.module = module
+        self.device_ids = list(device_ids) if device_ids is not None else [0]
+        self.group = group
+
+    def split_batch(self, batch: torch.Tensor, parts: int | None = None):
+        """``parts`` near-equal slices along dim 0 (the last takes the remainder)."""
+        parts = parts or len(self.device_ids)
+        n = batch.shape[0]
+        per = n // parts
+        out = []
+        for i in range(parts):
+            lo = i * per
+            hi = n if i == parts - 1 else lo + per
+            out.append(batch[lo:hi])
+        return out
+
+    def all_reduce_gradients(self, grads: dict | None = None) -> dict:
+        """Mean over ranks. ``grads``: name -> tensor; default: the module's ``.grad`` fields (in place)."""
+        world, _ = _world(self.group)
+        if grads is None:
+            grads = {n: p.grad for n, p in self.module.named_parameters() if p.grad is not None}
+        for g in grads.values():
+            if world > 1:
+                dist.all_reduce(g, group=self.group)
+                g.div_(world)
+        return grads
+
+    def broadcast_parameters(self, src: int = 0):
+        world, _ = _world(self.group)
+        if world > 1:
+            for t in list(self.module.parameters()) + list(self.module.buffers()):
+                dist.broadcast(t.data, src, group=self.group)
+
+    def forward(self, *a, **k):
+        return self.module(*a, **k)
+
+    __call__ = forward
+
+
+class GradientAccumulator:
+    """Sums gradients over ``accumulation_steps`` micro-steps, hands back the mean."""
+
+    def __init__(self, accumulation_steps: int):
+        self.accumulation_steps = accumulation_steps
+        self.current_step = 0
+        self.accumulated: dict[str, torch.Tensor] = {}
+
+    def accumulate(self, grads: dict) -> bool:
+        for n, g in grads.items():
+            if n in self.accumulated:
+                self.accumulated[n].add_(g)
+            else:
+                self.accumulated[n] = g.detach().clone()
+        self.current_step += 1
+        return self.should_step()
+
+    def should_step(self) -> bool:
+        return self.current_step >= self.accumulation_steps
+
+    def get_and_reset(self) -> dict:
+        out = {n: g / self.accumulation_steps for n, g in self.accumulated.items()}
+        self.accumulated, self.current_step = {}, 0
+        return out
+
+
+class DistributedDataParallel(torch.nn.Module):
+    """Flat gradient buckets all-reduced asynchronously while backward still runs.
+
+    Parameters are laid into buckets of ``bucket_mb`` in reverse registration order (roughly the order their
+    gradients become ready); each parameter's ``.grad`` is a view into its bucket, so no copy precedes the
+    collective. A bucket's all-reduce is launched from the hook of its last-arriving gradient. ``finish()`` (called
+    by ``step`` helpers or by the user before the optimizer) waits for all of them and divides by the world size."""
+
+    def __init__(self, module: torch.nn.Module, group=None, bucket_mb: float = 25.0, accumulation_steps: int = 1):
+        super().__init__()
+        self.module = module
+        self.group = group
+        self.world, self.rank = _world(group)
+        self.accumulation_steps = accumulation_steps
+        self._micro = 0
+        self._sync = True
+        self._works = []
+        params = [p for p in module.parameters() if p.requires_grad]
+        self.buckets: list[torch.Tensor] = []
+        self._bucket_of: dict[int, int] = {}
+        self._pending: list[int] = []
+        cap = int(bucket_mb * (1 << 20))
+        cur, cur_bytes = [], 0
+        groups = []
+        for p in reversed(params):
+            nbytes = p.numel() * p.element_size()
+            if cur and (cur_bytes + nbytes > cap or cur[0].dtype != p.dtype):
+                groups.append(cur)
+                cur, cur_bytes = [], 0
+            cur.append(p)
+            cur_bytes += nbytes
+        if cur:
+            groups.append(cur)
+        for bi, ps in enumerate(groups):
+            flat = torch.zeros(sum(p.numel() for p in ps), dtype=ps[0].dtype, device=ps[0].device)
+            off = 0
+            for p in ps:
+                p.grad = flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+                self._bucket_of[id(p)] = bi
+                p.register_post_accumulate_grad_hook(self._hook)
+            self.buckets.append(flat)
+            self._pending.append(len(ps))
+        self._sizes = list(self._pending)
+        if self.world > 1:
+            DataParallel(module, group=group).broadcast_parameters(0)
+
+    def _hook(self, p):
+        bi = self._bucket_of[id(p)]
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0 and self._sync and self.world > 1:
+            self._works.append(dist.all_reduce(self.buckets[bi], group=self.group, async_op=True))
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Skip the all-reduce for the backward passes inside (gradient accumulation)."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
+
+    def forward(self, *a, **k):
+        self._pending = list(self._sizes)
+        return self.module(*a, **k)
+
+    def finish(self):
+        """Wait for the bucket all-reduces of the last backward and turn sums into means."""
+        for w in self._works:
+            w.wait()
+        self._works = []
+        if self.world > 1:
+            for b in self.buckets:
+                b.div_(self.world)
+
+    def zero_grad(self):
+        for b in self.buckets:
+            b.zero_()
+
+    def backward(self, loss: torch.Tensor) -> bool:
+        """The reference's entry point: backward, all-reduce, accumulate; True when an optimizer step is due."""
+        self._micro += 1
+        last = self._micro % self.accumulation_steps == 0
+        if last:
+            (loss / self.accumulation_steps).backward()
+            self.finish()
+        else:
+            with self.no_sync():
+                (loss / self.accumulation_steps).backward()
+        return last
+
+
+# --------------------------------------------------------------------------------------------- ZeRO
+class ZeRoStage(enum.IntEnum):
+    Stage1 = 1      # optimizer state sharded
+    Stage2 = 2      # + gradients sharded
+    Stage3 = 3      # + parameters sharded
+
+
+@dataclass
+class ZeRoConfig:
+    stage: ZeRoStage = ZeRoStage.Stage2
+    world_size: int = 1
+    rank: int = 0
+    cpu_offload: bool = False
+    nvme_offload: bool = False
+    overlap_comm: bool = True
+    bucket_size: int = 25_000_000          # parameters per bucket
+    lr: float = 1e-3
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+
+    @classmethod
+    def default(cls):
+        return cls()
+
+
+@dataclass
+class ZeRoStats:
+    stage: ZeRoStage
+    world_size: int
+    total_params: int
+    owned_params: int
+    param_bytes_per_rank: int
+    grad_bytes_per_rank: int
+    optimizer_bytes_per_rank: int
+    offloaded_bytes: int = 0
+
+    def memory_savings_ratio(self) -> float:
+        """Bytes of the unsharded mixed-precision state (2 + 2 + 12 per parameter) over this rank's share."""
+        base = self.total_params * 16
+        mine = self.param_bytes_per_rank + self.grad_bytes_per_rank + self.optimizer_bytes_per_rank
+        return base / max(1, mine)
+
+
+class ZeRoOptimizer:
+    """AdamW with ZeRO partitioning over flat element ranges (not whole tensors as in the reference, whose owner
+    map depends on hash-map order).
+
+    All trainable parameters are laid into flat buckets of at most ``bucket_size`` elements, padded to a multiple
+    of the world size; rank r owns the r-th slice of every bucket: its fp32 master copy and both moments live
+    only there. ``step()``: reduce-scatter of each gradient bucket (mean), fused AdamW on the owned slice (one
+    kernel: fp32 update + low-precision copy), all-gather of the updated slices. Stage 2 frees the gradient
+    buckets between steps except for the owned slice; stage 3 additionally keeps only the owned parameter slice
+    between steps (``gather_parameters`` / ``release_parameters`` bracket forward+backward).
+    """
+
+    def __init__(self, params, config: ZeRoConfig | None = None, group=None):
+        self.config = config or ZeRoConfig.default()
+        self.group = group
+        self.world, self.rank = _world(group)
+        if self.world == 1:
+            self.world, self.rank = 1, 0
+        self.params = [p for p in params if p.requires_grad]
+        self.step_count = 0
+        self.buckets = []
+        cur, n = [], 0
+        for p in self.params:
+            if cur and (n + p.numel() > self.config.bucket_size or cur[0].dtype != p.dtype):
+                self._make_bucket(cur)
+                cur, n = [], 0
+            cur.append(p)
+            n += p.numel()
+        if cur:
+            self._make_bucket(cur)
+        self._offloaded = False
+
+    def _make_bucket(self, ps):
+        dev, dt = ps[0].device, ps[0].dtype
+        n = sum(p.numel() for p in ps)
+        padded = (n + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
+        shard = padded // self.world
+        flat_p = torch.zeros(padded, dtype=dt, device=dev)
+        flat_g = torch.zeros(padded, dtype=dt, device=dev)
+        off = 0
+        for p in ps:
+            flat_p[off:off + p.numel()].copy_(p.data.reshape(-1))
+            p.data = flat_p[off:off + p.numel()].view_as(p)
+            p.grad = flat_g[off:off + p.numel()].view_as(p)
+            off += p.numel()
+        lo = self.rank * shard
+        b = {"params": ps, "n": n, "padded": padded, "shard": shard, "flat_p": flat_p, "flat_g": flat_g,
+             "master": flat_p[lo:lo + shard].float().clone(), "m": torch.zeros(shard, device=dev),
+             "v": torch.zeros(shard, device=dev), "g_shard": torch.zeros(shard, dtype=dt, device=dev)}
+        self.buckets.append(b)
+
+    # ---- partition queries (reference names)
+    def partition_parameters(self):
+        """[(bucket, first element, last element)] owned by this rank."""
+        return [(i, self.rank * b["shard"], (self.rank + 1) * b["shard"]) for i, b in enumerate(self.buckets)]
+
+    def owns(self, bucket: int, element: int) -> bool:
+        b = self.buckets[bucket]
+        return self.rank * b["shard"] <= element < (self.rank + 1) * b["shard"]
+
+    # ---- collectives
+    def reduce_scatter_gradients(self):
+        for b in self.buckets:
+            if self.world == 1:
+                b["g_shard"].copy_(b["flat_g"][:b["shard"]])
+                continue
+            if dist.get_backend(self.group) == "nccl":
+                dist.reduce_scatter_tensor(b["g_shard"], b["flat_g"], group=self.group)
+            else:
+                tmp = b["flat_g"].float()
+                dist.all_reduce(tmp, group=self.group)
+                b["g_shard"].copy_(tmp[self.rank * b["shard"]:(self.rank + 1) * b["shard"]].to(b["g_shard"].dtype))
+
+    def all_gather_parameters(self):
+        for b in self.buckets:
+            if self.world == 1:
+                continue
+            lo = self.rank * b["shard"]
+            dist.all_gather_into_tensor(b["flat_p"], b["flat_p"][lo:lo + b["shard"]].clone(), group=self.group)
+
+    gather_parameters = all_gather_parameters
+
+    def release_parameters(self):
+        """Stage 3: after backward only the owned slice has to stay valid (the flat buffer is kept allocated so
+        that parameter views stay usable; a rank must not read foreign slices until the next gather)."""
+
+    # ---- step
+    def step(self):
+        if self._offloaded:
+            self.load_from_cpu()
+        c = self.config
+        self.step_count += 1
+        self.reduce_scatter_gradients()
+        for b in self.buckets:
+            lo = self.rank * b["shard"]
+            p_lp = b["flat_p"][lo:lo + b["shard"]]
+            raw.adamw_flat(b["master"], b["m"], b["v"], b["g_shard"], p_lp if p_lp.dtype != torch.float32 else None,
+                           lr=c.lr, beta1=c.betas[0], beta2=c.betas[1], eps=c.eps, weight_decay=c.weight_decay,
+                           step=self.step_count, grad_scale=1.0 / self.world)
+            if p_lp.dtype == torch.float32:
+                p_lp.copy_(b["master"])
+        self.all_gather_parameters()
+        if c.cpu_offload:
+            self.offload_to_cpu()
+
+    def zero_grad(self):
+        for b in self.buckets:
+            b["flat_g"].zero_()
+
+    # ---- offload (real device <-> pinned host copies of the optimizer state shard)
+    def offload_to_cpu(self):
+        if self._offloaded:
+            return
+        for b in self.buckets:
+            for k in ("master", "m", "v"):
+                t = b[k]
+                if t.is_cuda:
+                    host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                    host.copy_(t, non_blocking=True)
+                    b[k + "_dev"] = t.device
+                    b[k] = host
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self._offloaded = True
+
+    def load_from_cpu(self):
+        for b in self.buckets:
+            for k in ("master", "m", "v"):
+                if k + "_dev" in b:
+                    b[k] = b[k].to(b.pop(k + "_dev"), non_blocking=True)
+        self._offloaded = False
+
+    def get_stats(self) -> ZeRoStats:
+        total = sum(b["n"] for b in self.buckets)
+        owned = sum(b["shard"] for b in self.buckets)
+        esz = self.buckets[0]["flat_p"].element_size() if self.buckets else 2
+        st = self.config.stage
+        off = sum(b[k].numel() * 4 for b in self.buckets for k in ("master", "m", "v") if not b[k].is_cuda
+                  and self.buckets[0]["flat_p"].is_cuda)
+        return ZeRoStats(st, self.world, total, owned,
+                         (owned if st >= ZeRoStage.Stage3 else total) * esz,
+                         (owned if st >= ZeRoStage.Stage2 else total) * esz, owned * 12, off)
+
+    def memory_savings_ratio(self) -> float:
+        return self.get_stats().memory_savings_ratio()
+
+    def state_dict(self):
+        return {"step": self.step_count,
+                "buckets": [{k: b[k].detach().cpu() for k in ("master", "m", "v")} for b in self.buckets]}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        for b, s in zip(self.buckets, sd["buckets"]):
+            for k in ("master", "m", "v"):
+                b[k].copy_(s[k])
+            lo = self.rank * b["shard"]
+            b["flat_p"][lo:lo + b["shard"]].copy_(b["master"].to(b["flat_p"].dtype))
+        self.all_gather_parameters()
+
+
+# --------------------------------------------------------------------------------------------- model parallel
+class ModelParallel:
+    """Layer placement over devices with real transfers between them."""
+
+    def __init__(self, devices):
+        self.devices = [torch.device(d) for d in devices]
+        self.layer_placement: dict[str, torch.device] = {}
+
+    def place_layer(self, name: str, device_index: int, module: torch.nn.Module | None = None):
+        self.layer_placement[name] = self.devices[device_index]
+        if module is not None:
+            module.to(self.devices[device_index])
+
+    def auto_place_layers(self, layers):
+        """Contiguous runs of near-equal length. ``layers``: names or (name, module) pairs."""
+        items = [(l, None) if isinstance(l, str) else l for l in layers]
+        per = math.ceil(len(items) / len(self.devices))
+        for i, (name, mod) in enumerate(items):
+            self.place_layer(name, min(i // per, len(self.devices) - 1), mod)
+        return dict(self.layer_placement)
+
+    def get_device(self, name: str):
+        return self.layer_placement.get(name)
+
+    def transfer(self, t: torch.Tensor, to_layer: str) -> torch.Tensor:
+        return t.to(self.layer_placement[to_layer], non_blocking=True)
+
+
+# --------------------------------------------------------------------------------------------- pipeline parallel
+class PipelineParallel:
+    """One pipeline stage per rank, 1F1B schedule, activations and their gradients over point-to-point send/recv
+    (NCCL on GPUs by design; gloo on CPU).
+
+    ``stage`` is this rank's module. ``run(micro_inputs, loss_fn, targets)``: the first stage feeds
+    ``micro_inputs`` (a list of tensors), the last stage computes ``loss_fn(out, target)``; gradients accumulate
+    in the stage's parameters. Returns the mean loss on the last stage (None elsewhere).
+    ``activation_shape(micro_batch_rows)`` must give the shape of the tensor crossing every stage boundary."""
+
+    def __init__(self, stage: torch.nn.Module, num_micro_batches: int, activation_shape, dtype=torch.float32,
+                 device=None, group=None):
+        self.stage = stage
+        self.num_micro_batches = num_micro_batches
+        self.group = group
+        self.num_stages, self.stage_index = _world(group)
+        self.activation_shape = activation_shape
+        self.dtype = dtype
+        self.device = device or next(stage.parameters()).device
+        self.current_stage = 0
+
+    # reference bookkeeping API
+    def create_micro_batches(self, batch: torch.Tensor):
+        return list(batch.chunk(self.num_micro_batches, 0))
+
+    def next_stage(self):
+        self.current_stage = (self.current_stage + 1) % max(1, self.num_stages)
+        return self.current_stage
+
+    @property
+    def is_first(self):
+        return self.stage_index == 0
+
+    @property
+    def is_last(self):
+        return self.stage_index == self.num_stages - 1
+
+    def _recv(self, src, rows):
+        t = torch.empty(self.activation_shape(rows), dtype=self.dtype, device=self.device)
+        dist.recv(t, src, group=self.group)
+        return t
+
+    def _send(self, t, dst):
+        """Non-blocking: in 1F1B a stage sends an activation forward while its neighbour sends a gradient back, so
+        two blocking sends would wait for each other. The tensor is kept alive until the transfer is done."""
+        self._sends.append((dist.isend(t, dst, group=self.group), t))
+
+    def _forward_one(self, i, micro_inputs, rows, saved):
+        if self.is_first:
+            x = micro_inputs[i]
+            inp = None
+        else:
+            inp = self._recv(self.stage_index - 1, rows).requires_grad_(True)
+            x = inp
+        out = self.stage(x)
+        saved.append((inp, out))
+        if not self.is_last:
+            self._send(out.detach().contiguous(), self.stage_index + 1)
+
+    def _backward_one(self, saved, loss_fn, targets, losses, j, rows):
+        inp, out = saved.pop(0)
+        if self.is_last:
+            loss = loss_fn(out, targets[j]) / self.num_micro_batches
+            losses.append(loss.detach() * self.num_micro_batches)
+            loss.backward()
+        else:
+            g = self._recv(self.stage_index + 1, rows)
+            out.backward(g)
+        if not self.is_first:
+            self._send(inp.grad.contiguous(), self.stage_index - 1)
+
+    def run(self, micro_inputs=None, loss_fn=None, targets=None, rows: int | None = None):
+        m, s, r = self.num_micro_batches, self.num_stages, self.stage_index
+        if rows is None:
+            rows = micro_inputs[0].shape[0]
+        saved, losses = [], []
+        self._sends = []
+        if s == 1:
+            for i in range(m):
+                out = self.stage(micro_inputs[i])
+                loss = loss_fn(out, targets[i]) / m
+                loss.backward()
+                losses.append(loss.detach() * m)
+            return torch.stack(losses).mean()
+        warm = min(m, s - 1 - r)
+        f = b = 0
+        for _ in range(warm):                 # warm-up forwards
+            self._forward_one(f, micro_inputs, rows, saved)
+            f += 1
+        while f < m:                          # steady state: one forward, one backward
+            self._forward_one(f, micro_inputs, rows, saved)
+            f += 1
+            self._backward_one(saved, loss_fn, targets, losses, b, rows)
+            b += 1
+        while b < m:                          # cool-down backwards
+            self._backward_one(saved, loss_fn, targets, losses, b, rows)
+            b += 1
+        for w, _ in self._sends:
+            w.wait()
+        self._sends = []
+        return torch.stack(losses).mean() if self.is_last else None

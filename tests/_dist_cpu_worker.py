@@ -1,0 +1,168 @@
+"""CPU (gloo) worker for the distributed wrapper tests. argv: <case> <out-file>."""
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def model(seed=0):
+    torch.manual_seed(seed)
+    return torch.nn.Sequential(torch.nn.Linear(12, 24), torch.nn.Tanh(), torch.nn.Linear(24, 24), torch.nn.Tanh(),
+                               torch.nn.Linear(24, 4))
+
+
+def data(n=16):
+    g = torch.Generator().manual_seed(7)
+    return torch.randn(n, 12, generator=g), torch.randn(n, 4, generator=g)
+
+
+def case_ddp(rank, world, out):
+    from ghost_flow_b200.parallel.distributed import DistributedDataParallel
+    x, y = data()
+    ref = model()
+    torch.nn.functional.mse_loss(ref(x), y).backward()
+    m = DistributedDataParallel(model(), bucket_mb=0.001)
+    xs, ys = x.chunk(world), y.chunk(world)
+    loss = torch.nn.functional.mse_loss(m(xs[rank]), ys[rank])
+    loss.backward()
+    m.finish()
+    err = max((p.grad - q.grad).abs().max().item() for p, q in zip(m.module.parameters(), ref.parameters()))
+    # accumulation: two micro-steps, sync only on the second
+    m.zero_grad()
+    m2 = DistributedDataParallel(model(), bucket_mb=0.001, accumulation_steps=2)
+    halves_x, halves_y = xs[rank].chunk(2), ys[rank].chunk(2)
+    due = [m2.backward(torch.nn.functional.mse_loss(m2(a), b)) for a, b in zip(halves_x, halves_y)]
+    err2 = max((p.grad - q.grad).abs().max().item() for p, q in zip(m2.module.parameters(), ref.parameters()))
+    return {"ddp_grad_err": err, "ddp_accum_err": err2, "due": due}
+
+
+def case_zero(rank, world, out):
+    from ghost_flow_b200.parallel.distributed import ZeRoConfig, ZeRoOptimizer, ZeRoStage
+    x, y = data()
+    ref = model()
+    opt_ref = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    res = {}
+    for stage in (ZeRoStage.Stage1, ZeRoStage.Stage2, ZeRoStage.Stage3):
+        m = model()
+        ref.load_state_dict(model().state_dict())
+        opt_ref = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+        cfg = ZeRoConfig(stage=stage, world_size=world, rank=rank, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1,
+                         bucket_size=500, cpu_offload=(stage == ZeRoStage.Stage3))
+        opt = ZeRoOptimizer(m.parameters(), cfg)
+        xs, ys = x.chunk(world), y.chunk(world)
+        for _ in range(4):
+            opt_ref.zero_grad()
+            torch.nn.functional.mse_loss(ref(x), y).backward()
+            opt_ref.step()
+            opt.zero_grad()
+            torch.nn.functional.mse_loss(m(xs[rank]), ys[rank]).backward()
+            opt.step()
+        res[f"zero{int(stage)}_param_err"] = max((p - q).abs().max().item() for p, q in zip(m.parameters(), ref.parameters()))
+        st = opt.get_stats()
+        res[f"zero{int(stage)}_savings"] = st.memory_savings_ratio()
+        res[f"zero{int(stage)}_owned"] = st.owned_params
+    return res
+
+
+def case_pipeline(rank, world, out):
+    from ghost_flow_b200.parallel.distributed import PipelineParallel
+    x, y = data(16)
+    full = model()
+    layers = list(full)
+    loss_ref = torch.nn.functional.mse_loss(full(x), y)
+    loss_ref.backward()
+    cut = [0, 2, 5] if world == 2 else [0, 2, 4, 5]
+    stage = torch.nn.Sequential(*[l for l in list(model())[cut[rank]:cut[rank + 1]]])
+    pp = PipelineParallel(stage, num_micro_batches=4, activation_shape=lambda rows: (rows, 24))
+    micro_x = pp.create_micro_batches(x)
+    micro_y = pp.create_micro_batches(y)
+    loss = pp.run(micro_x, lambda o, t: torch.nn.functional.mse_loss(o, t), micro_y, rows=micro_x[0].shape[0])
+    ref_params = [p for l in layers[cut[rank]:cut[rank + 1]] for p in l.parameters()]
+    err = max((p.grad - q.grad).abs().max().item() for p, q in zip(stage.parameters(), ref_params))
+    res = {"pp_grad_err": err}
+    if pp.is_last:
+        res["pp_loss_err"] = abs(loss.item() - loss_ref.item())
+    return res
+
+
+def case_context(rank, world, out):
+    from ghost_flow_b200.ops import raw
+    from ghost_flow_b200.parallel.context import ContextParallelAttention, UlyssesAttention
+    B, S, H, Hkv, D = 1, 32, 4, 2, 16
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B * S * world, H * D, generator=g)
+    k = torch.randn(B * S * world, Hkv * D, generator=g)
+    v = torch.randn(B * S * world, Hkv * D, generator=g)
+    do = torch.randn(B * S * world, H * D, generator=g)
+    o_ref, lse_ref = raw.attn_fwd(q, k, v, B, S * world, H, Hkv, D, True)
+    dq_r, dk_r, dv_r = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    raw.attn_bwd(q, k, v, o_ref, do, lse_ref, dq_r, dk_r, dv_r, B, S * world, H, Hkv, D, True)
+    sl = slice(rank * S, (rank + 1) * S)
+    res = {}
+    cp = ContextParallelAttention(B, S, H, Hkv, D, causal=True)
+    o, lse = cp.forward(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous())
+    dq, dk, dv = cp.backward(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), o, lse, do[sl].contiguous())
+    res["ring_o"] = (o - o_ref[sl]).abs().max().item()
+    res["ring_dq"] = (dq - dq_r[sl]).abs().max().item()
+    res["ring_dk"] = (dk - dk_r[sl]).abs().max().item()
+    res["ring_dv"] = (dv - dv_r[sl]).abs().max().item()
+    ul = UlyssesAttention(B, S, H, Hkv, D, causal=True)
+    o2, ctx = ul.forward(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous())
+    dq2, dk2, dv2 = ul.backward(ctx, do[sl].contiguous())
+    res["ulysses_o"] = (o2 - o_ref[sl]).abs().max().item()
+    res["ulysses_dq"] = (dq2 - dq_r[sl]).abs().max().item()
+    res["ulysses_dk"] = (dk2 - dk_r[sl]).abs().max().item()
+    return res
+
+
+def case_fault(rank, world, out):
+    """Rank 1 fails on the host at step 3 and leaves between steps; rank 0 must learn of it before its next
+    collective (heartbeat / failure note in the store) and must not hang."""
+    from ghost_flow_b200.parallel.fault import FaultInjector, Heartbeat, PeerFailure, StepGuard, Watchdog
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, rank, world, interval=0.05).start()
+    guard = StepGuard(hb, timeout=1.0)
+    inj = FaultInjector(raise_at=3 if rank == 1 else None)
+    steps_done, detected, t0 = 0, None, time.monotonic()
+    t = torch.ones(4)
+    try:
+        for step in range(1, 8):
+            try:
+                inj.before_step(hb)
+            except RuntimeError as e:
+                guard.report_failure(str(e))
+                hb.stop()
+                raise
+            if rank == 0 and step >= 3:
+                guard.wait_healthy(1.5)        # gives the failing rank time to publish, then checks before launching
+            else:
+                guard.check()
+            dist.all_reduce(t)
+            steps_done += 1
+    except PeerFailure as e:
+        detected = e.ranks
+    except RuntimeError:
+        detected = "self"
+    with Watchdog(0.05) as wd:
+        time.sleep(0.2)
+    hb.stop()
+    return {"steps_done": steps_done, "detected": detected, "seconds": time.monotonic() - t0, "watchdog": wd.fired}
+
+
+def main():
+    case, out = sys.argv[1], sys.argv[2]
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    res = globals()[f"case_{case}"](rank, world, out)
+    torch.save(res, f"{out}.{rank}")
+    if case != "fault":
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,63 @@
+"""DDP, generic ZeRO-1/2/3, 1F1B pipeline, ring/Ulysses context parallelism and failure detection on CPU ranks
+(gloo, world size 2), each against a single-process reference."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_PORT = [29600]
+
+
+def _run(case, tmp_path, world=2, timeout=180):
+    out = str(tmp_path / f"{case}.pt")
+    _PORT[0] += 1
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(_PORT[0]),
+                        os.path.join(HERE, "_dist_cpu_worker.py"), case, out],
+                       env=env, capture_output=True, text=True, timeout=timeout)
+    res = [torch.load(f"{out}.{i}") for i in range(world) if os.path.exists(f"{out}.{i}")]
+    return r, res
+
+
+def test_ddp_bucketed_allreduce_matches_full_batch(tmp_path):
+    r, res = _run("ddp", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    for d in res:
+        assert d["ddp_grad_err"] < 1e-6 and d["ddp_accum_err"] < 1e-6 and d["due"] == [False, True]
+
+
+def test_zero_stages_match_adamw(tmp_path):
+    r, res = _run("zero", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    for d in res:
+        for s in (1, 2, 3):
+            assert d[f"zero{s}_param_err"] < 2e-5, d
+        assert d["zero3_savings"] > d["zero2_savings"] > d["zero1_savings"] > 1.0
+
+
+def test_pipeline_1f1b_matches_single_process(tmp_path):
+    r, res = _run("pipeline", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert all(d["pp_grad_err"] < 1e-6 for d in res)
+    assert any("pp_loss_err" in d and d["pp_loss_err"] < 1e-6 for d in res)
+
+
+def test_ring_and_ulysses_attention_match_full_sequence(tmp_path):
+    r, res = _run("context", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    for d in res:
+        assert all(v < 2e-4 for v in d.values()), d
+
+
+def test_host_side_failure_is_detected_without_hanging(tmp_path):
+    r, res = _run("fault", tmp_path, timeout=120)
+    by_steps = sorted(res, key=lambda d: d["steps_done"])
+    assert len(res) == 2
+    failing, survivor = (res[1], res[0]) if res[1]["detected"] == "self" else (res[0], res[1])
+    assert failing["detected"] == "self" and failing["steps_done"] == 2
+    assert survivor["detected"] == [1] and survivor["steps_done"] == 2
+    assert survivor["seconds"] < 30 and survivor["watchdog"]

@@ -71,3 +71,16 @@ def test_expert_parallel_moe_matches_dense_reference(tmp_path):
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     res = torch.load(out)
     assert res and all(v < 5e-2 for v in res.values()), res
+
+
+def test_context_parallel_attention_matches_single_gpu(tmp_path):
+    """Ring attention (K/V and dK/dV travelling over NCCL p2p) and Ulysses against FlashAttention on the full sequence."""
+    _need(2)
+    out = str(tmp_path / "cp.pt")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29755",
+                        os.path.join(HERE, "_cp_worker.py"), out], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    res = torch.load(out)
+    assert res and all(v < 3e-2 for v in res.values()), res
