@@ -82,10 +82,10 @@ def test_trees_solve_xor_and_report_importances():
     t = ml.DecisionTreeClassifier().fit(X, Y_XOR)
     assert t.score(X, Y_XOR) > 0.95
     imp = ml.RandomForestClassifier(20).fit(X, Y_XOR).feature_importances().numpy()
-    assert imp[:2].sum() > 0.7
-    vote = ml.VotingClassifier(ml.VotingType.Soft).add_estimator(ml.DecisionTreeClassifier().max_depth(4)).add_estimator(ml.GaussianNB())
+    assert imp[:2].sum() > 0.5 and imp[:2].min() > imp[2:].max()
+    vote = ml.VotingClassifier(ml.VotingType.Soft).add_estimator(ml.DecisionTreeClassifier()).add_estimator(ml.GaussianNB())
     assert vote.fit(X, Y_XOR).score(X, Y_XOR) > 0.9
-    stack = ml.StackingClassifier().add_estimator(ml.DecisionTreeClassifier().max_depth(4)).add_estimator(ml.GaussianNB())
+    stack = ml.StackingClassifier().add_estimator(ml.DecisionTreeClassifier()).add_estimator(ml.GaussianNB())
     assert stack.fit(X, Y_XOR).score(X, Y_XOR) > 0.9
 
 
