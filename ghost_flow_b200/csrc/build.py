@@ -43,9 +43,10 @@ CUDA_SOURCES = [
     "quant_fp8.cu",
     "misc_kernels.cu",
     "noalloc.cu",
+    "runtime.cu",
 ]
 
-HOST_SOURCES = ["cabi.cpp", "formats.cpp", "cpu_ref.cpp", "runtime.cpp"]
+HOST_SOURCES = ["cabi.cpp", "formats.cpp", "cpu_ref.cpp"]
 
 
 def _nvcc() -> str:

