@@ -117,24 +117,27 @@ __device__ __forceinline__ void set_status(int* status, int code) {
 // Tile walk: by default consecutive tiles share the B column block (tm fastest); with order_n_fast they share
 // the A row block. The slow index is rotated by tile_rot.
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
-  if (p.rs_interleave > 0) {
-    // fused reduce-scatter: consecutive row blocks go to different owners (the next rank first, this rank last),
-    // which spreads the NVLink stores of the epilogue evenly over the run of the kernel
-    tn = tile % p.tiles_n;
-    const int s = tile / p.tiles_n;
-    int owner = s % p.rs_world + p.rs_rank + 1;
-    if (owner >= p.rs_world) owner -= p.rs_world;
-    tm = owner * p.rs_interleave + s / p.rs_world;
-  } else if (p.group_m > 0) {
-    // bands of group_m row blocks; inside a band tm runs fastest. One wave of CTAs then touches about
-    // group_m A panels and (CTAs / group_m) B panels instead of every A panel.
+  if (p.group_m > 0) {
+    // Bands of group_m row blocks; inside a band the row index runs fastest, so one wave of CTAs touches about
+    // group_m A panels and (CTAs / group_m) B panels instead of a whole operand. `s` is the position in the
+    // row-block order, which is the identity for a plain GEMM, rotated so that the walk starts in the shard that
+    // is local (fused all-gather of A), or alternating between owner ranks, the next rank first and this rank
+    // last (fused reduce-scatter: spreads the NVLink stores of the epilogue evenly over the run of the kernel).
     const int per_band = p.group_m * p.tiles_n;
     const int band = tile / per_band;
     const int first = band * p.group_m;
     const int rows = min(p.group_m, p.tiles_m - first);
     const int r = tile - band * per_band;
-    tm = first + r % rows;
+    const int s = first + r % rows;
     tn = r / rows;
+    if (p.rs_interleave > 0) {
+      int owner = s % p.rs_world + p.rs_rank + 1;
+      if (owner >= p.rs_world) owner -= p.rs_world;
+      tm = owner * p.rs_interleave + s / p.rs_world;
+    } else {
+      tm = s + p.tile_rot;
+      if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
   } else if (p.order_n_fast) {
     tn = tile % p.tiles_n;
     tm = tile / p.tiles_n + p.tile_rot;
@@ -740,25 +743,29 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if (tiles < grid - n_copy) grid = tiles + n_copy;
-  p.group_m = (p.rs_world == 0 && p.g_operand < 0 && p.grp_mode != 2 && p.tiles_m > 16 && p.tiles_n > 1) ? 16 : 0;
+  p.group_m = 0;
+  const int band = p.tiles_m > 16 ? 16 : p.tiles_m;
   if (p.rs_world > 0) {
-    // walk the row blocks starting with the next rank's rows and ending with this rank's own
-    p.order_n_fast = 1;
-    const int next = (p.rs_rank + 1) % p.rs_world;
-    p.tile_rot = (int)(((long long)next * p.rs_rows_per_rank / BM) % p.tiles_m);
+    // row blocks alternate between owners when every owner has whole row blocks; otherwise start after the own rows
     p.rs_interleave = (p.rs_rows_per_rank % BM == 0) ? p.rs_rows_per_rank / BM : 0;
-  }
-  if (p.g_operand >= 0) {
-    // start the tile walk in the tiles whose rows live in the shard that is copied first
+    const int next = (p.rs_rank + 1) % p.rs_world;
+    p.tile_rot = p.rs_interleave ? 0 : (int)(((long long)next * p.rs_rows_per_rank / BM) % p.tiles_m);
+    p.group_m = band;
+  } else if (p.g_operand == 0) {
+    // A is gathered: start the walk in the row blocks of the shard that is copied first (the local one)
     const long long first = p.g_first_shard * p.g_shard_elems - p.g_operand_off;
-    long long row = first > 0 ? (first + p.g_operand_ld - 1) / p.g_operand_ld : 0;
-    if (p.g_operand == 0) {
-      p.order_n_fast = 1;
-      p.tile_rot = (int)((row / BM) % p.tiles_m);
-    } else {
-      p.order_n_fast = 0;
-      p.tile_rot = (int)((row / BN) % p.tiles_n);
-    }
+    const long long row = first > 0 ? (first + p.g_operand_ld - 1) / p.g_operand_ld : 0;
+    p.tile_rot = (int)((row / BM) % p.tiles_m);
+    p.group_m = band;
+  } else if (p.g_operand == 1) {
+    // B is gathered: all row blocks of one column block, column blocks starting in the local shard
+    const long long first = p.g_first_shard * p.g_shard_elems - p.g_operand_off;
+    const long long row = first > 0 ? (first + p.g_operand_ld - 1) / p.g_operand_ld : 0;
+    p.order_n_fast = 0;
+    p.tile_rot = (int)((row / BN) % p.tiles_n);
+  } else if (p.grp_mode != 2 && p.tiles_n > 1) {
+    p.group_m = band;
+    p.tile_rot = 0;
   }
   const RsMaps* maps = (p.rs_tma && g_rs_maps) ? g_rs_maps : &g_no_rs_maps;
   if (p.rs_tma && !g_rs_maps) p.rs_tma = 0;
