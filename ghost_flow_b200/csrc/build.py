@@ -38,6 +38,7 @@ CUDA_SOURCES = [
     "attn_fwd.cu",
     "attn_fwd2.cu",
     "attn_bwd.cu",
+    "attn_decode.cu",
     "comm_kernels.cu",
     "moe_kernels.cu",
     "quant_fp8.cu",

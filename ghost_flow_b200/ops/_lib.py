@@ -48,6 +48,7 @@ _SIGS = {
     "gf_grad_sumsq": [P, L, P, I, P],
     "gf_flash_attn_fwd": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
     "gf_flash_attn_fwd2": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
+    "gf_attn_decode": [P, L, P, P, I, P, I, P, L, I, I, I, I, F, I, P, P],
     "gf_flash_attn_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
     "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
     "gf_cast_f32_to_bf16_2d": [P, P, L, I, L, L, F, P],

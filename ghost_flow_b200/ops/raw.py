@@ -243,3 +243,37 @@ def adamw_flat(p32, m, v, g, p_lp, *, lr, beta1, beta2, eps, weight_decay, step,
     p32.sub_(lr * mh / (vh.sqrt() + eps))
     if p_lp is not None:
         p_lp.copy_(p32.to(p_lp.dtype))
+
+
+# ------------------------------------------------------------------ decode attention over a KV cache
+def attn_decode(q, kcache, vcache, length, B, Hq, Hkv, D, scale=None, splits=None, out=None):
+    """q [B, Hq * D]; caches [B, s_max, Hkv * D]; attends over the first ``length`` cache rows of every sequence
+    (``length``: int, or an int32 tensor [B] of per-sequence lengths). Returns [B, Hq * D]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if _k(q):
+        s_max = kcache.shape[1]
+        per_seq = torch.is_tensor(length)
+        n = s_max if per_seq else int(length)
+        if splits is None:
+            splits = max(1, min(16, (148 * 2) // max(1, B * Hkv), (n + 255) // 256))
+        if out is None:
+            out = torch.empty(B, Hq * D, dtype=q.dtype, device=q.device)
+        scratch = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)
+        _rc(_lib.cuda_lib().gf_attn_decode(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), s_max,
+                                           length.data_ptr() if per_seq else None, 0 if per_seq else n, out.data_ptr(),
+                                           out.stride(0), B, Hq, Hkv, D, float(scale), splits, scratch.data_ptr(),
+                                           _lib.stream_ptr()), "gf_attn_decode")
+        return out
+    G = Hq // Hkv
+    res = torch.empty(B, Hq * D, dtype=q.dtype, device=q.device)
+    for b in range(B):
+        n = int(length[b]) if torch.is_tensor(length) else int(length)
+        qf = q[b].float().view(Hkv, G, D)
+        kf = kcache[b, :n].float().view(n, Hkv, D).permute(1, 0, 2)
+        vf = vcache[b, :n].float().view(n, Hkv, D).permute(1, 0, 2)
+        p = torch.softmax(qf @ kf.transpose(-1, -2) * scale, -1)
+        res[b] = (p @ vf).reshape(Hq * D).to(q.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res

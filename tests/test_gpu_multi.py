@@ -84,3 +84,19 @@ def test_context_parallel_attention_matches_single_gpu(tmp_path):
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     res = torch.load(out)
     assert res and all(v < 3e-2 for v in res.values()), res
+
+
+def test_tensor_parallel_inference_matches_single_gpu(tmp_path):
+    """Prefill + greedy decode with heads and MLP columns sharded over 2 GPUs (fused, NCCL and fp8 linears)."""
+    _need(2)
+    out = str(tmp_path / "tpinf.pt")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29757",
+                        os.path.join(HERE, "_tpinf_worker.py"), out], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    res = torch.load(out)
+    for mode in ("fused", "nccl"):
+        assert res[f"{mode}_logit_rel"] < 3e-2 and res[f"{mode}_first_token_agreement"] == 1.0, res
+        assert res[f"{mode}_token_agreement"] >= 0.75, res
+    assert res["fp8_logit_rel"] < 0.15, res
