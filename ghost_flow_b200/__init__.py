@@ -13,6 +13,10 @@ from .tensor import (  # noqa: F401
     zeros,
 )
 from . import nn, optim  # noqa: F401,E402
+from . import autograd  # noqa: F401,E402
+from .core import (  # noqa: F401,E402
+    Cpu, Cuda, Device, GhostError, MemoryLayoutOptimizer, Serializable, Shape, StateDict, Strides, TensorElement,
+)
 
 
 def __getattr__(name):

@@ -303,3 +303,152 @@ class Tensor(_Tensor):
     @staticmethod
     def from_tensor(t, device=0):
         return _Tensor(getattr(t, "data", t).to(Tensor._dev(device)))
+
+
+# --------------------------------------------------------------------------------------------- result / launch types
+CudaResult = object        # functions here return values or raise CudaError; the alias keeps the reference's name
+
+
+def check_cuda_error(code: int = 0, what: str = "") -> None:
+    """Raises :class:`CudaError` for a non-zero runtime code (and for a pending asynchronous error)."""
+    if code != 0:
+        raise CudaError(CudaError.Kind.Unknown, f"{what} (code {code})")
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+class LaunchConfig:
+    """grid / block / dynamic shared memory of a launch, with the reference's helpers
+    (ghostflow-cuda/src/kernels/mod.rs:8-41)."""
+
+    def __init__(self, grid=(1, 1, 1), block=(256, 1, 1), shared: int = 0):
+        self.grid, self.block, self.shared = tuple(grid), tuple(block), shared
+
+    @classmethod
+    def for_elements(cls, n: int, block: int = 256):
+        return cls(((n + block - 1) // block, 1, 1), (block, 1, 1), 0)
+
+    @classmethod
+    def for_2d(cls, rows: int, cols: int, tile: int = 16):
+        return cls(((cols + tile - 1) // tile, (rows + tile - 1) // tile, 1), (tile, tile, 1), 0)
+
+    @classmethod
+    def persistent(cls, threads: int = 192, shared: int = 0, device: int = 0):
+        """One CTA per SM: the shape of this library's GEMM / attention kernels."""
+        sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
+        return cls((sms, 1, 1), (threads, 1, 1), shared)
+
+
+# The 17 kernel names of the reference's intended surface (kernels/mod.rs:47-110) and the entry points of this
+# library that implement them.
+KERNELS = {
+    "add": "gf_binary", "mul": "gf_binary", "relu": "gf_unary", "gelu": "gf_unary", "sigmoid": "gf_unary",
+    "matmul": "gf_gemm_bf16", "matmul_tiled": "gf_gemm_bf16", "matmul_tensor_core": "gf_gemm_bf16",
+    "flash_attention_forward": "gf_flash_attn_fwd2", "flash_attention_backward": "gf_flash_attn_bwd",
+    "sum_reduce": "gf_reduce", "max_reduce": "gf_reduce", "softmax": "gf_softmax_rows",
+    "cross_entropy": "gf_xent_fused", "layer_norm": "gf_layernorm_fwd", "rms_norm": "gf_rmsnorm_fwd",
+    "batch_norm": "gf_batchnorm_train",
+}
+
+
+class GpuTensor:
+    """fp32 device buffer with real copies in both directions (ghostflow-cuda/src/memory.rs:148-251)."""
+
+    def __init__(self, shape, device: int = 0):
+        _require()
+        self.shape = tuple(shape)
+        self.t = torch.empty(self.shape, dtype=torch.float32, device=torch.device("cuda", device))
+
+    @classmethod
+    def from_cpu(cls, data, shape=None, device: int = 0):
+        src = torch.as_tensor(data, dtype=torch.float32)
+        g = cls(tuple(shape) if shape is not None else tuple(src.shape), device)
+        g.copy_from_cpu(src)
+        return g
+
+    def copy_from_cpu(self, data):
+        self.t.copy_(torch.as_tensor(data, dtype=torch.float32).reshape(self.shape), non_blocking=False)
+
+    def copy_to_cpu(self) -> torch.Tensor:
+        return self.t.detach().cpu()
+
+    def numel(self) -> int:
+        return self.t.numel()
+
+    def size_bytes(self) -> int:
+        return self.t.numel() * 4
+
+
+class CudaTensor:
+    """Device tensor with the reference's method set (ghostflow-cuda/src/tensor.rs). The reference elides every
+    memcpy and falls back to the CPU for most ops; here data lives on the GPU and ops run there (matmul on the
+    tcgen05 GEMM kernel when the operands are bf16)."""
+
+    def __init__(self, data, device: int = 0):
+        _require()
+        src = getattr(data, "data", data)
+        self.device_id = device
+        self.t = torch.as_tensor(src).to(torch.device("cuda", device))
+
+    @classmethod
+    def from_tensor(cls, t, device: int = 0): return cls(t, device)
+    @classmethod
+    def zeros(cls, shape, device=0, dtype=torch.float32): return cls(torch.zeros(*shape, dtype=dtype), device)
+    @classmethod
+    def ones(cls, shape, device=0, dtype=torch.float32): return cls(torch.ones(*shape, dtype=dtype), device)
+    @classmethod
+    def full(cls, shape, value, device=0, dtype=torch.float32): return cls(torch.full(tuple(shape), value, dtype=dtype), device)
+
+    @property
+    def shape(self): return tuple(self.t.shape)
+    @property
+    def strides(self): return tuple(self.t.stride())
+    @property
+    def dtype(self): return self.t.dtype
+    @property
+    def size_bytes(self): return self.t.numel() * self.t.element_size()
+    @property
+    def ptr(self): return self.t.data_ptr()
+
+    def _w(self, t):
+        c = CudaTensor.__new__(CudaTensor)
+        c.device_id, c.t = self.device_id, t
+        return c
+
+    def to_tensor(self): return _Tensor(self.t.detach().cpu())
+    def clone(self): return self._w(self.t.clone())
+    def reshape(self, shape): return self._w(self.t.reshape(tuple(shape)))
+    def transpose(self, d0=0, d1=1): return self._w(self.t.transpose(d0, d1))
+    def add(self, o): return self._w(self.t + o.t)
+    def sub(self, o): return self._w(self.t - o.t)
+    def mul(self, o): return self._w(self.t * o.t)
+    def mul_scalar(self, s): return self._w(self.t * s)
+    def relu(self): return self._w(torch.relu(self.t))
+    def dot(self, o): return float((self.t.flatten().float() * o.t.flatten().float()).sum())
+    def norm(self): return float(self.t.float().norm())
+
+    def matmul(self, o):
+        from ..ops.gemm import matmul as gf_matmul
+        return self._w(gf_matmul(self.t, o.t))
+
+
+class CuBlas:
+    """BLAS-shaped entry points (ghostflow-cuda/src/blas.rs). ``sgemm`` on bf16 operands runs this library's
+    tcgen05 GEMM; fp32 operands go through the vendor library, which is the reference's own arrangement."""
+
+    def __init__(self, device: int = 0):
+        _require()
+        self.device = torch.device("cuda", device)
+
+    def sgemm(self, a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, beta: float = 0.0, c: torch.Tensor | None = None):
+        from ..ops.gemm import matmul as gf_matmul
+        y = gf_matmul(a, b) * alpha if a.dtype == torch.bfloat16 else alpha * (a @ b)
+        return y if c is None or beta == 0.0 else y + beta * c
+
+    def saxpy(self, alpha: float, x: torch.Tensor, y: torch.Tensor): return y.add_(x, alpha=alpha)
+    def sscal(self, alpha: float, x: torch.Tensor): return x.mul_(alpha)
+    def sdot(self, x, y): return float((x.float() * y.float()).sum())
+    def snrm2(self, x): return float(x.float().norm())
+
+    def matmul(self, a: CudaTensor, b: CudaTensor) -> CudaTensor:
+        return a.matmul(b)

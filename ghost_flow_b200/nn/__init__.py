@@ -18,6 +18,7 @@ from .loss import (  # noqa: F401
 from .attention import (  # noqa: F401
     CrossAttention, FlashAttention, FlashAttentionConfig, MultiHeadAttention, scaled_dot_product_attention,
 )
+from .transformer import RotaryEmbedding as RoPE  # noqa: F401
 from .transformer import (  # noqa: F401
     FeedForward, PositionalEncoding, RotaryEmbedding, TransformerDecoder, TransformerDecoderLayer,
     TransformerEncoder, TransformerEncoderLayer,
@@ -39,7 +40,7 @@ from .moe import Expert, MixtureOfExperts, MoEConfig, MoEStats, Router, RoutingS
 from .ring_attention import RingAttention, RingAttentionConfig, StripedRingAttention  # noqa: F401
 from .privacy import (  # noqa: F401
     AdversarialAttack, AdversarialTrainer, AdversarialTrainingConfig, AggregationStrategy, AttackConfig, AttackType,
-    DPConfig, DPSGDOptimizer, FederatedClient, FederatedServer, LocalDP, PATEEnsemble, PrivacyAccountant,
+    DPConfig, DPSGDOptimizer, DifferentialPrivacy, FederatedClient, FederatedServer, LocalDP, PATEEnsemble, PrivacyAccountant,
     RandomizedSmoothing, SecureAggregation,
 )
 from .inference import (  # noqa: F401

@@ -370,3 +370,27 @@ class RandomizedSmoothing:
         radius = torch.where(p_low > 0.5, self.sigma * torch.special.ndtri(p_low.double()).float(),
                              torch.zeros_like(p_low))
         return top, radius
+
+
+class DifferentialPrivacy:
+    """Clip-and-noise for federated updates (ghostflow-nn/src/federated.rs:311-380): every client update is clipped
+    to ``clip_norm`` in global L2 norm and Gaussian noise of standard deviation ``noise_multiplier * clip_norm`` is
+    added to the aggregate."""
+
+    def __init__(self, clip_norm: float = 1.0, noise_multiplier: float = 1.0, seed: int = 0):
+        self.clip_norm, self.noise_multiplier = clip_norm, noise_multiplier
+        self._gen = torch.Generator().manual_seed(seed)
+
+    def clip_update(self, update: dict) -> dict:
+        total = torch.sqrt(sum((v.float() ** 2).sum() for v in update.values()))
+        scale = min(1.0, self.clip_norm / max(float(total), 1e-12))
+        return {k: v * scale for k, v in update.items()}
+
+    def add_noise(self, aggregate: dict, num_clients: int = 1) -> dict:
+        std = self.noise_multiplier * self.clip_norm / max(1, num_clients)
+        return {k: v + torch.randn(v.shape, generator=self._gen).to(v.device, v.dtype) * std for k, v in aggregate.items()}
+
+    def privatize(self, updates: list) -> dict:
+        clipped = [self.clip_update(u) for u in updates]
+        mean = {k: sum(u[k] for u in clipped) / len(clipped) for k in clipped[0]}
+        return self.add_noise(mean, len(clipped))

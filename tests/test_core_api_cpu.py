@@ -1,0 +1,88 @@
+"""Core value types, the autograd tape / dynamic graph, and the inventory of reference names."""
+import importlib
+import pkgutil
+
+import pytest
+import torch
+
+import ghost_flow_b200 as gf
+from ghost_flow_b200.autograd import DynamicContext, DynamicTensor, GradTapeContext, grad_fns, is_recording, record_op
+
+
+def test_shape_strides_broadcast_offsets():
+    s = gf.Shape((2, 1, 4))
+    assert s.broadcast_with(gf.Shape((3, 1))) == (2, 3, 4)
+    assert s.default_strides() == (4, 4, 1) and s.numel() == 8
+    assert s.is_contiguous((4, 4, 1)) and not gf.Shape((2, 3)).is_contiguous((1, 2))
+    assert s.offset((1, 0, 2)) == 6
+    with pytest.raises(gf.GhostError) as e:
+        gf.Shape((2, 3)).broadcast_with(gf.Shape((4, 3)))
+    assert e.value.kind is gf.GhostError.Kind.BroadcastError
+    assert gf.Cuda(1).torch_device() == torch.device("cuda", 1) and gf.Cpu() == gf.Cpu()
+    buf, views = gf.MemoryLayoutOptimizer(64).pack([torch.ones(3), torch.arange(5.0)])
+    assert buf.numel() == 128 and views[1].data_ptr() % 64 == buf.data_ptr() % 64 and torch.equal(views[1], torch.arange(5.0))
+
+
+def test_serializable_round_trip(tmp_path):
+    class Box(gf.Serializable):
+        def __init__(self):
+            self.w = torch.randn(3, 4)
+
+        def state_dict(self):
+            return {"w": self.w}
+
+        def load_state_dict(self, s):
+            self.w = s["w"]
+
+    a, b = Box(), Box()
+    a.save(tmp_path / "box.gf")
+    b.load(tmp_path / "box.gf")
+    assert torch.equal(a.w, b.w)
+
+
+def test_tape_and_dynamic_graph_gradients_match_torch():
+    a = DynamicTensor(torch.randn(3, 4))
+    b = DynamicTensor(torch.randn(4, 2), a.graph)
+    y = a.matmul(b).relu().sum()
+    y.backward()
+    at, bt = a.data.clone().requires_grad_(True), b.data.clone().requires_grad_(True)
+    torch.relu(at @ bt).sum().backward()
+    assert torch.allclose(a.grad.data, at.grad) and torch.allclose(b.grad.data, bt.grad)
+    with DynamicContext.no_grad():
+        c = DynamicTensor(torch.ones(2), a.graph)
+        assert c.node not in a.graph.nodes
+    assert not is_recording()
+    with GradTapeContext() as tape:
+        assert is_recording()
+        x, w = torch.randn(3), torch.randn(3)
+        z = x * w
+        record_op("mul", [x, w], z, lambda g: grad_fns.mul_backward(g, x, w))
+        s = z.exp()
+        record_op("exp", [z], s, lambda g: (grad_fns.exp_backward(g, s),))
+        gx, gw = tape.gradient(s, [x, w])
+    xt = x.clone().requires_grad_(True)
+    (xt * w).exp().sum().backward()
+    assert torch.allclose(gx, xt.grad) and len(tape.operations) == 2
+
+
+def test_reference_class_names_are_present():
+    have = set(dir(gf))
+    for m in pkgutil.walk_packages(gf.__path__, "ghost_flow_b200."):
+        if ".csrc" in m.name or ".lib" in m.name:
+            continue
+        have |= set(dir(importlib.import_module(m.name)))
+    names = """Tensor Shape Strides DType GhostError StateDict Serializable MemoryPool MemoryStats MemoryLayoutOptimizer
+    TrackedAllocator Profiler ProfileScope Benchmark FusionEngine FusionPattern LayoutOptimizer MemoryLayout
+    HardwareBackend HardwareDevice HardwareOps list_devices SparseTensorCOO SparseTensorCSR SparseTensorCSC Device Cpu Cuda
+    CudaDevice DeviceGuard CudaStream CudaEvent CudaTimer GpuMemoryPool GpuTensor CudaTensor CuBlas CudaError LaunchConfig
+    GradTape GradTapeContext RecordedOp DynamicGraph DynamicContext DynamicTensor
+    Linear Conv1d Conv2d Conv3d TransposeConv2d BatchNorm1d BatchNorm2d LayerNorm GroupNorm InstanceNorm Dropout Embedding
+    MultiHeadAttention FlashAttention TransformerEncoder TransformerDecoderLayer PositionalEncoding RotaryEmbedding LSTM GRU
+    GradScaler AutocastContext CheckpointConfig LoRAConfig LoRALinear QLoRALinear PromptTuningConfig PrefixTuningConfig
+    DistillationConfig CurriculumConfig MoEConfig MixtureOfExperts RingAttention StripedRingAttention ZeRoConfig ZeRoOptimizer
+    ZeRoStats ZeRoStage DataParallel DistributedDataParallel GradientAccumulator ModelParallel PipelineParallel
+    DistributedBackend DistributedConfig FederatedClient FederatedServer SecureAggregation DifferentialPrivacy DPConfig
+    DPSGDOptimizer PrivacyAccountant AttackConfig AdversarialTrainingConfig InferenceSession BatchInference ONNXModel
+    SGD Adam AdamW StepLR CosineAnnealingLR Dataset DataLoader""".split()
+    missing = [n for n in names if n not in have]
+    assert not missing, missing
