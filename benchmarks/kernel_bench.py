@@ -47,6 +47,11 @@ def build(args, dev):
         out = torch.empty(M, N, device=dev, dtype=bf)
         fn = lambda: gemm_raw(a, k == "gemm_tn", b, k in ("gemm_nn", "gemm_tn"), M, N, K, out=out)  # noqa: E731
         return fn, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    if k == "gemm_skinny":
+        M, N, K = args.m, args.n, args.k
+        a = torch.randn(M, K, device=dev, dtype=bf)
+        b = torch.randn(N, K, device=dev, dtype=bf)
+        return (lambda: gemm_raw(a, False, b, False, M, N, K)), 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
     if k == "cublas_nt":
         M, N, K = args.m, args.n, args.k
         a = torch.randn(M, K, device=dev, dtype=bf)
@@ -67,6 +72,12 @@ def build(args, dev):
         from ghost_flow_b200.ops import fp8
         x = torch.randn(args.rows, args.cols, device=dev, dtype=bf)
         return (lambda: fp8.quantize_rows(x, 1)), 0.0, 3.0 * args.rows * args.cols
+    if k == "attn_decode":
+        B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads or args.heads, args.dim
+        q = torch.randn(B, H * D, device=dev, dtype=bf)
+        kc = torch.randn(B, S, Hkv * D, device=dev, dtype=bf)
+        vc = torch.randn(B, S, Hkv * D, device=dev, dtype=bf)
+        return (lambda: raw.attn_decode(q, kc, vc, S, B, H, Hkv, D)), 4.0 * B * H * S * D, 4.0 * B * S * Hkv * D
     if k in ("attn_fwd", "attn_bwd"):
         B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads or args.heads, args.dim
         q = torch.randn(B * S, H * D, device=dev, dtype=bf)

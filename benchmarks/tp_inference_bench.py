@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--linear", default="fused", choices=["fused", "nccl", "fp8"])
+    ap.add_argument("--graph", type=int, default=1, help="replay the decode step from a CUDA graph")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -76,27 +77,37 @@ def main():
     e1.record()
     barrier()
     prefill_ms = maxms(e0.elapsed_time(e1))
-    for t in range(3):                  # decode warm-up
-        tok = eng.decode_step(tok, a.prompt + t)
-    barrier()
-    e0.record()
-    for t in range(3, a.new - 1):
-        tok = eng.decode_step(tok, a.prompt + t)
-    e1.record()
-    barrier()
     steps = a.new - 1 - 3
+    if a.graph:
+        eng.capture_decode()
+        eng.graph_decode(tok, a.prompt, 3)          # warm-up replays
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            eng.graph.replay()
+        e1.record()
+    else:
+        for t in range(3):                  # decode warm-up
+            tok = eng.decode_step(tok, a.prompt + t)
+        barrier()
+        e0.record()
+        for t in range(3, a.new - 1):
+            tok = eng.decode_step(tok, a.prompt + t)
+        e1.record()
+    barrier()
     decode_ms = maxms(e0.elapsed_time(e1)) / steps
     _lib.check_status(dev)
     if rank == 0:
         params = sum(p.numel() if torch.is_tensor(p) else p[0].numel() for L in eng.layers for p in L.values()) * world
         print(json.dumps({"model": a.model, "layers": cfg.num_hidden_layers, "tp": world, "linear": a.linear, "batch": a.batch,
-                          "prompt_len": a.prompt, "decode_steps_timed": steps, "block_params": params,
+                          "prompt_len": a.prompt, "decode_steps_timed": steps, "cuda_graph": bool(a.graph), "block_params": params,
                           "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(a.batch * a.prompt / prefill_ms * 1e3),
                           "decode_ms_per_step": round(decode_ms, 3), "decode_tokens_per_s": round(a.batch / decode_ms * 1e3),
                           "data": "synthetic token ids, random-init weights", "dtype": "fp8 e4m3 weights+activations" if a.linear == "fp8" else "bf16"}))
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)      # a process group that took part in a graph capture can stall in its destructor
 
 
 if __name__ == "__main__":

@@ -84,6 +84,10 @@ struct GemmParams {
   long long sc_ld;
   int sc_world, sc_rank, sc_epoch;
   int* sc_counter;
+  // split-K for skinny problems (few output tiles, long K): tile index = (k slice, tile); every slice adds its
+  // partial product into the fp32 workspace `ws` [M, N] with atomics; a second kernel converts.
+  int split_k;
+  float* ws;
   int group_m;              // > 0: plain GEMM walks bands of group_m row blocks (keeps a wave's A and B panels in L2)
   int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
 };
@@ -175,6 +179,17 @@ __device__ __forceinline__ bool tile_info(const GemmParams& p, int tile, int num
     t.nkb = (k1 - k0) / BK;
     t.c_row_add = (long long)e * p.M;
     return true;              // an empty segment still owes zeros (or nothing, when accumulating) to the output
+  }
+  if (p.split_k > 1) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int ks = tile / per;
+    tile_coords(p, tile - ks * per, t.tm, t.tn);
+    t.a_row = t.tm * BM;
+    t.b_row = 0;
+    const int kbs = (num_kb + p.split_k - 1) / p.split_k;
+    t.k_begin = ks * kbs * BK;
+    t.nkb = min(kbs, num_kb - ks * kbs);
+    return t.nkb > 0;
   }
   tile_coords(p, tile, t.tm, t.tn);
   t.a_row = t.tm * BM;
@@ -295,7 +310,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1);
+  const int num_tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1) * (p.split_k > 1 ? p.split_k : 1);
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if ((int)blockIdx.x < n_copy) {
     gather_role(p, smem);
@@ -501,12 +516,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
           const bool full = (col0 + 32 <= p.N);
-          if (p.bias && p.rs_world == 0) {
+          if (p.bias && p.rs_world == 0 && p.split_k <= 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
           }
-          if (p.residual && p.rs_world == 0) {
+          if (p.residual && p.rs_world == 0 && p.split_k <= 1) {
             const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
             if (full && ((p.ldr & 7) == 0)) {
 #pragma unroll
@@ -571,6 +586,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
             }
+          } else if (p.split_k > 1) {
+            float* wp = p.ws + (long long)row * p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) atomicAdd(wp + j, v[j]);
           } else if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + (ti.c_row_add + row) * p.ldc + col0;
             if (full && ((p.ldc & 3) == 0)) {
@@ -738,7 +758,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  int tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1);
+  int tiles = p.tiles_m * p.tiles_n * (p.grp_mode == 2 ? p.grp_experts : 1) * (p.split_k > 1 ? p.split_k : 1);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
@@ -825,13 +845,50 @@ static int gemm_core(const void* A, const void* B, void* C, int M, int N, int K,
 #undef GF_DISPATCH
 }
 
+namespace gf {
+// C = bf16(ws + bias + residual); ws is the fp32 sum of the k slices (alpha already applied).
+__global__ void splitk_finish_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ C, long long ldc,
+                                     const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+                                     long long ldr, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int r = (int)(i / N), c = (int)(i % N);
+  float v = ws[i];
+  if (bias) v += __bfloat162float(bias[c]);
+  if (residual) v += __bfloat162float(residual[(long long)r * ldr + c]);
+  C[(long long)r * ldc + c] = __float2bfloat16(v);
+}
+
+// fp32 workspace per device, grown on demand and kept. Calls that use it on different streams of one device must
+// not overlap (the training engines issue GEMMs on one stream per device).
+static float* g_splitk_ws[32] = {};
+static size_t g_splitk_cap[32] = {};
+static float* splitk_workspace(size_t floats) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 32) return nullptr;
+  if (g_splitk_cap[dev] < floats) {
+    if (g_splitk_ws[dev]) cudaFree(g_splitk_ws[dev]);
+    size_t cap = floats < (size_t)(8 << 20) ? (size_t)(8 << 20) : floats;
+    if (cudaMalloc(&g_splitk_ws[dev], cap * sizeof(float)) != cudaSuccess) {
+      g_splitk_ws[dev] = nullptr;
+      g_splitk_cap[dev] = 0;
+      cudaGetLastError();
+      return nullptr;
+    }
+    g_splitk_cap[dev] = cap;
+  }
+  return g_splitk_ws[dev];
+}
+}  // namespace gf
+
 static void no_gather(gf::GemmParams& p) {
   p.g_operand = -1; p.g_copy_ctas = 0; p.g_world = 1; p.g_rank = 0; p.g_first_shard = 0;
   for (int i = 0; i < 8; ++i) p.g_src[i] = nullptr;
   p.g_dst = nullptr; p.g_shard_elems = 8; p.g_operand_off = 0; p.g_operand_ld = 1; p.g_ready = nullptr;
   p.g_counters = nullptr; p.g_epoch = 0; p.g_version_pad = nullptr; p.g_version_idx = 0; p.g_version_val = 0;
   p.order_n_fast = 0; p.tile_rot = 0; p.rs_interleave = 0; p.rs_tma = 0;
-  p.grp_offsets = nullptr; p.grp_experts = 0; p.grp_mode = 0; p.grp_b_rows = 0;
+  p.grp_offsets = nullptr; p.grp_experts = 0; p.grp_mode = 0; p.grp_b_rows = 0; p.split_k = 1; p.ws = nullptr;
   p.grp_src_start = nullptr; p.grp_arrived = nullptr; p.grp_world = 1; p.grp_epoch = 0;
   p.sc_ret = nullptr; p.sc_ld = 0; p.sc_world = 0; p.sc_rank = 0; p.sc_epoch = 0; p.sc_counter = nullptr;
   for (int i = 0; i < 8; ++i) { p.sc_dst[i] = nullptr; p.sc_flags[i] = nullptr; }
@@ -850,8 +907,36 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   gf::enter();
   gf::GemmParams p;
   no_gather(p);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  // Skinny problem (decode-sized M): too few output tiles to fill the machine, so the weight matrix would be
+  // streamed by a handful of SMs. Split K until there is about one work item per SM.
+  if (M <= 256 && !out_fp32 && !accumulate && K >= 2048 && bn_hint == 0 && max_ctas == 0) {
+    const int bn = N <= 128 ? 128 : 256;
+    const long long tiles = (long long)((M + gf::BM - 1) / gf::BM) * ((N + bn - 1) / bn);
+    const int sms = gf::sm_count();
+    int split = (int)(sms / (tiles > 0 ? tiles : 1));
+    if (split > K / 512) split = K / 512;
+    if (split > 16) split = 16;
+    if (split >= 2) {
+      float* ws = gf::splitk_workspace((size_t)M * N);
+      if (ws) {
+        if (cudaMemsetAsync(ws, 0, sizeof(float) * (size_t)M * N, st) != cudaSuccess) return gf::GFH_CUDA;
+        p.split_k = split;
+        p.ws = ws;
+        int rc = gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, 0, 0, nullptr, nullptr, 0, alpha,
+                           status, bn, 0, p, st);
+        if (rc) return rc;
+        const long long n = (long long)M * N;
+        gf::splitk_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+            ws, reinterpret_cast<__nv_bfloat16*>(C), ldc, reinterpret_cast<const __nv_bfloat16*>(bias),
+            reinterpret_cast<const __nv_bfloat16*>(residual), ldr, M, N);
+        gf::note_extra_launches(1);
+        return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
+      }
+    }
+  }
   return gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias, residual, ldr,
-                   alpha, status, bn_hint, max_ctas, p, reinterpret_cast<cudaStream_t>(stream_v));
+                   alpha, status, bn_hint, max_ctas, p, st);
 }
 
 // Grouped GEMM over the row segments of a row-sorted buffer (the experts of a mixture-of-experts layer).

@@ -255,7 +255,9 @@ def attn_decode(q, kcache, vcache, length, B, Hq, Hkv, D, scale=None, splits=Non
         per_seq = torch.is_tensor(length)
         n = s_max if per_seq else int(length)
         if splits is None:
-            splits = max(1, min(16, (148 * 2) // max(1, B * Hkv), (n + 255) // 256))
+            # enough CTAs for about eight per SM (the kernel hides DRAM latency with warps in flight), but no
+            # slice shorter than 128 cache rows
+            splits = max(1, min(32, -(-(148 * 8) // max(1, B * Hkv)), (n + 127) // 128))
         if out is None:
             out = torch.empty(B, Hq * D, dtype=q.dtype, device=q.device)
         scratch = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)

@@ -41,7 +41,10 @@ class _Linears:
         self.mode, self.group, self.T, self.d = mode, group, tokens, hidden
         self.world, self.rank = _world(group)
         self.device = device
-        if self.world > 1 and mode == "fused":
+        # decode-sized token counts are latency- and bandwidth-bound: there the weight matrices are streamed by
+        # the split-K GEMM and the (tiny) collectives stay separate
+        self.fused = self.world > 1 and mode == "fused" and tokens > 256
+        if self.fused:
             self.ag = AllGatherGemm(tokens, hidden, device, group)
             self.rs = GemmReduceScatter(tokens, hidden, device, group)
 
@@ -49,7 +52,7 @@ class _Linears:
         """all_gather(x_shard) @ w^T -> [T, n_local]. ``w``: bf16 [n_local, d] or (q, scale) for fp8."""
         if self.world == 1:
             full = x_shard
-        elif self.mode == "fused":
+        elif self.fused:
             return self.ag(x_shard, w)
         else:
             full = torch.empty(self.T, self.d, dtype=x_shard.dtype, device=self.device)
@@ -61,7 +64,7 @@ class _Linears:
 
     def row(self, x, w, residual):
         """reduce_scatter(x @ w^T) + residual -> [T / world, d]."""
-        if self.world > 1 and self.mode == "fused":
+        if self.fused:
             return self.rs(x, w, residual=residual)
         if self.mode == "fp8":
             xq, xs = fp8_ops.quantize_rows(x, 0)
@@ -150,21 +153,28 @@ class TPLlamaInference:
             self.lm_head = get("lm_head.weight")[r * self.V:(r + 1) * self.V].contiguous()
 
     # ------------------------------------------------------------------ one transformer block on a token shard
-    def _block(self, lin: _Linears, L, h, i, n_seq, seq_len, pos):
-        """h: [T / world, d]. Prefill: n_seq sequences of seq_len tokens at position 0; decode: seq_len = 1 at pos."""
+    def _block(self, lin: _Linears, L, h, i, n_seq, seq_len, pos, dev=None):
+        """h: [T / world, d]. Prefill: n_seq sequences of seq_len tokens at position 0; decode: seq_len = 1 at pos.
+        ``dev`` (decode inside a CUDA graph): (position as a device tensor [1], lengths [B] int32, the cos and sin
+        rows of that position) so that nothing in the step depends on a host value."""
         c, eps = self.cfg, self.cfg.rms_norm_eps
         T = lin.T
         x, _, _ = raw.rmsnorm_fwd(h, L["n1"], eps)
         qkv = lin.column(x, L["wqkv"])                                  # [T, (Hq + 2 Hkv) D]
         HD, KD = self.Hq * self.D, self.Hkv * self.D
         q, k, v = qkv[:, :HD], qkv[:, HD:HD + KD], qkv[:, HD + KD:]
-        raw.rope_(q.unflatten(1, (self.Hq, self.D)), self.cos, self.sin, seq_len, c.rope_interleaved, pos)
-        raw.rope_(k.unflatten(1, (self.Hkv, self.D)), self.cos, self.sin, seq_len, c.rope_interleaved, pos)
+        cos, sin, off = (self.cos, self.sin, pos) if dev is None else (dev[2], dev[3], 0)
+        raw.rope_(q.unflatten(1, (self.Hq, self.D)), cos, sin, seq_len, c.rope_interleaved, off)
+        raw.rope_(k.unflatten(1, (self.Hkv, self.D)), cos, sin, seq_len, c.rope_interleaved, off)
         kc, vc = self.kcache[i], self.vcache[i]
         if seq_len > 1:
             kc[:, :seq_len].copy_(k.view(n_seq, seq_len, KD))
             vc[:, :seq_len].copy_(v.view(n_seq, seq_len, KD))
             o, _ = raw.attn_fwd(q, k, v, n_seq, seq_len, self.Hq, self.Hkv, self.D, True)
+        elif dev is not None:
+            kc.index_copy_(1, dev[0], k.reshape(n_seq, 1, KD))
+            vc.index_copy_(1, dev[0], v.reshape(n_seq, 1, KD))
+            o = raw.attn_decode(q, kc, vc, dev[1], n_seq, self.Hq, self.Hkv, self.D)
         else:
             kc[:, pos].copy_(k)
             vc[:, pos].copy_(v)
@@ -208,13 +218,13 @@ class TPLlamaInference:
         return tok
 
     @torch.no_grad()
-    def decode_step(self, tokens: torch.Tensor, pos: int):
+    def decode_step(self, tokens: torch.Tensor, pos: int, dev=None):
         """tokens [B] at position ``pos`` -> next tokens [B]."""
         B, w, r, d = self.B, self.world, self.rank, self.cfg.hidden_size
         lo, hi = r * B // w, (r + 1) * B // w
         h = self.embed[tokens[lo:hi]]
         for i, L in enumerate(self.layers):
-            h = self._block(self.dec, L, h, i, B, 1, pos)
+            h = self._block(self.dec, L, h, i, B, 1, pos, dev)
         if w > 1:
             full = torch.empty(B, d, dtype=h.dtype, device=self.device)
             dist.all_gather_into_tensor(full, h.contiguous(), group=self.group)
@@ -223,9 +233,56 @@ class TPLlamaInference:
         tok, self.last_logits = self._next_tokens(full)
         return tok
 
+    # ------------------------------------------------------------------ decode as one CUDA graph
     @torch.no_grad()
-    def generate(self, ids: torch.Tensor, max_new_tokens: int):
-        out = [self.prefill(ids)]
+    def capture_decode(self):
+        """Captures one decode step (all layers, the collectives, sampling, and the bookkeeping that advances the
+        position) into a CUDA graph. A step is about 30 launches per layer, so replaying it removes the host from
+        the loop. State lives in device tensors: current tokens, position, lengths."""
+        dev = self.device
+        self.g_tokens = torch.zeros(self.B, dtype=torch.long, device=dev)
+        self.g_pos = torch.full((1,), self.S, dtype=torch.long, device=dev)
+        self.g_lens = torch.full((self.B,), self.S + 1, dtype=torch.int32, device=dev)
+
+        def step():
+            cos, sin = self.cos.index_select(0, self.g_pos), self.sin.index_select(0, self.g_pos)
+            nxt = self.decode_step(self.g_tokens, -1, (self.g_pos, self.g_lens, cos, sin))
+            self.g_tokens.copy_(nxt)
+            self.g_pos.add_(1)
+            self.g_lens.add_(1)
+
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):              # warm-up outside capture: lazy allocations, kernel attributes
+                step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            step()
+        return self.graph
+
+    def graph_decode(self, first_tokens: torch.Tensor, start_pos: int, steps: int):
+        """Runs ``steps`` captured decode steps from ``first_tokens`` at ``start_pos``; returns [B, steps]."""
+        self.g_tokens.copy_(first_tokens)
+        self.g_pos.fill_(start_pos)
+        self.g_lens.fill_(start_pos + 1)
+        out = []
+        for _ in range(steps):
+            self.graph.replay()
+            out.append(self.g_tokens.clone())
+        return torch.stack(out, 1)
+
+    @torch.no_grad()
+    def generate(self, ids: torch.Tensor, max_new_tokens: int, use_graph: bool = False):
+        first = self.prefill(ids)
+        if use_graph and self.device.type == "cuda" and max_new_tokens > 1:
+            if not hasattr(self, "graph"):
+                self.capture_decode()
+            rest = self.graph_decode(first, self.S, max_new_tokens - 1)
+            return torch.cat((first[:, None], rest), 1)
+        out = [first]
         for t in range(1, max_new_tokens):
             out.append(self.decode_step(out[-1], self.S + t - 1))
         return torch.stack(out, 1)

@@ -45,6 +45,11 @@ def main():
         res[f"{mode}_logit_rel"] = ((eng.last_logits - sl).norm() / sl.norm()).item()
         res[f"{mode}_token_agreement"] = (toks == ref_tokens).float().mean().item()
         res[f"{mode}_first_token_agreement"] = (first == ref_tokens[:, 0]).float().mean().item()
+        if mode == "nccl":
+            # the same decode replayed from a CUDA graph must reproduce the eager tokens exactly
+            toks_g = eng.generate(ids, NEW, use_graph=True)
+            torch.cuda.synchronize()
+            res["graph_matches_eager"] = 0.0 if torch.equal(toks_g, toks) else 1.0
         del eng
     if rank == 0:
         torch.save(res, out_path)

@@ -285,3 +285,21 @@ def test_flash_attention_fwd_large_scores_rescale(kernel_status):
     assert _rel_err(o, ops.attention_ref(q, k, v, causal=True)) < 2e-2
     o2 = ops.flash_attention(q, k, v, causal=False)
     assert _rel_err(o2, ops.attention_ref(q, k, v, causal=False)) < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 5120, 8192), (8, 1280, 8192), (200, 768, 4096)])
+def test_skinny_gemm_split_k_matches_fp32(M, N, K):
+    """Decode-sized products take the split-K path (fp32 atomics + conversion kernel, bias and residual there)."""
+    from ghost_flow_b200.ops import _lib
+    from ghost_flow_b200.ops.gemm import gemm_raw
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    y = gemm_raw(a, False, w, False, M, N, K, bias=bias, residual=res)
+    torch.cuda.synchronize()
+    _lib.check_status(a.device)
+    ref = a.float() @ w.float().t() + bias.float() + res.float()
+    assert ((y.float() - ref).norm() / ref.norm()) < 5e-3
