@@ -12,7 +12,7 @@ Megatron-style sequence-parallel layout: activations between blocks are sharded 
   arrived partials (``gf_gemm_bf16_reduce_scatter``).
 
 Both have an NCCL path (``fused=False``) that is the baseline and the test oracle. The reference has no tensor
-parallelism at all (SURVEY of ghostflow-nn/src/distributed.rs: only simulated data/model/pipeline wrappers).
+parallelism at all (ghostflow-nn/src/distributed.rs has only simulated data, model and pipeline wrappers).
 """
 from __future__ import annotations
 
