@@ -88,6 +88,7 @@ struct GemmParams {
   // partial product into the fp32 workspace `ws` [M, N] with atomics; a second kernel converts.
   int split_k;
   float* ws;
+  int act;                  // epilogue activation after bias and residual: 0 none, 1 ReLU
   int group_m;              // > 0: plain GEMM walks bands of group_m row blocks (keeps a wave's A and B panels in L2)
   int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
 };
@@ -538,6 +539,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
           }
+          if (p.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+          }
           if (p.rs_tma) {
             __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(rs_stage_smem) + (warp - 2) * 32 * RS_STAGE_COLS;
             const int sub = c & 3;
@@ -888,7 +893,7 @@ static void no_gather(gf::GemmParams& p) {
   p.g_dst = nullptr; p.g_shard_elems = 8; p.g_operand_off = 0; p.g_operand_ld = 1; p.g_ready = nullptr;
   p.g_counters = nullptr; p.g_epoch = 0; p.g_version_pad = nullptr; p.g_version_idx = 0; p.g_version_val = 0;
   p.order_n_fast = 0; p.tile_rot = 0; p.rs_interleave = 0; p.rs_tma = 0;
-  p.grp_offsets = nullptr; p.grp_experts = 0; p.grp_mode = 0; p.grp_b_rows = 0; p.split_k = 1; p.ws = nullptr;
+  p.grp_offsets = nullptr; p.grp_experts = 0; p.grp_mode = 0; p.grp_b_rows = 0; p.split_k = 1; p.ws = nullptr; p.act = 0;
   p.grp_src_start = nullptr; p.grp_arrived = nullptr; p.grp_world = 1; p.grp_epoch = 0;
   p.sc_ret = nullptr; p.sc_ld = 0; p.sc_world = 0; p.sc_rank = 0; p.sc_epoch = 0; p.sc_counter = nullptr;
   for (int i = 0; i < 8; ++i) { p.sc_dst[i] = nullptr; p.sc_flags[i] = nullptr; }
@@ -907,10 +912,11 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   gf::enter();
   gf::GemmParams p;
   no_gather(p);
+  p.act = unused_a == 1 ? 1 : 0;     // the former flag-granularity argument now selects the epilogue activation
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
   // Skinny problem (decode-sized M): too few output tiles to fill the machine, so the weight matrix would be
   // streamed by a handful of SMs. Split K until there is about one work item per SM.
-  if (M <= 256 && !out_fp32 && !accumulate && K >= 2048 && bn_hint == 0 && max_ctas == 0) {
+  if (M <= 256 && !out_fp32 && !accumulate && K >= 2048 && bn_hint == 0 && max_ctas == 0 && p.act == 0) {
     const int bn = N <= 128 ? 128 : 256;
     const long long tiles = (long long)((M + gf::BM - 1) / gf::BM) * ((N + bn - 1) / bn);
     const int sms = gf::sm_count();

@@ -357,3 +357,42 @@ GF_API int gf_batchnorm_train(const float* x, float* y, const float* gamma, cons
                                                              save_rstd, N, C, HW, eps, momentum);
   GF_RET();
 }
+
+
+// ------------------------------------------------------------------ im2col for the tensor-core convolution
+// x [N, C, H, W] fp32 -> cols [N * OH * OW, Kp] bf16 with column index (c * KH + ky) * KW + kx (the order of a
+// weight viewed as [Cout, C * KH * KW]); columns >= C * KH * KW (padding to a multiple of 8) are zero.
+namespace gf {
+__global__ void im2col_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ cols, int N, int C, int H,
+                                   int W, int KH, int KW, int OH, int OW, int stride, int pad, int Kp) {
+  const long long total = (long long)N * OH * OW * Kp;
+  const int K = C * KH * KW;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i % Kp);
+    const long long row = i / Kp;
+    float v = 0.f;
+    if (k < K) {
+      const int kx = k % KW, ky = (k / KW) % KH, c = k / (KW * KH);
+      const int ox = (int)(row % OW), oy = (int)((row / OW) % OH), n = (int)(row / ((long long)OW * OH));
+      const int iy = oy * stride - pad + ky, ix = ox * stride - pad + kx;
+      if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = x[(((long long)n * C + c) * H + iy) * W + ix];
+    }
+    cols[i] = __float2bfloat16(v);
+  }
+}
+}  // namespace gf
+
+GF_API int gf_im2col_bf16(const float* x, void* cols, int N, int C, int H, int W, int KH, int KW, int stride, int pad,
+                          int Kp, void* stream) {
+  gf::enter();
+  const int OH = (H + 2 * pad - KH) / stride + 1, OW = (W + 2 * pad - KW) / stride + 1;
+  if (OH <= 0 || OW <= 0 || Kp < C * KH * KW || Kp % 8) return gf::GFH_BAD_ARG;
+  const long long total = (long long)N * OH * OW * Kp;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)gf::sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  gf::im2col_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, (__nv_bfloat16*)cols, N, C, H, W, KH, KW,
+                                                                            OH, OW, stride, pad, Kp);
+  return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
+}

@@ -238,6 +238,41 @@ def conv_bn_relu(x, weight, bias, bn_weight, bn_bias, running_mean, running_var,
     return torch.relu(y) if relu else y
 
 
+def conv_bn_relu_tensorcore(x, weight, bias, bn_weight, bn_bias, running_mean, running_var, stride: int = 1,
+                            padding: int = 0, eps: float = 1e-5, relu: bool = True):
+    """The same fused inference op as :func:`conv_bn_relu`, on the tensor cores: batch norm is folded into the
+    weights and a per-channel bias, the input is unfolded to ``[N * OH * OW, Cin * KH * KW]`` bf16 by a gather
+    kernel, and one tcgen05 GEMM with bias + ReLU epilogue produces the output (bf16 operands, fp32 accumulation).
+    Returns NCHW fp32 like the direct kernel. Falls back to :func:`conv_bn_relu` off the GPU or when ``Cout`` is
+    not a multiple of 8."""
+    Cout = weight.shape[0]
+    if not (_gpu_plain(x, weight) and x.dim() == 4 and Cout % 8 == 0):
+        return conv_bn_relu(x, weight, bias, bn_weight, bn_bias, running_mean, running_var, stride, padding, eps, relu)
+    import ctypes
+    from .gemm import gemm_raw
+    N, Cin, H, W = x.shape
+    _, _, KH, KW = weight.shape
+    OH, OW = (H + 2 * padding - KH) // stride + 1, (W + 2 * padding - KW) // stride + 1
+    K = Cin * KH * KW
+    Kp = (K + 7) // 8 * 8
+    w2 = weight.reshape(Cout, K).float()
+    b = bias.float() if bias is not None else torch.zeros(Cout, device=x.device)
+    if bn_weight is not None:
+        scale = bn_weight.float() / torch.sqrt(running_var.float() + eps)
+        w2 = w2 * scale[:, None]
+        b = (b - running_mean.float()) * scale + bn_bias.float()
+    wp = torch.zeros(Cout, Kp, device=x.device, dtype=torch.bfloat16)
+    wp[:, :K] = w2.to(torch.bfloat16)
+    cols = torch.empty(N * OH * OW, Kp, device=x.device, dtype=torch.bfloat16)
+    lib = _lib.cuda_lib()
+    lib.gf_im2col_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p]
+    lib.gf_im2col_bf16.restype = ctypes.c_int
+    _lib.check_rc(lib.gf_im2col_bf16(x.contiguous().float().data_ptr(), cols.data_ptr(), N, Cin, H, W, KH, KW, stride,
+                                     padding, Kp, _lib.stream_ptr()), "gf_im2col_bf16")
+    y = gemm_raw(cols, False, wp, False, N * OH * OW, Cout, Kp, bias=b.to(torch.bfloat16), relu=relu)
+    return y.view(N, OH, OW, Cout).permute(0, 3, 1, 2).float()
+
+
 def batch_norm_train(x, weight, bias, running_mean, running_var, momentum: float = 0.1, eps: float = 1e-5):
     """Training-mode batch norm over ``[N, C, *]`` that also updates the running statistics."""
     if _gpu_plain(x, weight, bias):

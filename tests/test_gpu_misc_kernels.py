@@ -73,3 +73,23 @@ def test_conv_bn_relu_and_batchnorm(kernel_status):
     y = render.batch_norm_train(x, wt, bs, rm, rv, 0.1, 1e-5)
     yr = F.batch_norm(x, rm2, rv2, wt, bs, True, 0.1, 1e-5)
     assert torch.allclose(y, yr, atol=1e-3) and torch.allclose(rm, rm2, atol=1e-4) and torch.allclose(rv, rv2, atol=1e-3)
+
+
+def test_conv_bn_relu_on_tensor_cores_matches_fp32():
+    import torch.nn.functional as F
+    from ghost_flow_b200.ops import _lib
+    from ghost_flow_b200.ops.render import conv_bn_relu_tensorcore
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    x = torch.randn(4, 16, 20, 18, device=dev)
+    w = torch.randn(32, 16, 3, 3, device=dev) * 0.1
+    b = torch.randn(32, device=dev)
+    g, be = torch.rand(32, device=dev) + 0.5, torch.randn(32, device=dev)
+    mean, var = torch.randn(32, device=dev), torch.rand(32, device=dev) + 0.5
+    y = conv_bn_relu_tensorcore(x, w, b, g, be, mean, var, stride=2, padding=1)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device(dev))
+    ref = torch.relu(F.batch_norm(F.conv2d(x, w, b, 2, 1), mean, var, g, be, False, 0.0, 1e-5))
+    assert y.shape == ref.shape
+    assert ((y - ref).norm() / ref.norm()) < 2e-2
