@@ -68,6 +68,13 @@ def build(args, dev):
         bq, sb = fp8.quantize_rows(b, 0) if mode == 0 else fp8.quantize_block128(b)
         out = torch.empty(M, N, device=dev, dtype=bf)
         return (lambda: fp8.gemm_fp8(aq, sa, bq, sb, mode, out=out)), 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    if k == "gemm_fp8_skinny":
+        from ghost_flow_b200.ops import fp8
+        M, N, K = args.m, args.n, args.k
+        aq, sa = fp8.quantize_rows(torch.randn(M, K, device=dev, dtype=bf), 0)
+        bq, sb = fp8.quantize_rows(torch.randn(N, K, device=dev, dtype=bf), 0)
+        out = torch.empty(M, N, device=dev, dtype=bf)
+        return (lambda: fp8.gemm_fp8(aq, sa, bq, sb, 0, out=out)), 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
     if k == "quant_fp8_rows":
         from ghost_flow_b200.ops import fp8
         x = torch.randn(args.rows, args.cols, device=dev, dtype=bf)

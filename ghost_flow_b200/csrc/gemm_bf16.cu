@@ -593,9 +593,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           } else if (p.split_k > 1) {
             float* wp = p.ws + (long long)row * p.N + col0;
+            if (full && (p.N & 3) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) atomicAdd(wp + j, v[j]);
+              for (int q = 0; q < 8; ++q)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(wp + q * 4), "f"(v[q * 4]),
+                             "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3]) : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) atomicAdd(wp + j, v[j]);
+            }
           } else if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + (ti.c_row_add + row) * p.ldc + col0;
             if (full && ((p.ldc & 3) == 0)) {

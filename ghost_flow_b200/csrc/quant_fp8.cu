@@ -135,7 +135,24 @@ struct F8Params {
   const __nv_bfloat16* bias;
   int tiles_m, tiles_n;
   int* status;
+  // split-K (mode 0, skinny problems): tile index = (k slice, tile); raw partial sums are added into `ws` [M, N]
+  // with vector reductions and a second kernel applies scales and bias.
+  int split_k;
+  float* ws;
 };
+
+// Work item -> tile and k-block range. Returns false when the slice is empty.
+__device__ __forceinline__ bool f8_item(const F8Params& p, int item, int num_kb, int& tm, int& tn, int& kb0, int& nkb) {
+  const int per = p.tiles_m * p.tiles_n;
+  const int ks = item / per;
+  const int t = item - ks * per;
+  tm = t % p.tiles_m;
+  tn = t / p.tiles_m;
+  const int kbs = (num_kb + p.split_k - 1) / p.split_k;
+  kb0 = ks * kbs;
+  nkb = min(kbs, num_kb - kb0);
+  return nkb > 0;
+}
 
 template <int BN>
 struct F8Cfg {
@@ -167,7 +184,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + F8_BK - 1) / F8_BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int cta = blockIdx.x, nctas = gridDim.x;
   // accumulator hand-offs per tile: one (mode 0) or one per k block (mode 1)
   const int drains = MODE == 0 ? 1 : num_kb;
@@ -200,8 +217,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int tm, tn, kb0, nkb;
+        if (!f8_item(p, tile, num_kb, tm, tn, kb0, nkb)) continue;
+        for (int kb = kb0; kb < kb0 + nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             f8_set_status(p.status, GF_ERR_WAIT_EMPTY);
             ok = false;
@@ -226,8 +244,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int it = 0;      // accumulator hand-offs so far
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          const bool first = MODE == 1 || kb == 0;
+        int tm_, tn_, kb0, nkb;
+        if (!f8_item(p, tile, num_kb, tm_, tn_, kb0, nkb)) continue;
+        for (int kb = kb0; kb < kb0 + nkb && ok; ++kb) {
+          const bool first = MODE == 1 || kb == kb0;
           const int buf = it & 1;
           if (first) {
             if (!mbar_wait(&tempty_bar[buf], ((it >> 1) & 1) ^ 1)) {
@@ -257,7 +277,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             stage = 0;
             phase ^= 1;
           }
-          if (MODE == 1 || kb == num_kb - 1) {
+          if (MODE == 1 || kb == kb0 + nkb - 1) {
             umma_commit(&tfull_bar[buf]);
             ++it;
           }
@@ -268,7 +288,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int lane_grp = warp & 3;
     int it = 0;
     for (int tile = cta; tile < num_tiles; tile += nctas) {
-      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      int tm, tn, kb0_, nkb_;
+      if (!f8_item(p, tile, num_kb, tm, tn, kb0_, nkb_)) continue;
       const int row = tm * F8_BM + lane_grp * 32 + lane;
       const int n0 = tn * BN;
       bool ok = true;
@@ -288,7 +309,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
           const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) {
+          if (row < p.M && col0 < p.N && p.split_k > 1) {
+            float* wp = p.ws + (long long)row * p.N + col0;
+            if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+              for (int qd = 0; qd < 8; ++qd)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(wp + qd * 4),
+                             "f"(__uint_as_float(r[qd * 4])), "f"(__uint_as_float(r[qd * 4 + 1])),
+                             "f"(__uint_as_float(r[qd * 4 + 2])), "f"(__uint_as_float(r[qd * 4 + 3])) : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) atomicAdd(wp + j, __uint_as_float(r[j]));
+            }
+          } else if (row < p.M && col0 < p.N) {
             __nv_bfloat16* cp = p.C + (long long)row * p.ldc + col0;
             if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
@@ -396,9 +430,40 @@ static int launch_f8(const CUtensorMap& tmA, const CUtensorMap& tmB, F8Params& p
   p.tiles_m = (p.M + F8_BM - 1) / F8_BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   int grid = sm_count();
-  if (p.tiles_m * p.tiles_n < grid) grid = p.tiles_m * p.tiles_n;
+  if (p.tiles_m * p.tiles_n * p.split_k < grid) grid = p.tiles_m * p.tiles_n * p.split_k;
   kern<<<grid, F8_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+__global__ void f8_splitk_finish_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ C, long long ldc,
+                                        const float* __restrict__ sa, const float* __restrict__ sb,
+                                        const __nv_bfloat16* __restrict__ bias, int M, int N) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int r = (int)(i / N), c = (int)(i % N);
+  float v = ws[i] * sa[r] * sb[c];
+  if (bias) v += __bfloat162float(bias[c]);
+  C[(long long)r * ldc + c] = __float2bfloat16(v);
+}
+
+static float* g_f8_ws[32] = {};
+static size_t g_f8_cap[32] = {};
+static float* f8_workspace(size_t floats) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 32) return nullptr;
+  if (g_f8_cap[dev] < floats) {
+    if (g_f8_ws[dev]) cudaFree(g_f8_ws[dev]);
+    size_t cap = floats < (size_t)(8 << 20) ? (size_t)(8 << 20) : floats;
+    if (cudaMalloc(&g_f8_ws[dev], cap * sizeof(float)) != cudaSuccess) {
+      g_f8_ws[dev] = nullptr;
+      g_f8_cap[dev] = 0;
+      cudaGetLastError();
+      return nullptr;
+    }
+    g_f8_cap[dev] = cap;
+  }
+  return g_f8_ws[dev];
 }
 
 }  // namespace gf
@@ -442,7 +507,28 @@ GF_API int gf_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int 
   F8Params p;
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.sa = sa; p.sb = sb;
   p.bias = (const __nv_bfloat16*)bias; p.status = status;
+  p.split_k = 1; p.ws = nullptr;
   cudaStream_t st = (cudaStream_t)stream_v;
+  if (mode == 0 && M <= 256 && K >= 4096) {
+    // decode-sized: split K until there is about one work item per SM (see the bf16 kernel)
+    const long long tiles = (long long)((M + F8_BM - 1) / F8_BM) * ((N + 255) / 256);
+    int split = (int)(sm_count() / (tiles > 0 ? tiles : 1));
+    if (split > K / 1024) split = K / 1024;
+    if (split > 16) split = 16;
+    float* ws = split >= 2 ? f8_workspace((size_t)M * N) : nullptr;
+    if (ws) {
+      if (cudaMemsetAsync(ws, 0, sizeof(float) * (size_t)M * N, st) != cudaSuccess) return GFH_CUDA;
+      p.split_k = split;
+      p.ws = ws;
+      rc = launch_f8<256, 0>(tmA, tmB, p, st);
+      if (rc) return rc;
+      const long long n = (long long)M * N;
+      f8_splitk_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws, (__nv_bfloat16*)C, ldc, sa, sb,
+                                                                          (const __nv_bfloat16*)bias, M, N);
+      gf::note_extra_launches(1);
+      return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+    }
+  }
   if (mode == 0) return launch_f8<256, 0>(tmA, tmB, p, st);
   if (mode == 1) return launch_f8<128, 1>(tmA, tmB, p, st);
   return GFH_BAD_ARG;

@@ -51,3 +51,20 @@ def test_fp8_gemm_matches_dequantised_reference(mode, M, N, K):
     assert _rel(y, ref) < 6e-3
     # and the quantised product is close to the bf16 one
     assert _rel(y, a.float() @ b.float().t() + bias.float()) < 6e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 5120, 8192), (16, 1280, 8192)])
+def test_fp8_skinny_gemm_split_k(M, N, K):
+    from ghost_flow_b200.ops import _lib, fp8
+
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    aq, sa = fp8.quantize_rows(a, 0)
+    bq, sb = fp8.quantize_rows(b, 0)
+    y = fp8.gemm_fp8(aq, sa, bq, sb, 0, bias)
+    torch.cuda.synchronize()
+    _lib.check_status(a.device)
+    ref = fp8.dequantize(aq, sa, 0) @ fp8.dequantize(bq, sb, 0, weight=True).t() + bias.float()
+    assert _rel(y, ref) < 6e-3
