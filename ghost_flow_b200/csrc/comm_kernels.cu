@@ -376,3 +376,140 @@ GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, l
   allgather_pull_kernel<<<world * blocks_per_shard, 256, 0, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// One-shot all-reduce fused with the residual add and RMSNorm that follow a row-parallel projection in a
+// tensor-parallel decode step. Every rank holds a partial product [rows, d] (bf16) in peer-mapped memory; the
+// kernel of every rank reads all partials, adds the residual stream, writes the new residual h and its normalised
+// copy x (both replicated), so the next column-parallel projection needs no all-gather. One launch replaces
+// reduce-scatter + add + RMSNorm + all-gather.
+//
+// Synchronisation is entirely on the device, which makes the kernel replayable from a CUDA graph: the call number
+// is a device counter (`epoch`, bumped by the last CTA), a rank publishes "my partial of call e is written" with a
+// release store of e into every peer's flag array, and waits (bounded) until all peers' flags reach e. Partials are
+// double-buffered by call parity (given by the host; a rank can be at most one call ahead of a peer).
+namespace gf {
+struct ArPeers {
+  const __nv_bfloat16* partial[8];   // every rank's partial buffer of the current parity
+  int* flags[8];                     // every rank's flag array int[8], indexed by source rank
+};
+
+__global__ void __launch_bounds__(256)
+allreduce_residual_rmsnorm_kernel(ArPeers peers, int world, int rank, int* __restrict__ epoch_counter,
+                                  int* __restrict__ done_counter, const __nv_bfloat16* __restrict__ residual,
+                                  const __nv_bfloat16* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ h_out,
+                                  __nv_bfloat16* __restrict__ x_out, int rows, int d, long long wait_limit,
+                                  int* status) {
+  __shared__ int s_ok;
+  __shared__ float red[32];
+  const int epoch = *reinterpret_cast<volatile int*>(epoch_counter) + 1;
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();          // the partial written by the preceding kernels of this stream
+      for (int r = 0; r < world; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peers.flags[r] + rank), "r"(epoch) : "memory");
+    }
+    int ok = 1;
+    for (int r = 0; r < world && ok; ++r) {
+      long long it = 0;
+      while (true) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(peers.flags[rank] + r) : "memory");
+        if (v >= epoch) break;
+        if (++it > wait_limit) { ok = 0; break; }
+        __nanosleep(32);
+      }
+    }
+    if (!ok && status) atomicCAS(status, 0, GF_ERR_WAIT_PEER);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int nv = d >> 3;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      float sq = 0.f;
+      // pass 1: sum of partials + residual -> h (kept in registers for up to 4 vectors per thread)
+      float hv[4][8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nv) {
+          float acc[8];
+          {
+            const uint4 u = *reinterpret_cast<const uint4*>(residual + (long long)row * d + v * 8);
+            float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
+            acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = c.x; acc[5] = c.y; acc[6] = e.x; acc[7] = e.y;
+          }
+          for (int r = 0; r < world; ++r) {
+            const uint4 u = *reinterpret_cast<const uint4*>(peers.partial[r] + (long long)row * d + v * 8);
+            float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+            acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(h_out + (long long)row * d + v * 8) = o;
+          // the normalisation uses the bf16-rounded h, like a separate RMSNorm kernel reading h would
+          float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), e = unpack_bf16x2(o.w);
+          hv[i][0] = a.x; hv[i][1] = a.y; hv[i][2] = b.x; hv[i][3] = b.y;
+          hv[i][4] = c.x; hv[i][5] = c.y; hv[i][6] = e.x; hv[i][7] = e.y;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sq += hv[i][j] * hv[i][j];
+        }
+      }
+      for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < 8; ++w) tot += red[w];
+      __syncthreads();
+      const float rstd = rsqrtf(tot / (float)d + eps);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nv) {
+          const uint4 wu = *reinterpret_cast<const uint4*>(norm_w + v * 8);
+          float2 a = unpack_bf16x2(wu.x), b = unpack_bf16x2(wu.y), c = unpack_bf16x2(wu.z), e = unpack_bf16x2(wu.w);
+          uint4 o;
+          o.x = pack_bf16x2(hv[i][0] * rstd * a.x, hv[i][1] * rstd * a.y);
+          o.y = pack_bf16x2(hv[i][2] * rstd * b.x, hv[i][3] * rstd * b.y);
+          o.z = pack_bf16x2(hv[i][4] * rstd * c.x, hv[i][5] * rstd * c.y);
+          o.w = pack_bf16x2(hv[i][6] * rstd * e.x, hv[i][7] * rstd * e.y);
+          *reinterpret_cast<uint4*>(x_out + (long long)row * d + v * 8) = o;
+        }
+      }
+    }
+  }
+  // the last CTA advances the call counter (all CTAs have read it by now: they are past the first barrier)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int done = atomicAdd(done_counter, 1);
+    if (done == (int)gridDim.x - 1) {
+      *done_counter = 0;
+      *epoch_counter = epoch;
+      __threadfence();
+    }
+  }
+}
+}  // namespace gf
+
+// partial_ptrs / flag_ptrs: `world` device addresses (peer-mapped). rows x d bf16, d % 8 == 0 and d <= 8192.
+GF_API int gf_allreduce_residual_rmsnorm(const unsigned long long* partial_ptrs, const unsigned long long* flag_ptrs,
+                                         int world, int rank, int* epoch_counter, int* done_counter,
+                                         const void* residual, const void* norm_w, float eps, void* h_out, void* x_out,
+                                         int rows, int d, long long wait_limit, int* status, void* stream) {
+  gf::enter();
+  if (world < 1 || world > 8 || rows <= 0 || (d & 7) || d > 8192) return GFH_BAD_ARG;
+  gf::ArPeers peers;
+  for (int i = 0; i < 8; ++i) {
+    peers.partial[i] = i < world ? reinterpret_cast<const __nv_bfloat16*>(partial_ptrs[i]) : nullptr;
+    peers.flags[i] = i < world ? reinterpret_cast<int*>(flag_ptrs[i]) : nullptr;
+  }
+  int grid = rows < 148 ? rows : 148;
+  gf::allreduce_residual_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+      peers, world, rank, epoch_counter, done_counter, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)norm_w, eps,
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, rows, d, limit_or_default(wait_limit), status);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}

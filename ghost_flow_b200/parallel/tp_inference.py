@@ -24,7 +24,7 @@ from ..models.configs import LLaMAConfig
 from ..ops import fp8 as fp8_ops
 from ..ops import raw
 from ..ops.fused import rope_tables
-from .tp import AllGatherGemm, GemmReduceScatter
+from .tp import AllGatherGemm, GemmReduceScatter, SymmetricWorkspace
 
 
 def _world(group):
@@ -100,6 +100,22 @@ class TPLlamaInference:
         self._load(weights, seed)
         self.pre = _Linears(batch * prompt_len, c.hidden_size, self.device, group, linear)
         self.dec = _Linears(batch, c.hidden_size, self.device, group, linear)
+        # Decode with replicated activations: each row-parallel projection is followed by ONE kernel that all-reduces
+        # the partial products over peer memory, adds the residual and applies the next RMSNorm, so a layer has two
+        # collectives (both fused) instead of four. bf16 weights only; other cases use the sequence-parallel step.
+        self.oneshot = self.world > 1 and self.device.type == "cuda" and linear != "fp8" and c.hidden_size <= 8192
+        if self.oneshot:
+            d = c.hidden_size
+            self.ar_ws = SymmetricWorkspace(2 * batch * d * 2 + 4096, self.device, group or dist.group.WORLD)
+            self.ar_partial = [self.ar_ws.alloc(batch * d, torch.bfloat16).view(batch, d) for _ in range(2)]
+            self.ar_flags = self.ar_ws.alloc(8, torch.int32)
+            import ctypes
+            mk = lambda v: (ctypes.c_ulonglong * len(v))(*[int(x) for x in v])  # noqa: E731
+            self.ar_partial_ptrs = [mk(self.ar_ws.peer_ptrs(t)) for t in self.ar_partial]
+            self.ar_flag_ptrs = mk(self.ar_ws.peer_ptrs(self.ar_flags))
+            self.ar_epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.ar_done = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.ar_calls = 0
         self.cos, self.sin = rope_tables(self.max_len, self.D, c.rope_theta, self.device)
         kv = (batch, self.max_len, self.Hkv * self.D)
         self.kcache = [torch.zeros(kv, dtype=torch.bfloat16, device=self.device) for _ in range(c.num_hidden_layers)]
@@ -184,9 +200,62 @@ class TPLlamaInference:
         a = raw.swiglu_fwd(lin.column(x, L["w13"]))
         return lin.row(a, L["w2"], h)
 
-    def _next_tokens(self, last_hidden):
+    # ------------------------------------------------------------------ decode with replicated activations
+    def _ar_norm(self, partial_idx, h, norm_w):
+        """(h + sum over ranks of partial, RMSNorm of that) in one kernel; see ``gf_allreduce_residual_rmsnorm``."""
+        import ctypes
+        from ..ops import _lib
+        lib = _lib.cuda_lib()
+        if not getattr(lib, "_ar_bound", False):
+            P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+            lib.gf_allreduce_residual_rmsnorm.argtypes = [P, P, I, I, P, P, P, P, F, P, P, I, I, L, P, P]
+            lib.gf_allreduce_residual_rmsnorm.restype = I
+            lib._ar_bound = True
+        B, d = h.shape
+        h_out, x_out = torch.empty_like(h), torch.empty_like(h)
+        _lib.check_rc(lib.gf_allreduce_residual_rmsnorm(
+            self.ar_partial_ptrs[partial_idx], self.ar_flag_ptrs, self.world, self.rank, self.ar_epoch.data_ptr(),
+            self.ar_done.data_ptr(), h.data_ptr(), norm_w.data_ptr(), self.cfg.rms_norm_eps, h_out.data_ptr(),
+            x_out.data_ptr(), B, d, 0, _lib.status_word(self.device).data_ptr(), _lib.stream_ptr()),
+            "gf_allreduce_residual_rmsnorm")
+        return h_out, x_out
+
+    def _decode_oneshot(self, tokens, pos, dev=None):
+        c = self.cfg
+        B = self.B
+        h = self.embed[tokens]
+        x, _, _ = raw.rmsnorm_fwd(h, self.layers[0]["n1"], c.rms_norm_eps)
+        HD, KD = self.Hq * self.D, self.Hkv * self.D
+        cos, sin, off = (self.cos, self.sin, pos) if dev is None else (dev[2], dev[3], 0)
+        for i, L in enumerate(self.layers):
+            qkv = raw.gemm(x, False, L["wqkv"], True)
+            q, k, v = qkv[:, :HD], qkv[:, HD:HD + KD], qkv[:, HD + KD:]
+            raw.rope_(q.unflatten(1, (self.Hq, self.D)), cos, sin, 1, c.rope_interleaved, off)
+            raw.rope_(k.unflatten(1, (self.Hkv, self.D)), cos, sin, 1, c.rope_interleaved, off)
+            kc, vc = self.kcache[i], self.vcache[i]
+            if dev is not None:
+                kc.index_copy_(1, dev[0], k.reshape(B, 1, KD))
+                vc.index_copy_(1, dev[0], v.reshape(B, 1, KD))
+                o = raw.attn_decode(q, kc, vc, dev[1], B, self.Hq, self.Hkv, self.D)
+            else:
+                kc[:, pos].copy_(k)
+                vc[:, pos].copy_(v)
+                o = raw.attn_decode(q, kc, vc, pos + 1, B, self.Hq, self.Hkv, self.D)
+            par = self.ar_calls & 1
+            self.ar_calls += 1
+            raw.gemm(o, False, L["wo"], True, out=self.ar_partial[par])
+            h, x = self._ar_norm(par, h, L["n2"])
+            a = raw.swiglu_fwd(raw.gemm(x, False, L["w13"], True))
+            par = self.ar_calls & 1
+            self.ar_calls += 1
+            raw.gemm(a, False, L["w2"], True, out=self.ar_partial[par])
+            nxt = self.layers[i + 1]["n1"] if i + 1 < len(self.layers) else self.norm
+            h, x = self._ar_norm(par, h, nxt)
+        return x            # already normalised with the final norm
+
+    def _next_tokens(self, last_hidden, normed=False):
         """last_hidden [B, d] (same on all ranks) -> greedy token per sequence through the vocab-parallel head."""
-        x, _, _ = raw.rmsnorm_fwd(last_hidden, self.norm, self.cfg.rms_norm_eps)
+        x = last_hidden if normed else raw.rmsnorm_fwd(last_hidden, self.norm, self.cfg.rms_norm_eps)[0]
         logits = raw.gemm(x, False, self.lm_head, True, out_dtype=torch.float32)
         val, idx = logits.max(1)
         if self.world == 1:
@@ -221,6 +290,9 @@ class TPLlamaInference:
     def decode_step(self, tokens: torch.Tensor, pos: int, dev=None):
         """tokens [B] at position ``pos`` -> next tokens [B]."""
         B, w, r, d = self.B, self.world, self.rank, self.cfg.hidden_size
+        if self.oneshot:
+            tok, self.last_logits = self._next_tokens(self._decode_oneshot(tokens, pos, dev), normed=True)
+            return tok
         lo, hi = r * B // w, (r + 1) * B // w
         h = self.embed[tokens[lo:hi]]
         for i, L in enumerate(self.layers):
