@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--linear", default="fused", choices=["fused", "nccl", "fp8"])
     ap.add_argument("--graph", type=int, default=1, help="replay the decode step from a CUDA graph")
+    ap.add_argument("--decode", default="oneshot", choices=["oneshot", "sp"],
+                    help="oneshot: replicated activations, all-reduce+residual+RMSNorm in one kernel; sp: sequence-parallel")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -55,7 +57,7 @@ def main():
     if a.layers:
         kw["num_hidden_layers"] = a.layers
     cfg = LLaMAConfig(**kw)
-    eng = TPLlamaInference(cfg, a.batch, a.prompt, a.new, dev, linear=a.linear, seed=0)
+    eng = TPLlamaInference(cfg, a.batch, a.prompt, a.new, dev, linear=a.linear, seed=0, decode=a.decode)
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=torch.Generator().manual_seed(0)).to(dev)
 
     def barrier():
@@ -100,7 +102,7 @@ def main():
     if rank == 0:
         params = sum(p.numel() if torch.is_tensor(p) else p[0].numel() for L in eng.layers for p in L.values()) * world
         print(json.dumps({"model": a.model, "layers": cfg.num_hidden_layers, "tp": world, "linear": a.linear, "batch": a.batch,
-                          "prompt_len": a.prompt, "decode_steps_timed": steps, "cuda_graph": bool(a.graph), "block_params": params,
+                          "prompt_len": a.prompt, "decode_steps_timed": steps, "cuda_graph": bool(a.graph), "decode": "oneshot" if eng.oneshot else "sp", "block_params": params,
                           "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(a.batch * a.prompt / prefill_ms * 1e3),
                           "decode_ms_per_step": round(decode_ms, 3), "decode_tokens_per_s": round(a.batch / decode_ms * 1e3),
                           "data": "synthetic token ids, random-init weights", "dtype": "fp8 e4m3 weights+activations" if a.linear == "fp8" else "bf16"}))

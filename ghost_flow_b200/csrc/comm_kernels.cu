@@ -428,34 +428,53 @@ allreduce_residual_rmsnorm_kernel(ArPeers peers, int world, int rank, int* __res
     const int nv = d >> 3;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
       float sq = 0.f;
-      // pass 1: sum of partials + residual -> h (kept in registers for up to 4 vectors per thread)
+      // pass 1: sum of partials + residual -> h (kept in registers for up to 4 vectors per thread). The peer loads
+      // of two vectors (up to 16 loads of 16 bytes) are issued before any of them is used: a peer load costs a
+      // few microseconds of NVLink latency, so they must overlap.
       float hv[4][8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = threadIdx.x + i * 256;
-        if (v < nv) {
-          float acc[8];
-          {
-            const uint4 u = *reinterpret_cast<const uint4*>(residual + (long long)row * d + v * 8);
-            float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
-            acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = c.x; acc[5] = c.y; acc[6] = e.x; acc[7] = e.y;
-          }
-          for (int r = 0; r < world; ++r) {
-            const uint4 u = *reinterpret_cast<const uint4*>(peers.partial[r] + (long long)row * d + v * 8);
-            float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
-            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-            acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
-          }
-          uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-          *reinterpret_cast<uint4*>(h_out + (long long)row * d + v * 8) = o;
-          // the normalisation uses the bf16-rounded h, like a separate RMSNorm kernel reading h would
-          float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), e = unpack_bf16x2(o.w);
-          hv[i][0] = a.x; hv[i][1] = a.y; hv[i][2] = b.x; hv[i][3] = b.y;
-          hv[i][4] = c.x; hv[i][5] = c.y; hv[i][6] = e.x; hv[i][7] = e.y;
+      for (int i0 = 0; i0 < 4; i0 += 2) {
+        uint4 pu[2][8];
+        uint4 ru[2];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sq += hv[i][j] * hv[i][j];
+        for (int k = 0; k < 2; ++k) {
+          const int v = threadIdx.x + (i0 + k) * 256;
+          if (v < nv) {
+            ru[k] = *reinterpret_cast<const uint4*>(residual + (long long)row * d + v * 8);
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              pu[k][r] = r < world ? *reinterpret_cast<const uint4*>(peers.partial[r] + (long long)row * d + v * 8)
+                                   : make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int i = i0 + k;
+          const int v = threadIdx.x + i * 256;
+          if (v < nv) {
+            float acc[8];
+            {
+              float2 a = unpack_bf16x2(ru[k].x), b = unpack_bf16x2(ru[k].y), c = unpack_bf16x2(ru[k].z), e = unpack_bf16x2(ru[k].w);
+              acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = c.x; acc[5] = c.y; acc[6] = e.x; acc[7] = e.y;
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              const uint4 u = pu[k][r];
+              float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
+              acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+              acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4*>(h_out + (long long)row * d + v * 8) = o;
+            // the normalisation uses the bf16-rounded h, like a separate RMSNorm kernel reading h would
+            float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), c = unpack_bf16x2(o.z), e = unpack_bf16x2(o.w);
+            hv[i][0] = a.x; hv[i][1] = a.y; hv[i][2] = b.x; hv[i][3] = b.y;
+            hv[i][4] = c.x; hv[i][5] = c.y; hv[i][6] = e.x; hv[i][7] = e.y;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sq += hv[i][j] * hv[i][j];
+          }
         }
       }
       for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);

@@ -179,14 +179,27 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // Fold `nparts` partial rows of length D; writes bf16 (optionally accumulating into existing bf16).
-__global__ void fold_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nparts,
-                                     int D, int accumulate) {
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+// One CTA per 32 columns: its eight warps stride over the partial rows (each warp reads 128 contiguous bytes per
+// row), then the eight per-warp sums are combined through shared memory. With hundreds of partial rows this keeps
+// 4096 / 32 = 128 CTAs busy instead of 16 threads-per-column chains.
+__global__ void __launch_bounds__(256)
+fold_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nparts, int D,
+                     int accumulate) {
+  __shared__ float sm[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * D + d];
-  if (accumulate) s += __bfloat162float(out[d]);
-  out[d] = __float2bfloat16(s);
+  if (d < D)
+    for (int p = warp; p < nparts; p += 8) s += partial[(long long)p * D + d];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && d < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][lane];
+    if (accumulate) t += __bfloat162float(out[d]);
+    out[d] = __float2bfloat16(t);
+  }
 }
 
 // ------------------------------------------------------------------ LayerNorm forward
@@ -340,7 +353,7 @@ GF_API int gf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const fl
   kern<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, scratch, T, D);
-  fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
+  fold_partials_kernel<<<(D + 31) / 32, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
                                                                           accumulate);
   gf::note_extra_launches(1);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
@@ -367,11 +380,11 @@ GF_API int gf_layernorm_bwd(const void* x, const void* w, const void* dy, const 
   layernorm_bwd_kernel<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, mean, rstd, (__nv_bfloat16*)dx,
       scratch, s2, T, D);
-  fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
+  fold_partials_kernel<<<(D + 31) / 32, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
                                                                           accumulate);
   gf::note_extra_launches(db ? 2 : 1);
   if (db)
-    fold_partials_kernel<<<(D + 255) / 256, 256, 0, (cudaStream_t)stream>>>(s2, (__nv_bfloat16*)db, g, D,
+    fold_partials_kernel<<<(D + 31) / 32, 256, 0, (cudaStream_t)stream>>>(s2, (__nv_bfloat16*)db, g, D,
                                                                             accumulate);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }

@@ -85,7 +85,7 @@ class TPLlamaInference:
     (every rank slices its part), or None for random weights generated shard by shard on the device."""
 
     def __init__(self, cfg: LLaMAConfig, batch: int, prompt_len: int, max_new_tokens: int, device, group=None,
-                 linear: str = "fused", weights: dict | None = None, seed: int = 0):
+                 linear: str = "fused", weights: dict | None = None, seed: int = 0, decode: str = "oneshot"):
         assert linear in ("fused", "nccl", "fp8")
         self.cfg, self.group, self.mode = cfg, group, linear
         self.world, self.rank = _world(group)
@@ -103,7 +103,9 @@ class TPLlamaInference:
         # Decode with replicated activations: each row-parallel projection is followed by ONE kernel that all-reduces
         # the partial products over peer memory, adds the residual and applies the next RMSNorm, so a layer has two
         # collectives (both fused) instead of four. bf16 weights only; other cases use the sequence-parallel step.
-        self.oneshot = self.world > 1 and self.device.type == "cuda" and linear != "fp8" and c.hidden_size <= 8192
+        # ``decode="sp"`` keeps the sequence-parallel step (NCCL all-gather / reduce-scatter around split-K GEMMs).
+        self.oneshot = (decode == "oneshot" and self.world > 1 and self.device.type == "cuda" and linear != "fp8"
+                        and c.hidden_size <= 8192)
         if self.oneshot:
             d = c.hidden_size
             self.ar_ws = SymmetricWorkspace(2 * batch * d * 2 + 4096, self.device, group or dist.group.WORLD)
