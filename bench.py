@@ -115,6 +115,7 @@ class ClockSampler:
 
 def main():
     args = parse_args()
+    args.warmup = max(3, args.warmup)      # timing hygiene: never fewer than three untimed steps
     if args.impl == "reference":
         reference_arm()
         return 0

@@ -776,7 +776,13 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if (tiles < grid - n_copy) grid = tiles + n_copy;
   p.group_m = 0;
-  const int band = p.tiles_m > 16 ? 16 : p.tiles_m;
+  static int band_rows = 0;          // rows of a band of the tile walk; GF_GEMM_BAND overrides the default of 16
+  if (band_rows == 0) {
+    const char* e = getenv("GF_GEMM_BAND");
+    band_rows = e ? atoi(e) : 16;
+    if (band_rows < 1) band_rows = 16;
+  }
+  const int band = p.tiles_m > band_rows ? band_rows : p.tiles_m;
   if (p.rs_world > 0) {
     // row blocks alternate between owners when every owner has whole row blocks; otherwise start after the own rows
     p.rs_interleave = (p.rs_rows_per_rank % BM == 0) ? p.rs_rows_per_rank / BM : 0;
