@@ -109,6 +109,33 @@ def build(args, dev):
         dy = torch.randn_like(x)
         _, rstd, _ = raw.rmsnorm_fwd(x, w, 1e-5)
         return (lambda: raw.rmsnorm_bwd(x, w, dy, rstd)), 0.0, 6.0 * R * C
+    if k == "rope":
+        H, D = args.heads, args.dim
+        x = torch.randn(R, H, D, device=dev, dtype=bf)
+        from ghost_flow_b200.ops.fused import rope_tables
+        cos, sin = rope_tables(args.seq, D, 10000.0, dev)
+        return (lambda: raw.rope_(x, cos, sin, args.seq)), 0.0, 4.0 * R * H * D
+    if k == "swiglu_bwd":
+        gu = torch.randn(R, 2 * C, device=dev, dtype=bf)
+        dy = torch.randn(R, C, device=dev, dtype=bf)
+        return (lambda: raw.swiglu_bwd(gu, dy)), 0.0, 10.0 * R * C
+    if k == "layernorm":
+        from ghost_flow_b200.ops import fused
+        x = torch.randn(R, C, device=dev, dtype=bf)
+        w, b = torch.ones(C, device=dev, dtype=bf), torch.zeros(C, device=dev, dtype=bf)
+        return (lambda: fused.layer_norm(x, w, b, 1e-5)), 0.0, 4.0 * R * C
+    if k == "moe_layer":
+        from ghost_flow_b200.parallel.ep import ExpertParallelMoE
+        T, d, f = args.rows, args.cols, args.k
+        moe = ExpertParallelMoE(d, f, 8, 2, T, dev, seed=1)
+        moe.gate_pad[:8] = (torch.randn(8, d, device=dev) * 0.05).to(bf)
+        x = torch.randn(T, d, device=dev, dtype=bf)
+        dy = torch.randn(T, d, device=dev, dtype=bf) * 0.1
+
+        def step():
+            y, ctx = moe.forward(x)
+            moe.backward(ctx, dy)
+        return step, 2.0 * T * 2 * d * 3 * f * 3, 2.0 * 8 * 3 * d * f * 3
     if k == "swiglu_fwd":
         gu = torch.randn(R, 2 * C, device=dev, dtype=bf)
         return (lambda: raw.swiglu_fwd(gu)), 0.0, 6.0 * R * C
