@@ -383,6 +383,45 @@ __global__ void im2col_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* _
 }
 }  // namespace gf
 
+// Channels-last variant for the bf16 inference path: x [N, H, W, C] bf16 with C a multiple of 8 ->
+// cols [N * OH * OW, KH * KW * C] bf16 with column index (ky * KW + kx) * C + c (the order of a weight stored
+// [Cout, KH, KW, C]). One thread moves one 16-byte group of 8 channels, so both sides are full-width accesses;
+// taps that fall into the padding are written as zeros.
+namespace gf {
+__global__ void im2col_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ cols, int N, int C8, int H,
+                                        int W, int KH, int KW, int OH, int OW, int stride, int pad) {
+  const int per_row = KH * KW * C8;
+  const long long total = (long long)N * OH * OW * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % per_row);
+    const long long row = i / per_row;
+    const int c8 = j % C8, tap = j / C8;
+    const int kx = tap % KW, ky = tap / KW;
+    const int ox = (int)(row % OW), oy = (int)((row / OW) % OH), n = (int)(row / ((long long)OW * OH));
+    const int iy = oy * stride - pad + ky, ix = ox * stride - pad + kx;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = x[(((long long)n * H + iy) * W + ix) * C8 + c8];
+    cols[i] = v;
+  }
+}
+}  // namespace gf
+
+GF_API int gf_im2col_nhwc_bf16(const void* x, void* cols, int N, int C, int H, int W, int KH, int KW, int stride,
+                               int pad, void* stream) {
+  gf::enter();
+  if (C <= 0 || C % 8 || stride <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)cols & 15)) return gf::GFH_BAD_ARG;
+  const int OH = (H + 2 * pad - KH) / stride + 1, OW = (W + 2 * pad - KW) / stride + 1;
+  if (OH <= 0 || OW <= 0) return gf::GFH_BAD_ARG;
+  const long long total = (long long)N * OH * OW * KH * KW * (C / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)gf::sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  gf::im2col_nhwc_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, (uint4*)cols, N, C / 8, H, W, KH, KW, OH, OW, stride, pad);
+  return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
+}
+
 GF_API int gf_im2col_bf16(const float* x, void* cols, int N, int C, int H, int W, int KH, int KW, int stride, int pad,
                           int Kp, void* stream) {
   gf::enter();

@@ -234,6 +234,35 @@ __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, 
     stf(y, i, op == 0 ? av + alpha * bv : (op == 1 ? av * bv : av - alpha * bv));
   }
 }
+// fp32 operands, four elements (16 bytes) per thread iteration.
+__global__ void binary_f32x4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ y,
+                                    long long nvec, int op, float alpha) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 u = a[i], v = b[i];
+    float4 r;
+    if (op == 0) {
+      r = make_float4(u.x + alpha * v.x, u.y + alpha * v.y, u.z + alpha * v.z, u.w + alpha * v.w);
+    } else if (op == 1) {
+      r = make_float4(u.x * v.x, u.y * v.y, u.z * v.z, u.w * v.w);
+    } else {
+      r = make_float4(u.x - alpha * v.x, u.y - alpha * v.y, u.z - alpha * v.z, u.w - alpha * v.w);
+    }
+    y[i] = r;
+  }
+}
+__global__ void chain_fwd_f32x4_kernel(const float4* __restrict__ x, float4* __restrict__ y, long long nvec,
+                                       OpChain chain) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 v = x[i];
+    for (int k = 0; k < chain.n; ++k) {
+      const int op = chain.ops[k];
+      v = make_float4(apply_op(op, v.x), apply_op(op, v.y), apply_op(op, v.z), apply_op(op, v.w));
+    }
+    y[i] = v;
+  }
+}
 __global__ void add_bf16x8_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                                   __nv_bfloat16* __restrict__ y, long long nvec) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
@@ -378,6 +407,9 @@ GF_API int gf_unary_fwd(const void* x, void* y, long long n, int op, int dtype, 
     if (dtype == 1)
       chain_fwd_kernel<__nv_bfloat16><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>(
           (const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, c);
+    else if (n % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0))
+      chain_fwd_f32x4_kernel<<<ew_grid(n / 4, 256), 256, 0, (cudaStream_t)stream>>>((const float4*)x, (float4*)y,
+                                                                                  n / 4, c);
     else
       chain_fwd_kernel<float><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)y, n, c);
   }
@@ -399,6 +431,9 @@ GF_API int gf_op_chain(const void* x, void* y, long long n, const int* ops, int 
   if (dtype == 1)
     chain_fwd_kernel<__nv_bfloat16><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x,
                                                                                       (__nv_bfloat16*)y, n, c);
+  else if (n % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0))
+    chain_fwd_f32x4_kernel<<<ew_grid(n / 4, 256), 256, 0, (cudaStream_t)stream>>>((const float4*)x, (float4*)y, n / 4,
+                                                                                c);
   else
     chain_fwd_kernel<float><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)y, n, c);
   GF_RET();
@@ -413,6 +448,9 @@ GF_API int gf_binary(const void* a, const void* b, void* y, long long n, int op,
   } else if (dtype == 1) {
     binary_kernel<__nv_bfloat16><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, alpha);
+  } else if (n % 4 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)y % 16 == 0)) {
+    binary_f32x4_kernel<<<ew_grid(n / 4, 256), 256, 0, (cudaStream_t)stream>>>((const float4*)a, (const float4*)b,
+                                                                             (float4*)y, n / 4, op, alpha);
   } else {
     binary_kernel<float><<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const float*)a, (const float*)b,
                                                                            (float*)y, n, op, alpha);

@@ -16,3 +16,7 @@ from .geometry import (  # noqa: F401
     MeshConv, MeshEncoder, MeshPool, MeshUtils, MPNNLayer, PointNet, PointNetBackbone, PointNetConfig, PolicyNetwork,
     PPOAgent, QNetwork, REINFORCEAgent, ReplayBuffer, SAGEAggregator, STN3d, ValueNetwork,
 )
+from .vision import (  # noqa: F401
+    VGG, BasicBlock, Bottleneck, ChannelsLastEngine, InvertedResidual, MobileNetV2, ResNet, resnet18, resnet34,
+    resnet50, resnet101, resnet152, vgg11, vgg16, vgg19,
+)

@@ -10,6 +10,7 @@ from .conv import (  # noqa: F401
     AdaptiveAvgPool2d, AvgPool2d, Conv1d, Conv2d, Conv3d, ConvTranspose2d, Flatten, GlobalAvgPool2d,
     GlobalMaxPool2d, MaxPool2d, TransposeConv2d,
 )
+from .fused_conv import ConvBNReLU, fold_batch_norm, fuse_conv_bn_relu  # noqa: F401
 from .loss import (  # noqa: F401
     BCELoss, BCEWithLogitsLoss, CrossEntropyLoss, FocalLoss, HuberLoss, L1Loss, MSELoss, NLLLoss, SmoothL1Loss,
     binary_cross_entropy, binary_cross_entropy_with_logits, contrastive_loss, cosine_embedding_loss, cross_entropy,

@@ -273,6 +273,86 @@ def conv_bn_relu_tensorcore(x, weight, bias, bn_weight, bn_bias, running_mean, r
     return y.view(N, OH, OW, Cout).permute(0, 3, 1, 2).float()
 
 
+# ------------------------------------------------------------------ channels-last bf16 convolution (inference)
+def pack_conv_weight_nhwc(weight, bias=None, cin_pad: int | None = None):
+    """``[Cout, Cin, KH, KW]`` weights -> bf16 ``[Cout, KH * KW * Cp]`` in tap-major, channel-minor order (the column
+    order of :func:`im2col_nhwc`), with ``Cp`` = ``Cin`` rounded up to a multiple of 8 (extra channels are zero).
+    Returns ``(packed_weight, bf16_bias_or_None)``."""
+    cout, cin, kh, kw = weight.shape
+    cp = cin_pad if cin_pad is not None else (cin + 7) // 8 * 8
+    w = torch.zeros(cout, kh, kw, cp, device=weight.device, dtype=torch.bfloat16)
+    w[..., :cin] = weight.detach().permute(0, 2, 3, 1).to(torch.bfloat16)
+    return w.reshape(cout, kh * kw * cp), (bias.detach().to(torch.bfloat16).contiguous() if bias is not None else None)
+
+
+def im2col_nhwc(x, kh: int, kw: int, stride: int, padding: int):
+    """Unfolds a channels-last bf16 tensor ``[N, H, W, C]`` (``C % 8 == 0``) into ``[N * OH * OW, KH * KW * C]``.
+    A 1 x 1 stride-1 unpadded window is the input itself and is returned as a view."""
+    N, H, W, C = x.shape
+    OH, OW = (H + 2 * padding - kh) // stride + 1, (W + 2 * padding - kw) // stride + 1
+    if kh == 1 and kw == 1 and stride == 1 and padding == 0:
+        return x.reshape(N * H * W, C), OH, OW
+    if x.is_cuda:
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and C % 8 == 0
+        cols = torch.empty(N * OH * OW, kh * kw * C, device=x.device, dtype=torch.bfloat16)
+        lib = _lib.cuda_lib()
+        lib.gf_im2col_nhwc_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 8 + [ctypes.c_void_p]
+        lib.gf_im2col_nhwc_bf16.restype = ctypes.c_int
+        _lib.check_rc(lib.gf_im2col_nhwc_bf16(x.data_ptr(), cols.data_ptr(), N, C, H, W, kh, kw, stride, padding,
+                                              _lib.stream_ptr()), "gf_im2col_nhwc_bf16")
+        return cols, OH, OW
+    xp = F.pad(x, (0, 0, padding, padding, padding, padding))
+    taps = [xp[:, ky:ky + (OH - 1) * stride + 1:stride, kx:kx + (OW - 1) * stride + 1:stride, :]
+            for ky in range(kh) for kx in range(kw)]
+    return torch.cat(taps, dim=-1).reshape(N * OH * OW, kh * kw * C), OH, OW
+
+
+def conv2d_nhwc(x, packed_weight, bias, kernel_size, stride: int = 1, padding: int = 0, relu: bool = False,
+                residual=None):
+    """Channels-last convolution for inference: ``x`` is bf16 ``[N, H, W, C]``, ``packed_weight`` comes from
+    :func:`pack_conv_weight_nhwc`; the result is bf16 ``[N, OH, OW, Cout]``. On the GPU this is the gather kernel
+    (skipped for 1 x 1 windows) and one tcgen05 GEMM whose epilogue adds the bias, then ``residual`` (same shape as
+    the result), then applies ReLU - a whole ResNet block tail in one kernel."""
+    kh, kw = kernel_size
+    N = x.shape[0]
+    cout = packed_weight.shape[0]
+    cols, OH, OW = im2col_nhwc(x, kh, kw, stride, padding)
+    M, K = cols.shape
+    res2 = residual.reshape(M, cout) if residual is not None else None
+    if x.is_cuda:
+        from .gemm import gemm_raw
+
+        y = gemm_raw(cols, False, packed_weight, False, M, cout, K, bias=bias, residual=res2, relu=relu)
+    else:
+        y = cols.float() @ packed_weight.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        if res2 is not None:
+            y = y + res2.float()
+        y = (torch.relu(y) if relu else y).to(torch.bfloat16)
+    return y.view(N, OH, OW, cout)
+
+
+def conv_gemm_packed(x, packed_weight, bias, kernel_size, stride: int, padding: int, relu: bool):
+    """NCHW front end of :func:`conv2d_nhwc` for the ``ConvBNReLU`` layer. ``packed_weight`` is bf16
+    ``[Cout, Cin * KH * KW]`` in the layout of a flattened NCHW weight, zero-padded to a multiple of 8 columns; the
+    input goes through the fp32 gather kernel. Returns a bf16 NCHW-shaped tensor (channels-last strides)."""
+    from .gemm import gemm_raw
+
+    N, Cin, H, W = x.shape
+    kh, kw = kernel_size
+    OH, OW = (H + 2 * padding - kh) // stride + 1, (W + 2 * padding - kw) // stride + 1
+    cout, kp = packed_weight.shape
+    cols = torch.empty(N * OH * OW, kp, device=x.device, dtype=torch.bfloat16)
+    lib = _lib.cuda_lib()
+    lib.gf_im2col_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p]
+    lib.gf_im2col_bf16.restype = ctypes.c_int
+    _lib.check_rc(lib.gf_im2col_bf16(x.contiguous().float().data_ptr(), cols.data_ptr(), N, Cin, H, W, kh, kw, stride,
+                                     padding, kp, _lib.stream_ptr()), "gf_im2col_bf16")
+    y = gemm_raw(cols, False, packed_weight, False, N * OH * OW, cout, kp, bias=bias, relu=relu)
+    return y.view(N, OH, OW, cout).permute(0, 3, 1, 2)
+
+
 def batch_norm_train(x, weight, bias, running_mean, running_var, momentum: float = 0.1, eps: float = 1e-5):
     """Training-mode batch norm over ``[N, C, *]`` that also updates the running statistics."""
     if _gpu_plain(x, weight, bias):

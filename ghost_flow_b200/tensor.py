@@ -16,6 +16,7 @@ import torch
 
 from .dtype import DType, to_torch_dtype
 from . import ops as _ops
+from .ops import elementwise as _ew
 
 _DEFAULT_DEVICE = torch.device("cpu")
 
@@ -239,11 +240,15 @@ class Tensor:
     def _bin(self, other, fn):
         return Tensor(fn(self.data, _unwrap(other)))
 
-    def __add__(self, o): return self._bin(o, torch.add)
+    def _ew(self, other, op):
+        """add / sub / mul of two dense same-shape CUDA tensors runs the library's element-wise kernel."""
+        return Tensor(_ew.binary(self.data, _unwrap(other), op))
+
+    def __add__(self, o): return self._ew(o, "add")
     def __radd__(self, o): return self._bin(o, torch.add)
-    def __sub__(self, o): return self._bin(o, torch.sub)
+    def __sub__(self, o): return self._ew(o, "sub")
     def __rsub__(self, o): return Tensor(torch.sub(_as_t(o, self.data), self.data))
-    def __mul__(self, o): return self._bin(o, torch.mul)
+    def __mul__(self, o): return self._ew(o, "mul")
     def __rmul__(self, o): return self._bin(o, torch.mul)
     def __truediv__(self, o): return self._bin(o, torch.div)
     def __rtruediv__(self, o): return Tensor(torch.div(_as_t(o, self.data), self.data))
@@ -291,11 +296,11 @@ class Tensor:
     def contiguous(self): return Tensor(self.data.contiguous())
 
     # ------------------------------------------------------------------ activations
-    def relu(self): return Tensor(_ops.unary(self.data, "relu"))
-    def sigmoid(self): return Tensor(_ops.unary(self.data, "sigmoid"))
-    def tanh(self): return Tensor(_ops.unary(self.data, "tanh"))
-    def gelu(self): return Tensor(_ops.unary(self.data, "gelu"))
-    def silu(self): return Tensor(_ops.unary(self.data, "silu"))
+    def relu(self): return Tensor(_ew.unary_any(self.data, "relu"))
+    def sigmoid(self): return Tensor(_ew.unary_any(self.data, "sigmoid"))
+    def tanh(self): return Tensor(_ew.unary_any(self.data, "tanh"))
+    def gelu(self): return Tensor(_ew.unary_any(self.data, "gelu"))
+    def silu(self): return Tensor(_ew.unary_any(self.data, "silu"))
     def leaky_relu(self, slope=0.01): return Tensor(torch.nn.functional.leaky_relu(self.data, slope))
     def elu(self, alpha=1.0): return Tensor(torch.nn.functional.elu(self.data, alpha))
     def selu(self): return Tensor(torch.selu(self.data))
@@ -305,13 +310,26 @@ class Tensor:
     def hardtanh(self, lo=-1.0, hi=1.0): return Tensor(torch.nn.functional.hardtanh(self.data, lo, hi))
     def hardsigmoid(self): return Tensor(torch.nn.functional.hardsigmoid(self.data))
     def hardswish(self): return Tensor(torch.nn.functional.hardswish(self.data))
-    def softmax(self, dim=-1): return Tensor(torch.softmax(self.data, dim))
-    def log_softmax(self, dim=-1): return Tensor(torch.log_softmax(self.data, dim))
+    def softmax(self, dim=-1):
+        if dim in (-1, self.data.dim() - 1) and self.data.shape[-1] >= 32:
+            return Tensor(_ew.softmax_rows(self.data))
+        return Tensor(torch.softmax(self.data, dim))
+
+    def log_softmax(self, dim=-1):
+        if dim in (-1, self.data.dim() - 1) and self.data.shape[-1] >= 32:
+            return Tensor(_ew.softmax_rows(self.data, log=True))
+        return Tensor(torch.log_softmax(self.data, dim))
 
     # ------------------------------------------------------------------ reductions
-    def sum(self): return Tensor(self.data.sum())
+    def _full_reduce(self, mode):
+        d = self.data
+        if d.is_cuda and d.is_floating_point():
+            return Tensor(_ew.reduce_all(d, mode).to(d.dtype))
+        return Tensor(d.sum() if mode == "sum" else d.max())
+
+    def sum(self): return self._full_reduce("sum")
     def mean(self): return Tensor(self.data.mean())
-    def max(self): return Tensor(self.data.max())
+    def max(self): return self._full_reduce("max")
     def min(self): return Tensor(self.data.min())
     def prod(self): return Tensor(self.data.prod())
     def var(self, unbiased=False): return Tensor(self.data.var(unbiased=unbiased))

@@ -303,3 +303,39 @@ def test_skinny_gemm_split_k_matches_fp32(M, N, K):
     _lib.check_status(a.device)
     ref = a.float() @ w.float().t() + bias.float() + res.float()
     assert ((y.float() - ref).norm() / ref.norm()) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_tensor_api_elementwise_reductions_softmax(dtype, kernel_status):
+    """Tensor add / sub / mul, activations, full sum / max and row softmax run the library kernels."""
+    import torch.nn.functional as F
+
+    import ghost_flow_b200 as gf
+    from ghost_flow_b200.ops import _lib
+
+    torch.manual_seed(0)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    for n in (10_000_000, 1003):
+        a, b = torch.randn(n, device=DEV, dtype=dtype), torch.randn(n, device=DEV, dtype=dtype)
+        ta, tb = gf.Tensor(a), gf.Tensor(b)
+        before = _lib.launch_count()
+        got = {"add": ta + tb, "sub": ta - tb, "mul": ta * tb, "relu": ta.relu(), "sigmoid": ta.sigmoid(),
+               "tanh": ta.tanh(), "gelu": ta.gelu(), "silu": ta.silu()}
+        assert _lib.launch_count() - before >= len(got)
+        a32, b32 = a.float(), b.float()
+        want = {"add": a32 + b32, "sub": a32 - b32, "mul": a32 * b32, "relu": torch.relu(a32),
+                "sigmoid": torch.sigmoid(a32), "tanh": torch.tanh(a32), "gelu": F.gelu(a32, approximate="tanh"),
+                "silu": F.silu(a32)}
+        for k in got:
+            assert got[k].data.dtype == dtype
+            assert torch.allclose(got[k].data.float(), want[k], **tol), k
+        s, m = ta.sum().data.float(), ta.max().data.float()
+        assert torch.allclose(s, a32.sum(), atol=0.5 if dtype == torch.float32 else 40.0, rtol=1e-2)
+        assert torch.allclose(m, a32.max(), **tol)
+    for rows, cols in ((64, 1000), (3, 50257), (257, 33)):
+        x = torch.randn(rows, cols, device=DEV, dtype=dtype) * 3
+        t = gf.Tensor(x)
+        assert torch.allclose(t.softmax(-1).data.float(), torch.softmax(x.float(), -1),
+                              atol=1e-5 if dtype == torch.float32 else 4e-3)
+        assert torch.allclose(t.log_softmax(1).data.float(), torch.log_softmax(x.float(), -1),
+                              atol=1e-4 if dtype == torch.float32 else 8e-2)

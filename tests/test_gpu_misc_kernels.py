@@ -93,3 +93,52 @@ def test_conv_bn_relu_on_tensor_cores_matches_fp32():
     ref = torch.relu(F.batch_norm(F.conv2d(x, w, b, 2, 1), mean, var, g, be, False, 0.0, 1e-5))
     assert y.shape == ref.shape
     assert ((y - ref).norm() / ref.norm()) < 2e-2
+
+
+def test_channels_last_conv_matches_fp32(kernel_status):
+    """Gather kernel + tcgen05 GEMM with bias, shortcut and ReLU in the epilogue against conv2d in fp32."""
+    from ghost_flow_b200.ops.render import conv2d_nhwc, im2col_nhwc, pack_conv_weight_nhwc
+
+    torch.manual_seed(0)
+    for (N, C, H, W, Co, k, s, p) in ((3, 16, 19, 23, 64, 3, 1, 1), (2, 8, 33, 33, 24, 7, 2, 3), (4, 64, 14, 14, 128, 1, 1, 0),
+                                      (2, 32, 15, 15, 64, 1, 2, 0), (2, 3, 32, 32, 16, 3, 1, 1)):
+        x = torch.randn(N, C, H, W, device=DEV)
+        w = torch.randn(Co, C, k, k, device=DEV) / (C * k * k) ** 0.5
+        b = torch.randn(Co, device=DEV)
+        wp, bp = pack_conv_weight_nhwc(w, b)
+        Cp = wp.shape[1] // (k * k)
+        xn = torch.zeros(N, H, W, Cp, device=DEV, dtype=torch.bfloat16)
+        xn[..., :C] = x.permute(0, 2, 3, 1)
+        xr = xn[..., :C].float().permute(0, 3, 1, 2)
+        ref = F.conv2d(xr, w.bfloat16().float(), b.bfloat16().float(), s, p)
+        cols, OH, OW = im2col_nhwc(xn, k, k, s, p)
+        cols_cpu, _, _ = im2col_nhwc(xn.cpu(), k, k, s, p)
+        assert torch.equal(cols.cpu(), cols_cpu)
+        res = torch.randn(N, OH, OW, Co, device=DEV).bfloat16()
+        y = conv2d_nhwc(xn, wp, bp, (k, k), s, p, relu=True, residual=res)
+        want = torch.relu(ref + res.float().permute(0, 3, 1, 2))
+        got = y.float().permute(0, 3, 1, 2)
+        assert got.shape == want.shape
+        assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (got - want).abs().max()
+
+
+def test_resnet_serving_program_matches_the_model():
+    from ghost_flow_b200.models import resnet18, resnet50
+    from ghost_flow_b200.nn import fuse_conv_bn_relu
+
+    torch.manual_seed(0)
+    for make in (lambda: resnet18(16, small_input=True), lambda: resnet50(16, width=16)):
+        m = make().to(DEV)
+        for mod in m.modules():
+            if hasattr(mod, "running_mean"):
+                mod.running_mean.normal_(0, 0.1)
+                mod.running_var.uniform_(0.5, 1.5)
+        m.eval()
+        x = torch.randn(4, 3, 64, 64, device=DEV)
+        with torch.no_grad():
+            ref = m(x)
+            got = m.compile_inference()(x)
+            assert (got - ref).abs().max() <= 0.05 * ref.abs().max() + 0.05
+            assert fuse_conv_bn_relu(m) > 0
+            fused = m(x)
+            assert (fused - ref).abs().max() <= 0.05 * ref.abs().max() + 0.05

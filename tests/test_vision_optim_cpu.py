@@ -1,0 +1,95 @@
+"""Vision models, Conv+BN+ReLU folding and the RMSprop / AdaGrad / Adadelta optimizers on CPU."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from ghost_flow_b200 import nn, optim
+from ghost_flow_b200.models import MobileNetV2, resnet18, resnet50, vgg11
+
+
+def _randomise_bn(m):
+    for mod in m.modules():
+        if hasattr(mod, "running_mean"):
+            mod.running_mean.normal_(0, 0.1)
+            mod.running_var.uniform_(0.5, 1.5)
+            mod.weight.data.uniform_(0.5, 1.5)
+            mod.bias.data.normal_(0, 0.1)
+
+
+def test_fold_batch_norm_is_exact():
+    torch.manual_seed(0)
+    conv, bn = nn.Conv2d(5, 8, 3, 2, 1), nn.BatchNorm2d(8)
+    _randomise_bn(bn)
+    bn.eval()
+    x = torch.randn(2, 5, 9, 9)
+    want = torch.relu(bn(conv(x)))
+    fused = nn.ConvBNReLU(conv, bn)
+    assert torch.allclose(fused(x), want, atol=1e-5)
+    assert torch.allclose(nn.ConvBNReLU(conv, bn, relu=False)(x), bn(conv(x)), atol=1e-5)
+    w, b = nn.fold_batch_norm(conv.weight, conv.bias, bn.weight, bn.bias, bn.running_mean, bn.running_var, bn.eps)
+    assert torch.allclose(F.conv2d(x, w, b, 2, 1), bn(conv(x)), atol=1e-5)
+
+
+@pytest.mark.parametrize("make", [lambda: resnet18(10, small_input=True), lambda: resnet50(10, width=16),
+                                  lambda: vgg11(10, hidden=32, pool_size=1)])
+def test_fused_model_matches_unfused(make):
+    torch.manual_seed(0)
+    m = make()
+    _randomise_bn(m)
+    m.eval()
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        want = m(x)
+        assert nn.fuse_conv_bn_relu(m) > 0
+        assert not any(isinstance(mod, nn.BatchNorm2d) for mod in m.modules())
+        got = m(x)
+    assert torch.allclose(got, want, atol=1e-3, rtol=1e-3)
+
+
+def test_channels_last_engine_on_cpu_matches_model():
+    torch.manual_seed(0)
+    m = resnet18(10, small_input=True)
+    _randomise_bn(m)
+    m.eval()
+    x = torch.randn(2, 3, 16, 16)
+    with torch.no_grad():
+        want, got = m(x), m.compile_inference()(x)
+    assert (got - want).abs().max() <= 0.03 * want.abs().max() + 0.03
+
+
+def test_resnet_trains_and_mobilenet_runs():
+    torch.manual_seed(0)
+    m = resnet18(4, small_input=True, width=8)
+    opt = optim.SGD(m.parameters(), lr=0.05, momentum=0.9)
+    x, y = torch.randn(8, 3, 16, 16), torch.randint(0, 4, (8,))
+    losses = []
+    for _ in range(8):
+        opt.zero_grad()
+        loss = F.cross_entropy(m(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < losses[0]
+    assert m.bn1.num_batches_tracked.item() == 8
+    assert MobileNetV2(7, 0.5).eval()(torch.randn(1, 3, 64, 64)).shape == (1, 7)
+
+
+@pytest.mark.parametrize("ours,theirs,kw", [
+    (optim.RMSprop, torch.optim.RMSprop, dict(lr=0.01, momentum=0.9, centered=True, weight_decay=0.01)),
+    (optim.RMSprop, torch.optim.RMSprop, dict(lr=0.01, alpha=0.9)),
+    (optim.AdaGrad, torch.optim.Adagrad, dict(lr=0.1, lr_decay=0.1, weight_decay=0.01)),
+    (optim.Adadelta, torch.optim.Adadelta, dict(lr=1.0, rho=0.9, weight_decay=0.01)),
+])
+def test_extra_optimizers_follow_the_textbook_updates(ours, theirs, kw):
+    torch.manual_seed(0)
+    a = [torch.randn(5, 3, requires_grad=True), torch.randn(7, requires_grad=True)]
+    b = [t.detach().clone().requires_grad_() for t in a]
+    oa, ob = ours(a, **kw), theirs(b, **kw)
+    for _ in range(6):
+        for ps, o in ((a, oa), (b, ob)):
+            o.zero_grad()
+            sum(((p * p).sum() + p.sin().sum()) for p in ps).backward()
+            o.step()
+    for p, q in zip(a, b):
+        assert torch.allclose(p, q, atol=1e-6)
+    assert oa.get_lr() == kw["lr"]
