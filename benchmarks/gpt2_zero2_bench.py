@@ -36,6 +36,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--stage", type=int, default=2)
+    ap.add_argument("--comm", default="nccl", choices=["nccl", "fused"],
+                    help="fused: gradient reduce-scatter + AdamW in one peer-memory kernel, pull all-gather")
     a = ap.parse_args()
     cuda = torch.cuda.is_available()
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -53,7 +55,8 @@ def main():
     model = GPTForCausalLM(cfg)
     model = model.to(dev, torch.bfloat16 if cuda else torch.float32)
     opt = ZeRoOptimizer(model.parameters(), ZeRoConfig(stage=ZeRoStage(a.stage), world_size=world, rank=rank, lr=3e-4,
-                                                       betas=(0.9, 0.95), weight_decay=0.1, bucket_size=50_000_000))
+                                                       betas=(0.9, 0.95), weight_decay=0.1, bucket_size=50_000_000),
+                        comm=a.comm if (cuda and world > 1) else "nccl")
     mb = a.global_batch // world
     g = torch.Generator().manual_seed(1 + rank)
 
@@ -97,7 +100,7 @@ def main():
     if rank == 0:
         n_params = sum(p.numel() for p in model.parameters())
         print(json.dumps({"metric": "GPT-2 ZeRO-%d train tokens/s" % a.stage, "model": a.model, "params": n_params, "n_gpus": world,
-                          "global_batch": a.global_batch, "seq_len": a.seq, "ms_per_step": round(float(t), 3),
+                          "global_batch": a.global_batch, "seq_len": a.seq, "comm": a.comm if world > 1 else "none", "ms_per_step": round(float(t), 3),
                           "value": round(a.global_batch * a.seq / float(t) * 1e3), "unit": "tokens/s",
                           "loss": round(float(loss), 4), "dtype": "bf16" if cuda else "fp32",
                           "memory_savings_ratio": round(opt.memory_savings_ratio(), 2),

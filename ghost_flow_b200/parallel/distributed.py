@@ -290,7 +290,16 @@ class ZeRoOptimizer:
     between steps (``gather_parameters`` / ``release_parameters`` bracket forward+backward).
     """
 
-    def __init__(self, params, config: ZeRoConfig | None = None, group=None):
+    # signal-pad layout of the fused path (int32 indices, 8 per bucket, one slot per writer rank)
+    _PAD_READY, _PAD_CONSUMED, _PAD_VERSION, _MAX_FUSED_BUCKETS = 1024, 2048, 3072, 128
+
+    def __init__(self, params, config: ZeRoConfig | None = None, group=None, comm: str = "nccl"):
+        """``comm="fused"`` (bf16 CUDA parameters, 2 to 8 ranks of one NVSwitch box): the gradient buckets live
+        in symmetric memory and ``step()`` runs, per bucket, ONE kernel that reads this rank's slice of every
+        rank's gradients over NVLink, averages it and applies AdamW to the owned shard (``gf_rs_adamw_fused``),
+        then a pull all-gather of the updated bf16 shards (``gf_allgather_pull``); ranks order themselves with
+        release/acquire flags, every wait is bounded. ``comm="nccl"`` uses reduce-scatter / all-gather collectives
+        around the flat AdamW kernel."""
         self.config = config or ZeRoConfig.default()
         self.group = group
         self.world, self.rank = _world(group)
@@ -299,24 +308,51 @@ class ZeRoOptimizer:
         self.params = [p for p in params if p.requires_grad]
         self.step_count = 0
         self.buckets = []
-        cur, n = [], 0
+        groups, cur, n = [], [], 0
         for p in self.params:
             if cur and (n + p.numel() > self.config.bucket_size or cur[0].dtype != p.dtype):
-                self._make_bucket(cur)
+                groups.append(cur)
                 cur, n = [], 0
             cur.append(p)
             n += p.numel()
         if cur:
-            self._make_bucket(cur)
+            groups.append(cur)
+        self._fc = None
+        if comm == "fused":
+            ok = (2 <= self.world <= 8 and len(groups) <= self._MAX_FUSED_BUCKETS
+                  and all(p.is_cuda and p.dtype == torch.bfloat16 for p in self.params))
+            if not ok:
+                raise RuntimeError("comm='fused' needs bf16 CUDA parameters, 2..8 ranks and at most "
+                                   f"{self._MAX_FUSED_BUCKETS} buckets")
+            from .symm import FusedComm
+
+            self._fc = FusedComm(self.params[0].device, group)
+            total = 0
+            for g in groups:
+                padded = self._padded(sum(p.numel() for p in g))
+                total += (padded * 2 + 255) // 256 * 256 + (padded // self.world * 2 + 255) // 256 * 256
+            self._fc.reserve(total)
+        elif comm != "nccl":
+            raise ValueError(f"unknown comm {comm!r}")
+        for g in groups:
+            self._make_bucket(g)
         self._offloaded = False
+
+    def _padded(self, n: int) -> int:
+        return (n + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
 
     def _make_bucket(self, ps):
         dev, dt = ps[0].device, ps[0].dtype
         n = sum(p.numel() for p in ps)
-        padded = (n + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
+        padded = self._padded(n)
         shard = padded // self.world
         flat_p = torch.zeros(padded, dtype=dt, device=dev)
-        flat_g = torch.zeros(padded, dtype=dt, device=dev)
+        if self._fc is not None:
+            flat_g = self._fc.alloc(padded, dt)
+            shard_lp = self._fc.alloc(shard, dt)
+        else:
+            flat_g = torch.zeros(padded, dtype=dt, device=dev)
+            shard_lp = None
         off = 0
         for p in ps:
             flat_p[off:off + p.numel()].copy_(p.data.reshape(-1))
@@ -326,7 +362,10 @@ class ZeRoOptimizer:
         lo = self.rank * shard
         b = {"params": ps, "n": n, "padded": padded, "shard": shard, "flat_p": flat_p, "flat_g": flat_g,
              "master": flat_p[lo:lo + shard].float().clone(), "m": torch.zeros(shard, device=dev),
-             "v": torch.zeros(shard, device=dev), "g_shard": torch.zeros(shard, dtype=dt, device=dev)}
+             "v": torch.zeros(shard, device=dev), "g_shard": torch.zeros(shard, dtype=dt, device=dev),
+             "shard_lp": shard_lp}
+        if shard_lp is not None:
+            shard_lp.copy_(flat_p[lo:lo + shard])
         self.buckets.append(b)
 
     # ---- partition queries (reference names)
@@ -365,9 +404,49 @@ class ZeRoOptimizer:
         that parameter views stay usable; a rank must not read foreign slices until the next gather)."""
 
     # ---- step
+    def _step_fused(self):
+        """Per bucket: tell the peers that my gradients are complete; one kernel = wait for everybody's gradients,
+        sum my slice over peer memory, AdamW on my shard; pull every rank's new bf16 shard into the parameter
+        buffer; wait until the peers have read my gradients, so that the next backward may overwrite them."""
+        from ..ops import _lib
+
+        c, fc = self.config, self._fc
+        self.step_count += 1
+        t, W, R = self.step_count, self.world, self.rank
+        status, stream = _lib.status_word(fc.device).data_ptr(), _lib.stream_ptr()
+        # waits give up after about 2 s; the first step gets about 13 s, since ranks reach it with start-up skew
+        limit = (1 << 27) if t == 1 else 0
+        with torch.cuda.device(fc.device):
+            for i in range(len(self.buckets)):
+                _lib.check_rc(fc.lib.gf_signal_peers(fc.pad_ptrs, W, R, self._PAD_READY + 8 * i, t, stream),
+                              "gf_signal_peers")
+            for i, b in enumerate(self.buckets):
+                rc = fc.lib.gf_rs_adamw_fused(
+                    fc.peer_ptrs(b["flat_g"]), fc.mc_ptr(b["flat_g"]), fc.pad_ptrs, W, R, R * b["shard"], b["shard"],
+                    b["master"].data_ptr(), b["m"].data_ptr(), b["v"].data_ptr(), b["shard_lp"].data_ptr(),
+                    float(c.lr), float(c.betas[0]), float(c.betas[1]), float(c.eps), float(c.weight_decay), t,
+                    1.0 / W, self._PAD_READY + 8 * i, t, self._PAD_CONSUMED + 8 * i, t, self._PAD_VERSION + 8 * i, t,
+                    fc.rs_counter.data_ptr(), 0, limit, status, stream)
+                _lib.check_rc(rc, "gf_rs_adamw_fused")
+            for i, b in enumerate(self.buckets):
+                fc.ag_epoch += 1
+                rc = fc.lib.gf_allgather_pull(
+                    fc.peer_ptrs(b["shard_lp"]), b["flat_p"].data_ptr(), b["shard"], W, R, fc.pad.data_ptr(),
+                    self._PAD_VERSION + 8 * i, t, fc.ag_ready.data_ptr(), fc.ag_epoch, fc.ag_counters.data_ptr(),
+                    max(8, 256 // W), limit, status, stream)
+                _lib.check_rc(rc, "gf_allgather_pull")
+            for i in range(len(self.buckets)):
+                _lib.check_rc(fc.lib.gf_wait_flags(fc.pad.data_ptr(), self._PAD_CONSUMED + 8 * i, W, t, limit, status,
+                                                   stream), "gf_wait_flags")
+
     def step(self):
         if self._offloaded:
             self.load_from_cpu()
+        if self._fc is not None:
+            self._step_fused()
+            if self.config.cpu_offload:
+                self.offload_to_cpu()
+            return
         c = self.config
         self.step_count += 1
         self.reduce_scatter_gradients()
@@ -435,6 +514,8 @@ class ZeRoOptimizer:
                 b[k].copy_(s[k])
             lo = self.rank * b["shard"]
             b["flat_p"][lo:lo + b["shard"]].copy_(b["master"].to(b["flat_p"].dtype))
+            if b.get("shard_lp") is not None:
+                b["shard_lp"].copy_(b["flat_p"][lo:lo + b["shard"]])
         self.all_gather_parameters()
 
 

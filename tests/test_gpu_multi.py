@@ -100,3 +100,24 @@ def test_tensor_parallel_inference_matches_single_gpu(tmp_path):
         assert res[f"{mode}_logit_rel"] < 3e-2 and res[f"{mode}_first_token_agreement"] == 1.0, res
         assert res[f"{mode}_token_agreement"] >= 0.75, res
     assert res["fp8_logit_rel"] < 0.15, res
+
+
+def test_zero2_reduce_scatter_fused_with_adamw_matches_nccl(tmp_path):
+    """Generic ZeRO-2 optimizer: per bucket one peer-memory kernel (gradient reduce-scatter + AdamW) and a pull
+    all-gather, against NCCL reduce-scatter / all-gather around the flat AdamW kernel."""
+    _need(2)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    res = {}
+    for kind, port in (("fused", 29761), ("nccl", 29763)):
+        out = str(tmp_path / f"z2_{kind}.pt")
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                            "--master-addr", "127.0.0.1", "--master-port", str(port),
+                            os.path.join(HERE, "_zero2_worker.py"), kind, out, "6"],
+                           env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+        res[kind] = torch.load(out)
+    assert res["fused"]["fused"] and not res["nccl"]["fused"] and res["fused"]["buckets"] >= 2
+    for a, b in zip(res["fused"]["losses"], res["nccl"]["losses"]):
+        assert abs(a - b) < 3e-2, (res["fused"]["losses"], res["nccl"]["losses"])
+    assert res["fused"]["losses"][-1] < res["fused"]["losses"][0]
+    assert (res["fused"]["w"] - res["nccl"]["w"]).norm() / res["nccl"]["w"].norm() < 2e-2
