@@ -482,3 +482,38 @@ GF_API int gf_softmax_rows(const void* x, void* y, int rows, int cols, int log_m
                                                                    log_mode);
   GF_RET();
 }
+
+// ------------------------------------------------------------------ fp32 -> (hi, lo) bf16 split for 3-term GEMMs
+// x = hi + lo + O(2^-16 |x|) with hi = bf16(x), lo = bf16(x - hi). An fp32 product A B is then approximated to
+// about 2^-16 relative by hi_A hi_B + hi_A lo_B + lo_A hi_B, which is ONE bf16 GEMM over a three times longer
+// contraction: A' = [hi_A | hi_A | lo_A] (columns), B' = [hi_B ; lo_B ; hi_B] (rows). This kernel writes x's three
+// copies into such a buffer: copy j of element (r, c) lands at out[r * out_pitch + c + off[j]], and copy
+// `lo_slot` (1 or 2) is the low part.
+namespace gf {
+__global__ void split_bf16_cat_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long rows,
+                                      int cols, long long in_pitch, long long out_pitch, long long off1, long long off2,
+                                      int lo_slot) {
+  const long long total = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int c = (int)(i - r * cols);
+    const float v = x[r * in_pitch + c];
+    const __nv_bfloat16 hi = __float2bfloat16(v);
+    const __nv_bfloat16 lo = __float2bfloat16(v - __bfloat162float(hi));
+    __nv_bfloat16* o = out + r * out_pitch + c;
+    o[0] = hi;
+    o[off1] = lo_slot == 1 ? lo : hi;
+    o[off2] = lo_slot == 2 ? lo : hi;
+  }
+}
+}  // namespace gf
+
+GF_API int gf_split_bf16_cat(const float* x, void* out, long long rows, int cols, long long in_pitch,
+                             long long out_pitch, long long off1, long long off2, int lo_slot, void* stream) {
+  gf::enter();
+  if (rows <= 0 || cols <= 0 || (lo_slot != 1 && lo_slot != 2)) return GFH_BAD_ARG;
+  split_bf16_cat_kernel<<<ew_grid(rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(
+      x, (__nv_bfloat16*)out, rows, cols, in_pitch, out_pitch, off1, off2, lo_slot);
+  GF_RET();
+}

@@ -442,7 +442,8 @@ class CuBlas:
 
     def sgemm(self, a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, beta: float = 0.0, c: torch.Tensor | None = None):
         from ..ops.gemm import matmul as gf_matmul
-        y = gf_matmul(a, b) * alpha if a.dtype == torch.bfloat16 else alpha * (a @ b)
+        y = gf_matmul(a, b)  # bf16: tcgen05 kernel; fp32: the same kernel over hi/lo bf16 splits
+        y = y if alpha == 1.0 else y * alpha
         return y if c is None or beta == 0.0 else y + beta * c
 
     def saxpy(self, alpha: float, x: torch.Tensor, y: torch.Tensor): return y.add_(x, alpha=alpha)

@@ -123,8 +123,8 @@ class ResNet(Module):
     def forward(self, x):
         return self.fc(self.avgpool(self.features(x)).flatten(1))
 
-    def compile_inference(self) -> "ChannelsLastEngine":
-        return ChannelsLastEngine(self)
+    def compile_inference(self, cuda_graph: bool = False) -> "ChannelsLastEngine":
+        return ChannelsLastEngine(self, cuda_graph=cuda_graph)
 
 
 def resnet18(num_classes=1000, **kw): return ResNet(BasicBlock, [2, 2, 2, 2], num_classes, **kw)
@@ -165,9 +165,16 @@ class ChannelsLastEngine:
     when the engine is built; rebuild it after further training.
     """
 
-    def __init__(self, model: ResNet, device=None):
+    def __init__(self, model: ResNet, device=None, cuda_graph: bool = False):
+        """``cuda_graph=True`` replays the whole program from a CUDA graph (one per input shape): for small images
+        the program is bound by launch latency, not by the GPU."""
         device = torch.device(device) if device is not None else next(model.parameters()).device
         self.device = device
+        self._runner = None
+        if cuda_graph and device.type == "cuda":
+            from ..nn.inference import CudaGraphRunner
+
+            self._runner = CudaGraphRunner(self._forward)
         self.stem = _PackedConv(model.conv1, model.bn1, device)
         self.pool = model.maxpool is not None
         self.blocks = []
@@ -186,8 +193,13 @@ class ChannelsLastEngine:
         out[..., :c] = x.to(self.device).permute(0, 2, 3, 1)
         return out
 
-    @torch.no_grad()
     def __call__(self, x):
+        if self._runner is not None and torch.is_tensor(x) and x.is_cuda:
+            return self._runner(x)
+        return self._forward(x)
+
+    @torch.no_grad()
+    def _forward(self, x):
         x = self.stem(self._to_nhwc(x), relu=True)
         if self.pool:
             x = F.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1).contiguous()
@@ -198,15 +210,11 @@ class ChannelsLastEngine:
                 y = conv(y, relu=True)
             x = convs[-1](y, relu=True, residual=identity)  # bias + shortcut + ReLU in the GEMM epilogue
         pooled = x.float().mean(dim=(1, 2))
-        if pooled.is_cuda:
+        if pooled.is_cuda and pooled.shape[0] >= 64 and self.fc_w.shape[0] >= 128 and self.fc_w.shape[0] % 8 == 0:
             from ..ops.gemm import matmul_nt
 
-            rows = pooled.shape[0]
-            pad = torch.zeros(max(rows, 8), pooled.shape[1], device=self.device, dtype=torch.bfloat16)
-            pad[:rows] = pooled.to(torch.bfloat16)
-            logits = matmul_nt(pad, self.fc_w)[:rows].float() if self.fc_w.shape[0] % 8 == 0 else \
-                pooled @ self.fc_w.float().t()
-        else:
+            logits = matmul_nt(pooled.to(torch.bfloat16), self.fc_w).float()
+        else:  # a handful of rows: not worth a tensor-core launch
             logits = pooled @ self.fc_w.float().t()
         return logits + self.fc_b if self.fc_b is not None else logits
 

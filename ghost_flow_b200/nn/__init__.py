@@ -45,6 +45,6 @@ from .privacy import (  # noqa: F401
     RandomizedSmoothing, SecureAggregation,
 )
 from .inference import (  # noqa: F401
-    BatchInference, InferenceConfig, InferenceOptimizer, InferenceSession, ONNXAttribute, ONNXGraph, ONNXModel,
+    BatchInference, CudaGraphRunner, InferenceConfig, InferenceOptimizer, InferenceSession, ONNXAttribute, ONNXGraph, ONNXModel,
     ONNXNode, ONNXTensor, onnx_to_tensor, tensor_to_onnx, warmup_model,
 )

@@ -28,6 +28,7 @@ class InferenceConfig:
     fold_constants: bool = True
     use_half_precision: bool = False
     num_threads: int = 1
+    use_cuda_graph: bool = False     # replay CUDA inputs from a captured graph (see CudaGraphRunner)
 
 
 class InferenceOptimizer:
@@ -77,6 +78,76 @@ class InferenceOptimizer:
         return list(self.applied)
 
 
+def _map_tensors(obj, fn):
+    """Applies ``fn`` to every torch tensor inside tuples / lists / dicts / dataclasses / named tuples."""
+    import dataclasses
+
+    from ..tensor import Tensor
+
+    if isinstance(obj, torch.Tensor):
+        return fn(obj)
+    if isinstance(obj, Tensor):
+        return Tensor(fn(obj.data))
+    if isinstance(obj, tuple) and hasattr(obj, "_fields"):
+        return type(obj)(*[_map_tensors(o, fn) for o in obj])
+    if isinstance(obj, (tuple, list)):
+        return type(obj)(_map_tensors(o, fn) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _map_tensors(v, fn) for k, v in obj.items()}
+    if dataclasses.is_dataclass(obj) and not isinstance(obj, type):
+        return dataclasses.replace(obj, **{f.name: _map_tensors(getattr(obj, f.name), fn)
+                                           for f in dataclasses.fields(obj)})
+    return obj
+
+
+class CudaGraphRunner:
+    """Replays a forward pass from a CUDA graph, so that a launch-bound model costs one launch per call.
+
+    ``runner = CudaGraphRunner(fn)``; ``runner(x, ...)`` takes CUDA tensors. The first call with a new combination
+    of input shapes and dtypes runs ``fn`` a few times eagerly on a side stream (so that every lazily created
+    workspace exists), then captures it with the inputs held in static buffers; later calls copy their inputs into
+    those buffers and replay. ``fn`` must be free of autograd, host synchronisation and data-dependent control
+    flow, and its parameters must stay where they are (rebuild the runner after ``model.to(...)``). Results are
+    cloned out of the graph's static outputs unless ``clone_outputs=False`` (then they are overwritten by the
+    next call). The library's own kernels launch on the current stream and keep their tensor maps in kernel
+    arguments, so they are captured like any other launch.
+    """
+
+    def __init__(self, fn, warmup: int = 3, clone_outputs: bool = True, max_graphs: int = 16):
+        self.fn, self.warmup, self.clone_outputs, self.max_graphs = fn, warmup, clone_outputs, max_graphs
+        self._cache: dict = {}
+
+    def _capture(self, inputs):
+        static_in = [t.clone() for t in inputs]
+        side = torch.cuda.Stream(device=inputs[0].device)
+        side.wait_stream(torch.cuda.current_stream(inputs[0].device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(self.warmup, 1)):
+                self.fn(*static_in)
+        torch.cuda.current_stream(inputs[0].device).wait_stream(side)
+        torch.cuda.synchronize(inputs[0].device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph), torch.no_grad():
+            static_out = self.fn(*static_in)
+        return static_in, graph, static_out
+
+    def __call__(self, *inputs):
+        from ..tensor import Tensor
+
+        inputs = [t.data if isinstance(t, Tensor) else t for t in inputs]
+        key = tuple((tuple(t.shape), t.dtype, t.device.index) for t in inputs)
+        entry = self._cache.get(key)
+        if entry is None:
+            if len(self._cache) >= self.max_graphs:
+                self._cache.pop(next(iter(self._cache)))
+            entry = self._cache[key] = self._capture(inputs)
+        static_in, graph, static_out = entry
+        for s, t in zip(static_in, inputs):
+            s.copy_(t)
+        graph.replay()
+        return _map_tensors(static_out, torch.clone) if self.clone_outputs else static_out
+
+
 class BatchInference:
     """Collects single requests into batches of ``batch_size`` (or whatever is there after ``max_wait_ms``)."""
 
@@ -113,11 +184,16 @@ class InferenceSession:
         self.config = config or InferenceConfig()
         self.optimizer = InferenceOptimizer(self.config)
         self.model = self.optimizer.optimize(model)
+        self._graphs = CudaGraphRunner(self.model) if self.config.use_cuda_graph else None
 
     @torch.no_grad()
     def run(self, x):
         from ..tensor import Tensor
 
+        data = x.data if isinstance(x, Tensor) else x
+        if self._graphs is not None and torch.is_tensor(data) and data.is_cuda:
+            out = self._graphs(data)
+            return Tensor(out) if isinstance(x, Tensor) and torch.is_tensor(out) else out
         if isinstance(x, Tensor):
             return Tensor(self.model(x.data))
         return self.model(x)

@@ -146,8 +146,45 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return y
 
 
+def matmul_fp32_split(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b`` for fp32 CUDA matrices on the bf16 tensor-core kernel with close to fp32 accuracy.
+
+    Each operand is split into two bf16 numbers (``x = hi + lo`` up to 2^-16 relative); the three significant cross
+    terms ``hi hi + hi lo + lo hi`` are evaluated as ONE GEMM over a three times longer contraction
+    (``[hi_a | hi_a | lo_a] @ [hi_b ; lo_b ; hi_b]``) with fp32 accumulation in tensor memory and an fp32 result.
+    The relative error is about 2e-5 of ``|a| @ |b|``, between TF32 (1e-3) and an fp32 FMA loop (1e-6).
+    Needs ``K`` and ``N`` to be multiples of 8 (16-byte rows for the copy engine)."""
+    import ctypes
+
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2 and K % 8 == 0 and N % 8 == 0
+    a = a if a.stride(1) == 1 else a.contiguous()
+    b = b if b.stride(1) == 1 else b.contiguous()
+    a3 = torch.empty(M, 3 * K, device=a.device, dtype=torch.bfloat16)
+    b3 = torch.empty(3 * K, N, device=a.device, dtype=torch.bfloat16)
+    lib = _lib.cuda_lib()
+    L, I, P = ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p
+    lib.gf_split_bf16_cat.argtypes = [P, P, L, I, L, L, L, L, I, P]
+    lib.gf_split_bf16_cat.restype = I
+    _lib.check_rc(lib.gf_split_bf16_cat(a.data_ptr(), a3.data_ptr(), M, K, a.stride(0), 3 * K, K, 2 * K, 2,
+                                        _lib.stream_ptr()), "gf_split_bf16_cat")
+    _lib.check_rc(lib.gf_split_bf16_cat(b.data_ptr(), b3.data_ptr(), K, N, b.stride(0), N, K * N, 2 * K * N, 1,
+                                        _lib.stream_ptr()), "gf_split_bf16_cat")
+    return gemm_raw(a3, False, b3, True, M, N, 3 * K, out_dtype=torch.float32)
+
+
+def _fp32_split_ok(a, b) -> bool:
+    return (a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32 and a.shape[1] % 8 == 0
+            and b.shape[1] % 8 == 0 and a.shape[0] >= 64 and b.shape[1] >= 64 and a.shape[1] >= 16
+            and not (torch.is_grad_enabled() and (a.requires_grad or b.requires_grad)))
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """General matmul for the tensor API: 2-D bf16 CUDA operands use the tcgen05 kernel."""
+    """General matmul for the tensor API: 2-D bf16 CUDA operands use the tcgen05 kernel; 2-D fp32 CUDA operands
+    use it through :func:`matmul_fp32_split`."""
+    if a.dim() == 2 and b.dim() == 2 and _fp32_split_ok(a, b):
+        return matmul_fp32_split(a, b)
     if a.dim() == 2 and b.dim() == 2 and _kernel_ok(a, b) and not (a.requires_grad or b.requires_grad):
         if a.stride(1) == 1 and b.stride(1) == 1:
             return matmul_nn(a, b)

@@ -339,3 +339,23 @@ def test_tensor_api_elementwise_reductions_softmax(dtype, kernel_status):
                               atol=1e-5 if dtype == torch.float32 else 4e-3)
         assert torch.allclose(t.log_softmax(1).data.float(), torch.log_softmax(x.float(), -1),
                               atol=1e-4 if dtype == torch.float32 else 8e-2)
+
+
+def test_fp32_matmul_on_tensor_cores_is_close_to_fp32(kernel_status):
+    """Tensor.matmul of fp32 CUDA matrices: one bf16 tcgen05 GEMM over hi/lo splits, error far below bf16's."""
+    import ghost_flow_b200 as gf
+    from ghost_flow_b200.ops import _lib
+
+    torch.manual_seed(0)
+    for M, K, N in ((1024, 1024, 1024), (300, 72, 136), (2048, 512, 128), (200, 64, 136)):
+        a, b = torch.randn(M, K, device=DEV), torch.randn(K, N, device=DEV)
+        before = _lib.launch_count()
+        y = gf.Tensor(a).matmul(gf.Tensor(b)).data
+        assert _lib.launch_count() - before >= 3 and y.dtype == torch.float32
+        ref = a.double() @ b.double()
+        scale = (a.abs().double() @ b.abs().double()).max()
+        err = (y.double() - ref).abs().max() / scale
+        bf16_err = ((a.bfloat16().float() @ b.bfloat16().float()).double() - ref).abs().max() / scale
+        assert err < 3e-5 and err < bf16_err / 20, (M, K, N, float(err), float(bf16_err))
+        yt = gf.Tensor(a).matmul(gf.Tensor(b.t().contiguous()).t()).data  # strided right operand
+        assert torch.allclose(yt, y, atol=1e-4 * float(scale))

@@ -142,3 +142,26 @@ def test_resnet_serving_program_matches_the_model():
             assert fuse_conv_bn_relu(m) > 0
             fused = m(x)
             assert (fused - ref).abs().max() <= 0.05 * ref.abs().max() + 0.05
+
+
+def test_cuda_graph_replay_matches_eager():
+    """A BERT encoder and the ResNet serving program replayed from CUDA graphs give the eager results, also after
+    the inputs change and for a second input shape."""
+    from ghost_flow_b200 import models, nn
+
+    torch.manual_seed(0)
+    cfg = models.BertConfig.bert_tiny()
+    bert = models.BertModel(cfg).to(DEV).to(torch.bfloat16).eval()
+    runner = nn.CudaGraphRunner(lambda t: bert(t).last_hidden_state)
+    with torch.no_grad():
+        for shape in ((4, 64), (2, 128), (4, 64)):
+            ids = torch.randint(0, cfg.vocab_size, shape, device=DEV)
+            want = bert(ids).last_hidden_state.float()
+            got = runner(ids).float()
+            assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), (got - want).abs().max()
+    assert len(runner._cache) == 2
+    m = models.resnet18(128, small_input=True).to(DEV).eval()
+    eager, graphed = m.compile_inference(), m.compile_inference(cuda_graph=True)
+    for n in (64, 64, 16):
+        x = torch.randn(n, 3, 32, 32, device=DEV)
+        assert torch.allclose(graphed(x), eager(x), atol=1e-2, rtol=1e-2)
