@@ -4,7 +4,7 @@ from .module import Identity, Module, ModuleDict, ModuleList, Parameter, Sequent
 from .layers import (  # noqa: F401
     BatchNorm1d, BatchNorm2d, Dropout, Dropout2d, ELU, Embedding, GELU, GroupNorm, InstanceNorm, InstanceNorm2d,
     LayerNorm, LeakyReLU, Linear, LogSoftmax, Mish, ReLU, RMSNorm, SELU, Sigmoid, SiLU, Softmax, Softplus, Swish,
-    SwiGLU, Tanh, TokenPositionEmbedding,
+    SwiGLU, SyncBatchNorm, Tanh, TokenPositionEmbedding,
 )
 from .conv import (  # noqa: F401
     AdaptiveAvgPool2d, AvgPool2d, Conv1d, Conv2d, Conv3d, ConvTranspose2d, Flatten, GlobalAvgPool2d,

@@ -270,6 +270,89 @@ class BatchNorm2d(_BatchNorm):
     pass
 
 
+class _SyncBNFn(torch.autograd.Function):
+    """Batch norm whose statistics are taken over the batches of every rank: one all-reduce of
+    ``[sum, sum of squares, count]`` in forward and one of ``[sum dy, sum dy * xhat]`` in backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, eps, momentum, group):
+        import torch.distributed as dist
+
+        C = x.shape[1]
+        dims = [0] + list(range(2, x.dim()))
+        xf = x.float()
+        stats = torch.cat([xf.sum(dims), (xf * xf).sum(dims), torch.full((1,), float(x.numel() // C), device=x.device)])
+        dist.all_reduce(stats, group=group)
+        n = stats[-1]
+        mean = stats[:C] / n
+        var = (stats[C:2 * C] / n - mean * mean).clamp_min_(0.0)
+        rstd = torch.rsqrt(var + eps)
+        shape = [1, C] + [1] * (x.dim() - 2)
+        xhat = (xf - mean.view(shape)) * rstd.view(shape)
+        if running_mean is not None:
+            with torch.no_grad():
+                running_mean.mul_(1 - momentum).add_(mean, alpha=momentum)
+                running_var.mul_(1 - momentum).add_(var * (n / (n - 1).clamp_min(1.0)), alpha=momentum)
+        y = xhat * weight.float().view(shape) + bias.float().view(shape) if weight is not None else xhat
+        ctx.save_for_backward(xhat, weight, rstd)
+        ctx.group, ctx.n, ctx.dims, ctx.shape = group, n, dims, shape
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        import torch.distributed as dist
+
+        xhat, weight, rstd = ctx.saved_tensors
+        dyf = dy.float()
+        C = xhat.shape[1]
+        dw = (dyf * xhat).sum(ctx.dims)
+        db = dyf.sum(ctx.dims)
+        red = torch.cat([db, dw])
+        dist.all_reduce(red, group=ctx.group)
+        g = dyf * weight.float().view(ctx.shape) if weight is not None else dyf
+        sum_g, sum_gx = red[:C], red[C:]
+        if weight is not None:
+            sum_g, sum_gx = sum_g * weight.float(), sum_gx * weight.float()
+        dx = (g - sum_g.view(ctx.shape) / ctx.n - xhat * sum_gx.view(ctx.shape) / ctx.n) * rstd.view(ctx.shape)
+        return (dx.to(dy.dtype), dw.to(weight.dtype) if weight is not None else None,
+                db.to(weight.dtype) if weight is not None else None, None, None, None, None, None)
+
+
+class SyncBatchNorm(_BatchNorm):
+    """Batch norm over the global batch of a data-parallel group (the reference's BatchNorm neither synchronises
+    nor updates running statistics: ghostflow-nn/src/norm.rs:50-79). Without an initialised process group, or in
+    eval mode, it is the plain layer. ``SyncBatchNorm.convert(model)`` swaps every BatchNorm1d/2d of a model."""
+
+    def __init__(self, num_features, eps: float = 1e-5, momentum: float = 0.1, affine: bool = True, group=None):
+        super().__init__(num_features, eps, momentum, affine)
+        self.group = group
+
+    def forward(self, x):
+        import torch.distributed as dist
+
+        if not (self.training and dist.is_available() and dist.is_initialized()
+                and dist.get_world_size(self.group) > 1):
+            return super().forward(x)
+        self.num_batches_tracked += 1
+        return _SyncBNFn.apply(x, self.weight, self.bias, self.running_mean, self.running_var, self.eps,
+                               self.momentum, self.group)
+
+    @classmethod
+    def convert(cls, module: torch.nn.Module, group=None) -> torch.nn.Module:
+        for name, child in list(module.named_children()):
+            if isinstance(child, _BatchNorm) and not isinstance(child, cls):
+                new = cls(child.num_features, child.eps, child.momentum, child.weight is not None, group)
+                new.load_state_dict(child.state_dict())
+                new.to(child.running_mean.device)
+                if isinstance(module, (torch.nn.ModuleList, torch.nn.Sequential)) and name.isdigit():
+                    module[int(name)] = new
+                else:
+                    setattr(module, name, new)
+            else:
+                cls.convert(child, group)
+        return module
+
+
 class GroupNorm(Module):
     def __init__(self, num_groups, num_channels, eps: float = 1e-5, affine: bool = True):
         super().__init__()

@@ -153,6 +153,37 @@ def case_fault(rank, world, out):
     return {"steps_done": steps_done, "detected": detected, "seconds": time.monotonic() - t0, "watchdog": wd.fired}
 
 
+def case_syncbn(rank, world, out):
+    """SyncBatchNorm over two ranks against plain batch norm over the concatenated batch."""
+    from ghost_flow_b200 import nn
+    torch.manual_seed(3)
+    x = torch.randn(8, 5, 4, 4)
+    w = torch.randn(8, 5, 4, 4)
+    ref = torch.nn.BatchNorm2d(5)
+    ref.weight.data.uniform_(0.5, 1.5)
+    ref.bias.data.normal_()
+    xr = x.clone().requires_grad_()
+    (ref(xr) * w).sum().backward()
+    net = nn.Sequential([nn.BatchNorm2d(5)])
+    net[0].load_state_dict(ref.state_dict())
+    net[0].running_mean.zero_()
+    net[0].running_var.fill_(1.0)
+    net = nn.SyncBatchNorm.convert(net)
+    assert isinstance(net[0], nn.SyncBatchNorm)
+    xs = x.chunk(world)[rank].clone().requires_grad_()
+    y = net(xs)
+    (y * w.chunk(world)[rank]).sum().backward()
+    wg = net[0].weight.grad.clone()
+    dist.all_reduce(wg)
+    with torch.no_grad():
+        y_ref = ref(x)  # second call only to compare outputs; running stats of `ref` advance twice
+    return {"y_err": (y - y_ref.chunk(world)[rank]).abs().max().item(),
+            "dx_err": (xs.grad - xr.grad.chunk(world)[rank]).abs().max().item(),
+            "dw_err": (wg - ref.weight.grad).abs().max().item(),
+            "rv_err": (net[0].running_var - (0.9 + 0.1 * x.var((0, 2, 3), unbiased=True))).abs().max().item(),
+            "rm_err": (net[0].running_mean - 0.1 * x.mean((0, 2, 3))).abs().max().item()}
+
+
 def main():
     case, out = sys.argv[1], sys.argv[2]
     dist.init_process_group("gloo")

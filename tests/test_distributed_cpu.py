@@ -53,6 +53,14 @@ def test_ring_and_ulysses_attention_match_full_sequence(tmp_path):
         assert all(v < 2e-4 for v in d.values()), d
 
 
+def test_sync_batch_norm_matches_full_batch(tmp_path):
+    r, res = _run("syncbn", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert len(res) == 2
+    for d in res:
+        assert all(v < 1e-4 for v in d.values()), d
+
+
 def test_host_side_failure_is_detected_without_hanging(tmp_path):
     r, res = _run("fault", tmp_path, timeout=120)
     by_steps = sorted(res, key=lambda d: d["steps_done"])
