@@ -119,6 +119,34 @@ def build(args, dev):
         gu = torch.randn(R, 2 * C, device=dev, dtype=bf)
         dy = torch.randn(R, C, device=dev, dtype=bf)
         return (lambda: raw.swiglu_bwd(gu, dy)), 0.0, 10.0 * R * C
+    if k in ("add_f32", "relu_f32", "softmax_f32", "sum_f32"):
+        from ghost_flow_b200.ops import elementwise as ew
+        if k == "softmax_f32":
+            x = torch.randn(R, C, device=dev)
+            return (lambda: ew.softmax_rows(x)), 0.0, 8.0 * R * C
+        x, y = torch.randn(R * C, device=dev), torch.randn(R * C, device=dev)
+        if k == "add_f32":
+            return (lambda: ew.binary(x, y, "add")), 0.0, 12.0 * R * C
+        if k == "sum_f32":
+            return (lambda: ew.reduce_all(x, "sum")), 0.0, 4.0 * R * C
+        return (lambda: ew.unary_any(x, "relu")), 0.0, 8.0 * R * C
+    if k == "split_bf16":
+        from ghost_flow_b200.ops.gemm import matmul_fp32_split
+        M, N, K = args.m, args.n, args.k
+        a, b = torch.randn(M, K, device=dev), torch.randn(K, N, device=dev)
+        return (lambda: matmul_fp32_split(a, b)), 2.0 * M * N * K, 4.0 * (M * K + N * K + M * N)
+    if k in ("im2col_nhwc", "conv_nhwc"):
+        # --batch images of --rows x --rows pixels, --cols channels in and out, 3 x 3 window, stride 1
+        from ghost_flow_b200.ops.render import conv2d_nhwc, im2col_nhwc, pack_conv_weight_nhwc
+        B, HW, Cc = args.batch, args.rows, args.cols
+        x = torch.randn(B, HW, HW, Cc, device=dev, dtype=bf)
+        w = torch.randn(Cc, Cc, 3, 3, device=dev) / (3.0 * Cc ** 0.5)
+        wp, bp = pack_conv_weight_nhwc(w, torch.zeros(Cc, device=dev))
+        px = B * HW * HW
+        if k == "im2col_nhwc":
+            return (lambda: im2col_nhwc(x, 3, 3, 1, 1)), 0.0, 2.0 * px * Cc * 10
+        return (lambda: conv2d_nhwc(x, wp, bp, (3, 3), 1, 1, relu=True)), 2.0 * px * Cc * Cc * 9, \
+            2.0 * (2 * px * Cc + 9 * Cc * Cc)
     if k == "layernorm":
         from ghost_flow_b200.ops import fused
         x = torch.randn(R, C, device=dev, dtype=bf)
