@@ -5,8 +5,10 @@ launcher :308-333) that nothing calls, and a string-pattern "ConvBNReLU" fusion 
 (ghostflow-core/src/fusion.rs:108-144) that only records names. Here the fusion is a real layer:
 
 * ``ConvBNReLU(conv, bn, relu=True)`` folds the batch-norm statistics into the convolution once (weights scaled per
-  output channel, one bias vector) and keeps the folded bf16 weight matrix, so a forward pass is the im2col gather
-  kernel followed by one tcgen05 GEMM whose epilogue adds the bias and applies ReLU.
+  output channel, one bias vector) and keeps the folded bf16 weight matrix in tap-major, channel-minor order, so a
+  forward pass on the GPU is: one cast-and-reorder of the input to channels-last bf16, the 16-byte-wide gather
+  kernel (skipped for 1 x 1 windows), and one tcgen05 GEMM whose epilogue adds the bias and applies ReLU. The
+  result has NCHW shape with channels-last strides, so a following folded layer reorders nothing.
 * ``fuse_conv_bn_relu(model)`` walks a model and replaces every ``Conv2d -> BatchNorm2d [-> ReLU]`` run inside a
   ``Sequential`` (and the ``conv/bn`` attribute pairs that the vision models use) by that layer.
 
@@ -70,20 +72,26 @@ class ConvBNReLU(Module):
 
     def _pack(self):
         if self._packed is None or self._packed[0].device != self.weight.device:
-            cout = self.out_channels
-            k = self.weight[0].numel()
-            kp = (k + 7) // 8 * 8
-            wp = torch.zeros(cout, kp, device=self.weight.device, dtype=torch.bfloat16)
-            wp[:, :k] = self.weight.reshape(cout, k).to(torch.bfloat16)
-            self._packed = (wp, self.bias.to(torch.bfloat16))
+            from ..ops.render import pack_conv_weight_nhwc
+
+            self._packed = pack_conv_weight_nhwc(self.weight, self.bias)
         return self._packed
 
     def forward(self, x):
         if self._gemm_path(x):
-            from ..ops.render import conv_gemm_packed
+            from ..ops.render import conv2d_nhwc
 
             wp, bp = self._pack()
-            y = conv_gemm_packed(x, wp, bp, self.kernel_size, self.stride[0], self.padding[0], self.relu)
+            kh, kw = self.kernel_size
+            cp = wp.shape[1] // (kh * kw)
+            n, c, h, w = x.shape
+            if cp == c:  # one pass: cast to bf16 and reorder to channels-last
+                xn = x.to(dtype=torch.bfloat16, memory_format=torch.channels_last).permute(0, 2, 3, 1)
+            else:
+                xn = torch.zeros(n, h, w, cp, device=x.device, dtype=torch.bfloat16)
+                xn[..., :c] = x.permute(0, 2, 3, 1)
+            y = conv2d_nhwc(xn, wp, bp, self.kernel_size, self.stride[0], self.padding[0], self.relu)
+            y = y.permute(0, 3, 1, 2)  # NCHW shape, channels-last strides
             return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
         y = F.conv2d(x, self.weight.to(x.dtype), self.bias.to(x.dtype), self.stride, self.padding, self.dilation,
                      self.groups)

@@ -333,26 +333,6 @@ def conv2d_nhwc(x, packed_weight, bias, kernel_size, stride: int = 1, padding: i
     return y.view(N, OH, OW, cout)
 
 
-def conv_gemm_packed(x, packed_weight, bias, kernel_size, stride: int, padding: int, relu: bool):
-    """NCHW front end of :func:`conv2d_nhwc` for the ``ConvBNReLU`` layer. ``packed_weight`` is bf16
-    ``[Cout, Cin * KH * KW]`` in the layout of a flattened NCHW weight, zero-padded to a multiple of 8 columns; the
-    input goes through the fp32 gather kernel. Returns a bf16 NCHW-shaped tensor (channels-last strides)."""
-    from .gemm import gemm_raw
-
-    N, Cin, H, W = x.shape
-    kh, kw = kernel_size
-    OH, OW = (H + 2 * padding - kh) // stride + 1, (W + 2 * padding - kw) // stride + 1
-    cout, kp = packed_weight.shape
-    cols = torch.empty(N * OH * OW, kp, device=x.device, dtype=torch.bfloat16)
-    lib = _lib.cuda_lib()
-    lib.gf_im2col_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p]
-    lib.gf_im2col_bf16.restype = ctypes.c_int
-    _lib.check_rc(lib.gf_im2col_bf16(x.contiguous().float().data_ptr(), cols.data_ptr(), N, Cin, H, W, kh, kw, stride,
-                                     padding, kp, _lib.stream_ptr()), "gf_im2col_bf16")
-    y = gemm_raw(cols, False, packed_weight, False, N * OH * OW, cout, kp, bias=bias, relu=relu)
-    return y.view(N, OH, OW, cout).permute(0, 3, 1, 2)
-
-
 def batch_norm_train(x, weight, bias, running_mean, running_var, momentum: float = 0.1, eps: float = 1e-5):
     """Training-mode batch norm over ``[N, C, *]`` that also updates the running statistics."""
     if _gpu_plain(x, weight, bias):
