@@ -91,6 +91,12 @@ struct GemmParams {
   int act;                  // epilogue activation after bias and residual: 0 none, 1 ReLU
   int group_m;              // > 0: plain GEMM walks bands of group_m row blocks (keeps a wave's A and B panels in L2)
   int tile_rot;             // rotation of the slow tile index so that the walk starts in the local shard
+  // Implicit convolution (stride 1, odd window, "same" padding) over a channels-last image whose rows and images
+  // are separated by `pad` zero pixels: pixel (n, y, x) is row (n * Hp + y) * conv_pitch + x of a [rows, C] matrix
+  // and the neighbour (y + dy, x + dx) is row + dy * conv_pitch + dx, so the A tile of window tap (ky, kx) is the
+  // same 2-D tensor map read `(ky - pad) * conv_pitch + (kx - pad)` rows further on. k block kb covers channels
+  // (kb % conv_cpb) * 64 ... of tap kb / conv_cpb. conv_cpb = 0: off.
+  int conv_cpb, conv_kw, conv_pitch, conv_pad;
 };
 
 constexpr int BM = 128;
@@ -411,7 +417,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           const int k0 = ti.k_begin + kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+            int ak = k0, am = m0;
+            if (p.conv_cpb > 0) {
+              const int kbi = k0 / BK;
+              const int tap = kbi / p.conv_cpb;
+              const int ky = tap / p.conv_kw, kx = tap - ky * p.conv_kw;
+              ak = (kbi - tap * p.conv_cpb) * BK;
+              am = m0 + (ky - p.conv_pad) * p.conv_pitch + (kx - p.conv_pad);   // may be negative: zero fill
+            }
+            tma_load_2d(sa, &tmA, &full_bar[stage], ak, am);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[stage], m0 + c * 64, k0);
@@ -837,8 +851,9 @@ static int gemm_core(const void* A, const void* B, void* C, int M, int N, int K,
   const int bn = pick_bn(M, N, bn_hint);
   CUtensorMap tmA, tmB;
   int rc;
-  if (!a_mn_major)
-    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, BM, BK);
+  if (!a_mn_major)   // implicit convolution: the map covers the [rows, C] image, not an unfolded [rows, taps * C]
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, p.conv_cpb > 0 ? p.conv_cpb * BK : K, lda * 2,
+                      BM, BK);
   else
     rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda * 2, BK, 64);
   if (rc) return rc;
@@ -912,6 +927,7 @@ static void no_gather(gf::GemmParams& p) {
   for (int i = 0; i < 8; ++i) { p.sc_dst[i] = nullptr; p.sc_flags[i] = nullptr; }
   p.rs_world = 0; p.rs_rank = 0; p.rs_rows_per_rank = 1; p.rs_call = 0; p.rs_out = nullptr; p.rs_ldo = 0;
   for (int i = 0; i < 8; ++i) { p.rs_stage[i] = nullptr; p.rs_counters[i] = nullptr; }
+  p.conv_cpb = 0; p.conv_kw = 1; p.conv_pitch = 0; p.conv_pad = 0;
 }
 
 // lda/ldb: row pitch in elements of the matrix as stored.
@@ -956,6 +972,29 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   }
   return gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias, residual, ldr,
                    alpha, status, bn_hint, max_ctas, p, st);
+}
+
+// Stride-1 "same" convolution without unfolding: Y[rows, Cout] = act(conv(Xp) + bias) on the padded pixel grid.
+//   Xp  bf16 [rows, C], rows = images * (H + pad) * (W + pad): channels-last pixels, `pad` zero pixels after every
+//       image row and `pad` zero rows after every image (pad = (window - 1) / 2), C a multiple of 64
+//   Wt  bf16 [Cout, KH * KW * C], tap-major, channel-minor
+//   Y   bf16 [rows, Cout]: rows of padding pixels hold values that mean nothing; the caller drops them
+//   residual (optional) bf16 [rows, Cout] on the same padded grid, added before the activation
+// One GEMM with K = KH * KW * C whose A tiles are row-shifted reads of Xp (see GemmParams::conv_*).
+GF_API int gf_conv_implicit_bf16(const void* Xp, const void* Wt, void* Y, long long rows, int C, int Cout, int KH,
+                                 int KW, int pitch, const void* bias, const void* residual, int relu, int* status,
+                                 void* stream_v) {
+  gf::enter();
+  if (rows <= 0 || rows > 0x7fffffffLL || C <= 0 || C % gf::BK || Cout <= 0 || Cout % 8 || KH != KW || !(KH & 1) ||
+      pitch <= (KW - 1) / 2)
+    return gf::GFH_BAD_ARG;
+  gf::GemmParams p;
+  no_gather(p);
+  p.act = relu ? 1 : 0;
+  p.conv_cpb = C / gf::BK; p.conv_kw = KW; p.conv_pitch = pitch; p.conv_pad = (KW - 1) / 2;
+  const int K = KH * KW * C;
+  return gemm_core(Xp, Wt, Y, (int)rows, Cout, K, 0, C, 0, K, Cout, 0, 0, bias, residual, Cout, 1.f, status, 0, 0, p,
+                   reinterpret_cast<cudaStream_t>(stream_v));
 }
 
 // Grouped GEMM over the row segments of a row-sorted buffer (the experts of a mixture-of-experts layer).

@@ -422,6 +422,39 @@ GF_API int gf_im2col_nhwc_bf16(const void* x, void* cols, int N, int C, int H, i
   return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
 }
 
+// x [N, H, W, C] bf16 -> xp [N, H + pad, W + pad, C] with the image in the top-left corner and zeros in the `pad`
+// trailing columns of every row and the `pad` trailing rows of every image (the layout the implicit convolution
+// reads: one strip of zeros serves as right border of a row and left border of the next). 16 bytes per thread.
+namespace gf {
+__global__ void pad_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ xp, int N, int C8, int H, int W,
+                                     int pad) {
+  const int Hp = H + pad, Wp = W + pad;
+  const long long total = (long long)N * Hp * Wp * C8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c8 = (int)(i % C8);
+    const long long pix = i / C8;
+    const int xx = (int)(pix % Wp), yy = (int)((pix / Wp) % Hp), n = (int)(pix / ((long long)Wp * Hp));
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (xx < W && yy < H) v = x[(((long long)n * H + yy) * W + xx) * C8 + c8];
+    xp[i] = v;
+  }
+}
+}  // namespace gf
+
+GF_API int gf_pad_nhwc_bf16(const void* x, void* xp, int N, int C, int H, int W, int pad, void* stream) {
+  gf::enter();
+  if (C <= 0 || C % 8 || pad < 0 || N <= 0 || H <= 0 || W <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)xp & 15))
+    return gf::GFH_BAD_ARG;
+  const long long total = (long long)N * (H + pad) * (W + pad) * (C / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)gf::sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  gf::pad_nhwc_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)xp, N, C / 8, H,
+                                                                             W, pad);
+  return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
+}
+
 GF_API int gf_im2col_bf16(const float* x, void* cols, int N, int C, int H, int W, int KH, int KW, int stride, int pad,
                           int Kp, void* stream) {
   gf::enter();

@@ -6,6 +6,7 @@ ops/conv.rs + norm.rs)."""
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -307,6 +308,51 @@ def im2col_nhwc(x, kh: int, kw: int, stride: int, padding: int):
     return torch.cat(taps, dim=-1).reshape(N * OH * OW, kh * kw * C), OH, OW
 
 
+# The implicit (no unfolding) path of conv2d_nhwc; GF_CONV_IMPLICIT=0 forces the gather kernel everywhere.
+IMPLICIT_CONV = os.environ.get("GF_CONV_IMPLICIT", "0") == "1"
+
+
+def pad_nhwc(x, pad: int):
+    """``[N, H, W, C]`` bf16 -> ``[N, H + pad, W + pad, C]`` with zeros after every row and every image."""
+    N, H, W, C = x.shape
+    if x.is_cuda:
+        xp = torch.empty(N, H + pad, W + pad, C, device=x.device, dtype=torch.bfloat16)
+        lib = _lib.cuda_lib()
+        lib.gf_pad_nhwc_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_void_p]
+        lib.gf_pad_nhwc_bf16.restype = ctypes.c_int
+        _lib.check_rc(lib.gf_pad_nhwc_bf16(x.data_ptr(), xp.data_ptr(), N, C, H, W, pad, _lib.stream_ptr()),
+                      "gf_pad_nhwc_bf16")
+        return xp
+    return F.pad(x, (0, 0, 0, pad, 0, pad))
+
+
+def conv2d_nhwc_implicit(x, packed_weight, bias, kernel_size, relu: bool = False, residual=None):
+    """Stride-1 "same" convolution of a channels-last bf16 tensor WITHOUT unfolding it (GPU, ``C % 64 == 0``, odd
+    square window). The image is copied once into a grid with ``pad`` zero pixels after every row and every image;
+    on that grid the neighbour ``(dy, dx)`` of a pixel is a fixed number of rows away, so the GEMM reads the A tile
+    of every window tap from the same ``[pixels, C]`` matrix with a row offset (TMA fills rows before the first
+    pixel with zeros) and the unfolded ``[pixels, taps * C]`` matrix never exists. Bias, ``residual`` and ReLU are
+    applied in the epilogue; the padding pixels of the result are dropped on return."""
+    kh, kw = kernel_size
+    pad = (kw - 1) // 2
+    N, H, W, C = x.shape
+    cout = packed_weight.shape[0]
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and C % 64 == 0 and kh == kw and kw % 2 == 1
+    xp = pad_nhwc(x, pad)
+    rp = pad_nhwc(residual.contiguous(), pad) if residual is not None else None
+    Hp, Wp = H + pad, W + pad
+    yp = torch.empty(N, Hp, Wp, cout, device=x.device, dtype=torch.bfloat16)
+    lib = _lib.cuda_lib()
+    P, I = ctypes.c_void_p, ctypes.c_int
+    lib.gf_conv_implicit_bf16.argtypes = [P, P, P, ctypes.c_longlong, I, I, I, I, I, P, P, I, P, P]
+    lib.gf_conv_implicit_bf16.restype = I
+    _lib.check_rc(lib.gf_conv_implicit_bf16(xp.data_ptr(), packed_weight.data_ptr(), yp.data_ptr(), N * Hp * Wp, C,
+                                            cout, kh, kw, Wp, _p(bias), _p(rp), 1 if relu else 0,
+                                            _lib.status_word(x.device).data_ptr(), _lib.stream_ptr()),
+                  "gf_conv_implicit_bf16")
+    return yp[:, :H, :W, :].contiguous()
+
+
 def conv2d_nhwc(x, packed_weight, bias, kernel_size, stride: int = 1, padding: int = 0, relu: bool = False,
                 residual=None):
     """Channels-last convolution for inference: ``x`` is bf16 ``[N, H, W, C]``, ``packed_weight`` comes from
@@ -316,6 +362,9 @@ def conv2d_nhwc(x, packed_weight, bias, kernel_size, stride: int = 1, padding: i
     kh, kw = kernel_size
     N = x.shape[0]
     cout = packed_weight.shape[0]
+    if (IMPLICIT_CONV and x.is_cuda and stride == 1 and kh == kw and kw > 1 and kw % 2 == 1
+            and padding == (kw - 1) // 2 and x.shape[-1] % 64 == 0):
+        return conv2d_nhwc_implicit(x, packed_weight, bias, kernel_size, relu, residual)
     cols, OH, OW = im2col_nhwc(x, kh, kw, stride, padding)
     M, K = cols.shape
     res2 = residual.reshape(M, cout) if residual is not None else None
