@@ -71,9 +71,9 @@ class Embedding(Module):
         idx = ids.long() if ids.is_floating_point() else ids
         oob = (idx < 0) | (idx >= self.num_embeddings)
         out = F.embedding(idx.clamp(0, self.num_embeddings - 1), self.weight, self.padding_idx)
-        if bool(oob.any()):
-            out = out.masked_fill(oob.unsqueeze(-1), 0.0)
-        return out
+        # applied unconditionally: asking the device whether any id is out of range would stall the host on every
+        # call and cannot be captured in a CUDA graph
+        return out.masked_fill_(oob.unsqueeze(-1), 0.0)
 
     forward_indices = forward
 
