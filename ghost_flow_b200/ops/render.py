@@ -309,7 +309,7 @@ def im2col_nhwc(x, kh: int, kw: int, stride: int, padding: int):
 
 
 # The implicit (no unfolding) path of conv2d_nhwc; GF_CONV_IMPLICIT=0 forces the gather kernel everywhere.
-IMPLICIT_CONV = os.environ.get("GF_CONV_IMPLICIT", "0") == "1"
+IMPLICIT_CONV = os.environ.get("GF_CONV_IMPLICIT", "1") == "1"
 
 
 def pad_nhwc(x, pad: int):

@@ -165,3 +165,34 @@ def test_cuda_graph_replay_matches_eager():
     for n in (64, 64, 16):
         x = torch.randn(n, 3, 32, 32, device=DEV)
         assert torch.allclose(graphed(x), eager(x), atol=1e-2, rtol=1e-2)
+
+
+def test_implicit_convolution_matches_fp32():
+    """Stride-1 'same' convolutions read straight from the padded channels-last image (row-shifted TMA tiles)
+    against conv2d in fp32, with and without the shortcut."""
+    from ghost_flow_b200.ops import _lib
+    from ghost_flow_b200.ops.render import conv2d_nhwc, conv2d_nhwc_implicit, pack_conv_weight_nhwc
+
+    torch.manual_seed(0)
+    for (N, C, H, W, Co, k) in ((3, 64, 19, 23, 64, 3), (32, 128, 28, 28, 128, 3), (2, 64, 9, 9, 256, 5),
+                                (1, 192, 7, 7, 72, 3), (5, 512, 7, 7, 512, 3)):
+        x = torch.randn(N, H, W, C, device=DEV).bfloat16()
+        w = torch.randn(Co, C, k, k, device=DEV) / (C * k * k) ** 0.5
+        b = torch.randn(Co, device=DEV)
+        wp, bp = pack_conv_weight_nhwc(w, b)
+        res = torch.randn(N, H, W, Co, device=DEV).bfloat16()
+        ref = F.conv2d(x.float().permute(0, 3, 1, 2), w.bfloat16().float(), b.bfloat16().float(), 1, (k - 1) // 2)
+        got = conv2d_nhwc_implicit(x, wp, bp, (k, k), relu=False).float().permute(0, 3, 1, 2)
+        _lib.check_status()
+        assert torch.allclose(got, ref, atol=3e-2, rtol=3e-2), (N, C, H, W, Co, k, float((got - ref).abs().max()))
+        got = conv2d_nhwc_implicit(x, wp, bp, (k, k), relu=True, residual=res).float().permute(0, 3, 1, 2)
+        want = torch.relu(ref + res.float().permute(0, 3, 1, 2))
+        assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
+        from ghost_flow_b200.ops import render
+
+        saved, render.IMPLICIT_CONV = render.IMPLICIT_CONV, False   # the gather + GEMM path of the same call
+        try:
+            unfolded = conv2d_nhwc(x, wp, bp, (k, k), 1, (k - 1) // 2, relu=True, residual=res)
+        finally:
+            render.IMPLICIT_CONV = saved
+        assert torch.allclose(got, unfolded.float().permute(0, 3, 1, 2), atol=3e-2, rtol=3e-2)
