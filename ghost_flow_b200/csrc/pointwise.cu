@@ -507,13 +507,46 @@ __global__ void split_bf16_cat_kernel(const float* __restrict__ x, __nv_bfloat16
     o[off2] = lo_slot == 2 ? lo : hi;
   }
 }
+// Same, eight columns per thread: two 16-byte loads, three 16-byte stores (cols, pitches and offsets multiples of 8,
+// 16-byte aligned pointers).
+__global__ void split_bf16_cat_x8_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long rows,
+                                         int cols8, long long in_pitch, long long out_pitch, long long off1,
+                                         long long off2, int lo_slot) {
+  const long long total = rows * cols8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols8;
+    const int c = (int)(i - r * cols8) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(x + r * in_pitch + c);
+    const float4 b = *reinterpret_cast<const float4*>(x + r * in_pitch + c + 4);
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat16 h0 = __float2bfloat16(v[2 * q]), h1 = __float2bfloat16(v[2 * q + 1]);
+      hi[q] = pack_bf16x2(__bfloat162float(h0), __bfloat162float(h1));
+      lo[q] = pack_bf16x2(v[2 * q] - __bfloat162float(h0), v[2 * q + 1] - __bfloat162float(h1));
+    }
+    const uint4 H = make_uint4(hi[0], hi[1], hi[2], hi[3]), L = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    __nv_bfloat16* o = out + r * out_pitch + c;
+    *reinterpret_cast<uint4*>(o) = H;
+    *reinterpret_cast<uint4*>(o + off1) = lo_slot == 1 ? L : H;
+    *reinterpret_cast<uint4*>(o + off2) = lo_slot == 2 ? L : H;
+  }
+}
 }  // namespace gf
 
 GF_API int gf_split_bf16_cat(const float* x, void* out, long long rows, int cols, long long in_pitch,
                              long long out_pitch, long long off1, long long off2, int lo_slot, void* stream) {
   gf::enter();
   if (rows <= 0 || cols <= 0 || (lo_slot != 1 && lo_slot != 2)) return GFH_BAD_ARG;
-  split_bf16_cat_kernel<<<ew_grid(rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(
-      x, (__nv_bfloat16*)out, rows, cols, in_pitch, out_pitch, off1, off2, lo_slot);
+  if (cols % 8 == 0 && in_pitch % 4 == 0 && out_pitch % 8 == 0 && off1 % 8 == 0 && off2 % 8 == 0 &&
+      ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    split_bf16_cat_x8_kernel<<<ew_grid(rows * (cols / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+        x, (__nv_bfloat16*)out, rows, cols / 8, in_pitch, out_pitch, off1, off2, lo_slot);
+  } else {
+    split_bf16_cat_kernel<<<ew_grid(rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(
+        x, (__nv_bfloat16*)out, rows, cols, in_pitch, out_pitch, off1, off2, lo_slot);
+  }
   GF_RET();
 }
