@@ -936,12 +936,13 @@ static void no_gather(gf::GemmParams& p) {
 GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
                         int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate,
                         const void* bias, const void* residual, long long ldr, float alpha, int* status,
-                        int bn_hint, int max_ctas, const int* unused_flags, int unused_a, int unused_b,
+                        int bn_hint, int max_ctas, const int* reserved_ptr, int activation, int reserved_int,
                         void* stream_v) {
   gf::enter();
   gf::GemmParams p;
   no_gather(p);
-  p.act = unused_a == 1 ? 1 : 0;     // the former flag-granularity argument now selects the epilogue activation
+  p.act = activation == 1 ? 1 : 0;   // epilogue activation after bias and residual: 0 none, 1 ReLU
+  (void)reserved_ptr; (void)reserved_int;   // kept so that the exported signature stays what callers bound
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
   // Skinny problem (decode-sized M): too few output tiles to fill the machine, so the weight matrix would be
   // streamed by a handful of SMs. Split K until there is about one work item per SM.

@@ -19,7 +19,7 @@ def _is_dense_2d(t: torch.Tensor) -> bool:
 
 
 def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bfloat16, bias=None, residual=None,
-             accumulate=False, alpha=1.0, bn_hint=0, max_ctas=0, b_ready=None, b_rows_per_flag=0, b_epoch=0, relu=False):
+             accumulate=False, alpha=1.0, bn_hint=0, max_ctas=0, relu=False):
     """Launches the kernel on 2-D row-major views.
 
     ``a`` is stored ``[M, K]`` (K-major) or ``[K, M]`` when ``a_mn_major``; ``b`` is stored
@@ -40,7 +40,7 @@ def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bf
         residual.data_ptr() if residual is not None else None,
         residual.stride(0) if residual is not None else 0,
         float(alpha), _lib.status_word(a.device).data_ptr(), bn_hint, max_ctas,
-        b_ready.data_ptr() if b_ready is not None else None, 1 if relu else 0, b_epoch,
+        None, 1 if relu else 0, 0,
         _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "gf_gemm_bf16")
