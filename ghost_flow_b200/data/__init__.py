@@ -219,6 +219,10 @@ class DataLoader:
         self.collate_fn = collate_fn or collate_batch
         self.epoch = 0
 
+    @classmethod
+    def new(cls, *args, **kwargs):
+        return cls(*args, **kwargs)
+
     # builder methods of the reference
     def shuffle(self, v: bool = True):
         self._shuffle = v

@@ -56,6 +56,11 @@ class Module(torch.nn.Module):
             out = super().__call__(*a, **k)
         return _wrap_out(out) if wrapped else out
 
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """``Linear.new(10, 5)``: the reference's constructor spelling (``Linear::new``), same as ``Linear(10, 5)``."""
+        return cls(*args, **kwargs)
+
     def parameters_list(self):
         return list(self.parameters())
 

@@ -45,6 +45,11 @@ class Optimizer:
         self.step_count = 0
 
     # -- reference API
+    @classmethod
+    def new(cls, *args, **kwargs):
+        """``SGD.new(params, 0.01)``: the reference's constructor spelling."""
+        return cls(*args, **kwargs)
+
     def get_lr(self) -> float:
         return self.param_groups[0]["lr"]
 
