@@ -359,6 +359,53 @@ __global__ void softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, 
   }
 }
 
+// Rows of at most 256 * PER elements: the row stays in registers between the three steps (max, sum, write), so
+// memory is read once and written once.
+template <typename T, int PER>
+__global__ void __launch_bounds__(256)
+softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols, int log_mode) {
+  __shared__ float red[32];
+  const int nw = blockDim.x >> 5;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + (long long)r * cols;
+    float v[PER];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int c = threadIdx.x + j * 256;
+      v[j] = c < cols ? ldf(xr, c) : -INFINITY;
+      m = fmaxf(m, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+    for (int w = 1; w < nw; ++w) m = fmaxf(m, red[w]);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      v[j] -= m;                                  // -inf for the columns past the end: exp gives 0
+      s += __expf(v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    s = 0.f;
+    for (int w = 0; w < nw; ++w) s += red[w];
+    const float inv = 1.f / s, ls = logf(s);
+    T* yr = y + (long long)r * cols;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int c = threadIdx.x + j * 256;
+      if (c < cols) stf(yr, c, log_mode ? v[j] - ls : __expf(v[j]) * inv);
+    }
+  }
+}
+
 static inline int ew_grid(long long n, int threads) {
   long long g = (n + threads - 1) / threads;
   const long long cap = (long long)sm_count() * 16;
@@ -474,12 +521,22 @@ GF_API int gf_reduce(const void* x, float* partial, float* out, long long n, int
 GF_API int gf_softmax_rows(const void* x, void* y, int rows, int cols, int log_mode, int dtype, void* stream) {
   gf::enter();
   int g = rows < sm_count() * 8 ? rows : sm_count() * 8;
-  if (dtype == 1)
-    softmax_rows_kernel<__nv_bfloat16><<<g, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x,
-                                                                           (__nv_bfloat16*)y, rows, cols, log_mode);
-  else
-    softmax_rows_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)y, rows, cols,
-                                                                   log_mode);
+  cudaStream_t st = (cudaStream_t)stream;
+#define GF_SOFTMAX_REG(T_, PER_)                                                                              \
+  softmax_rows_reg_kernel<T_, PER_><<<g, 256, 0, st>>>((const T_*)x, (T_*)y, rows, cols, log_mode)
+  if (dtype == 1) {
+    if (cols <= 256 * 4) GF_SOFTMAX_REG(__nv_bfloat16, 4);
+    else if (cols <= 256 * 16) GF_SOFTMAX_REG(__nv_bfloat16, 16);
+    else if (cols <= 256 * 32) GF_SOFTMAX_REG(__nv_bfloat16, 32);
+    else softmax_rows_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, cols,
+                                                              log_mode);
+  } else {
+    if (cols <= 256 * 4) GF_SOFTMAX_REG(float, 4);
+    else if (cols <= 256 * 16) GF_SOFTMAX_REG(float, 16);
+    else if (cols <= 256 * 32) GF_SOFTMAX_REG(float, 32);
+    else softmax_rows_kernel<float><<<g, 256, 0, st>>>((const float*)x, (float*)y, rows, cols, log_mode);
+  }
+#undef GF_SOFTMAX_REG
   GF_RET();
 }
 

@@ -332,7 +332,7 @@ def test_tensor_api_elementwise_reductions_softmax(dtype, kernel_status):
         s, m = ta.sum().data.float(), ta.max().data.float()
         assert torch.allclose(s, a32.sum(), atol=0.5 if dtype == torch.float32 else 40.0, rtol=1e-2)
         assert torch.allclose(m, a32.max(), **tol)
-    for rows, cols in ((64, 1000), (3, 50257), (257, 33)):
+    for rows, cols in ((64, 1000), (3, 50257), (257, 33), (300, 4096), (17, 8000)):
         x = torch.randn(rows, cols, device=DEV, dtype=dtype) * 3
         t = gf.Tensor(x)
         assert torch.allclose(t.softmax(-1).data.float(), torch.softmax(x.float(), -1),
