@@ -388,21 +388,36 @@ __global__ void im2col_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* _
 // [Cout, KH, KW, C]). One thread moves one 16-byte group of 8 channels, so both sides are full-width accesses;
 // taps that fall into the padding are written as zeros.
 namespace gf {
-__global__ void im2col_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ cols, int N, int C8, int H,
-                                        int W, int KH, int KW, int OH, int OW, int stride, int pad) {
+// Block = 32 x 8 threads: threadIdx.y picks one of 8 output pixels, whose (n, oy, ox) is decomposed once; the 32
+// threads of that pixel walk its KH * KW * C / 8 groups of 16 bytes, so a warp writes 512 contiguous bytes per step.
+// c8_shift >= 0 when C / 8 is a power of two (the usual case): tap and channel group then come from a shift and a mask.
+__global__ void __launch_bounds__(256)
+im2col_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ cols, int N, int C8, int H, int W, int KH,
+                        int KW, int OH, int OW, int stride, int pad, int c8_shift) {
   const int per_row = KH * KW * C8;
-  const long long total = (long long)N * OH * OW * per_row;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int j = (int)(i % per_row);
-    const long long row = i / per_row;
-    const int c8 = j % C8, tap = j / C8;
-    const int kx = tap % KW, ky = tap / KW;
-    const int ox = (int)(row % OW), oy = (int)((row / OW) % OH), n = (int)(row / ((long long)OW * OH));
-    const int iy = oy * stride - pad + ky, ix = ox * stride - pad + kx;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = x[(((long long)n * H + iy) * W + ix) * C8 + c8];
-    cols[i] = v;
+  const long long rows = (long long)N * OH * OW;
+  for (long long row = (long long)blockIdx.x * 8 + threadIdx.y; row < rows; row += (long long)gridDim.x * 8) {
+    const int ox = (int)(row % OW);
+    const long long t = row / OW;
+    const int oy = (int)(t % OH), n = (int)(t / OH);
+    const int iy0 = oy * stride - pad, ix0 = ox * stride - pad;
+    const uint4* xin = x + (long long)n * H * W * C8;
+    uint4* out = cols + row * per_row;
+    for (int j = threadIdx.x; j < per_row; j += 32) {
+      int tap, c8;
+      if (c8_shift >= 0) {
+        tap = j >> c8_shift;
+        c8 = j & (C8 - 1);
+      } else {
+        tap = j / C8;
+        c8 = j - tap * C8;
+      }
+      const int ky = tap / KW, kx = tap - ky * KW;
+      const int iy = iy0 + ky, ix = ix0 + kx;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = xin[((long long)iy * W + ix) * C8 + c8];
+      out[j] = v;
+    }
   }
 }
 }  // namespace gf
@@ -413,45 +428,18 @@ GF_API int gf_im2col_nhwc_bf16(const void* x, void* cols, int N, int C, int H, i
   if (C <= 0 || C % 8 || stride <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)cols & 15)) return gf::GFH_BAD_ARG;
   const int OH = (H + 2 * pad - KH) / stride + 1, OW = (W + 2 * pad - KW) / stride + 1;
   if (OH <= 0 || OW <= 0) return gf::GFH_BAD_ARG;
-  const long long total = (long long)N * OH * OW * KH * KW * (C / 8);
-  long long blocks = (total + 255) / 256;
+  const long long rows = (long long)N * OH * OW;
+  long long blocks = (rows + 7) / 8;
   const long long cap = (long long)gf::sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  gf::im2col_nhwc_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const uint4*)x, (uint4*)cols, N, C / 8, H, W, KH, KW, OH, OW, stride, pad);
-  return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
-}
-
-// x [N, H, W, C] bf16 -> xp [N, H + pad, W + pad, C] with the image in the top-left corner and zeros in the `pad`
-// trailing columns of every row and the `pad` trailing rows of every image (the layout the implicit convolution
-// reads: one strip of zeros serves as right border of a row and left border of the next). 16 bytes per thread.
-namespace gf {
-__global__ void pad_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ xp, int N, int C8, int H, int W,
-                                     int pad) {
-  const int Hp = H + pad, Wp = W + pad;
-  const long long total = (long long)N * Hp * Wp * C8;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c8 = (int)(i % C8);
-    const long long pix = i / C8;
-    const int xx = (int)(pix % Wp), yy = (int)((pix / Wp) % Hp), n = (int)(pix / ((long long)Wp * Hp));
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (xx < W && yy < H) v = x[(((long long)n * H + yy) * W + xx) * C8 + c8];
-    xp[i] = v;
+  const int C8 = C / 8;
+  int shift = -1;
+  if ((C8 & (C8 - 1)) == 0) {
+    shift = 0;
+    while ((1 << shift) < C8) ++shift;
   }
-}
-}  // namespace gf
-
-GF_API int gf_pad_nhwc_bf16(const void* x, void* xp, int N, int C, int H, int W, int pad, void* stream) {
-  gf::enter();
-  if (C <= 0 || C % 8 || pad < 0 || N <= 0 || H <= 0 || W <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)xp & 15))
-    return gf::GFH_BAD_ARG;
-  const long long total = (long long)N * (H + pad) * (W + pad) * (C / 8);
-  long long blocks = (total + 255) / 256;
-  const long long cap = (long long)gf::sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  gf::pad_nhwc_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)xp, N, C / 8, H,
-                                                                             W, pad);
+  gf::im2col_nhwc_bf16_kernel<<<(unsigned)blocks, dim3(32, 8), 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, (uint4*)cols, N, C8, H, W, KH, KW, OH, OW, stride, pad, shift);
   return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
 }
 

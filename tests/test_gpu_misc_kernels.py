@@ -101,7 +101,7 @@ def test_channels_last_conv_matches_fp32(kernel_status):
 
     torch.manual_seed(0)
     for (N, C, H, W, Co, k, s, p) in ((3, 16, 19, 23, 64, 3, 1, 1), (2, 8, 33, 33, 24, 7, 2, 3), (4, 64, 14, 14, 128, 1, 1, 0),
-                                      (2, 32, 15, 15, 64, 1, 2, 0), (2, 3, 32, 32, 16, 3, 1, 1)):
+                                      (2, 32, 15, 15, 64, 1, 2, 0), (2, 3, 32, 32, 16, 3, 1, 1), (2, 24, 10, 11, 16, 3, 2, 1)):
         x = torch.randn(N, C, H, W, device=DEV)
         w = torch.randn(Co, C, k, k, device=DEV) / (C * k * k) ** 0.5
         b = torch.randn(Co, device=DEV)
