@@ -443,6 +443,40 @@ GF_API int gf_im2col_nhwc_bf16(const void* x, void* cols, int N, int C, int H, i
   return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
 }
 
+// x [N, H, W, C] bf16 -> xp [N, H + pad, W + pad, C] with the image in the top-left corner and zeros in the `pad`
+// trailing columns of every row and the `pad` trailing rows of every image (the layout the implicit convolution
+// reads: one strip of zeros serves as right border of a row and left border of the next).
+namespace gf {
+// One block per padded image row: its first W * C8 groups of 16 bytes are a straight copy of the source row (when
+// the row is inside the image), everything else is zero, so no thread divides anything.
+__global__ void __launch_bounds__(256)
+pad_nhwc_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ xp, int N, int C8, int H, int W, int pad) {
+  const int Hp = H + pad, Wp = W + pad;
+  const int valid = W * C8, width = Wp * C8;
+  for (int r = blockIdx.x; r < N * Hp; r += gridDim.x) {
+    const int n = r / Hp, yy = r - n * Hp;
+    const bool inside = yy < H;
+    const uint4* src = x + ((long long)n * H + yy) * valid;
+    uint4* dst = xp + (long long)r * width;
+    for (int k = threadIdx.x; k < width; k += blockDim.x)
+      dst[k] = (inside && k < valid) ? src[k] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+}  // namespace gf
+
+GF_API int gf_pad_nhwc_bf16(const void* x, void* xp, int N, int C, int H, int W, int pad, void* stream) {
+  gf::enter();
+  if (C <= 0 || C % 8 || pad < 0 || N <= 0 || H <= 0 || W <= 0 || ((uintptr_t)x & 15) || ((uintptr_t)xp & 15))
+    return gf::GFH_BAD_ARG;
+  long long blocks = (long long)N * (H + pad);
+  if (blocks > 0x7fffffffLL) return gf::GFH_BAD_ARG;
+  const long long cap = (long long)gf::sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  gf::pad_nhwc_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)xp, N, C / 8, H,
+                                                                             W, pad);
+  return cudaGetLastError() == cudaSuccess ? gf::GFH_OK : gf::GFH_CUDA;
+}
+
 GF_API int gf_im2col_bf16(const float* x, void* cols, int N, int C, int H, int W, int KH, int KW, int stride, int pad,
                           int Kp, void* stream) {
   gf::enter();
