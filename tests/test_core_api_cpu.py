@@ -86,3 +86,28 @@ def test_reference_class_names_are_present():
     SGD Adam AdamW StepLR CosineAnnealingLR Dataset DataLoader""".split()
     missing = [n for n in names if n not in have]
     assert not missing, missing
+
+
+def test_every_kernel_entry_point_named_in_python_is_exported():
+    """The ctypes layer looks symbols up lazily, so a missing export would only show on the GPU box: check here that
+    every ``lib.gf_*`` attribute the package, the benchmarks and the tests touch exists in the built library."""
+    import ctypes
+    import glob
+    import os
+    import re
+
+    from ghost_flow_b200.ops import _lib
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = ctypes.CDLL(str(_lib.lib_path()))
+    files = (glob.glob(os.path.join(root, "ghost_flow_b200", "**", "*.py"), recursive=True)
+             + glob.glob(os.path.join(root, "benchmarks", "*.py")) + glob.glob(os.path.join(root, "tests", "*.py"))
+             + [os.path.join(root, "bench.py"), os.path.join(root, "__graft_entry__.py")])
+    names = set()
+    for f in files:
+        src = open(f).read()
+        names |= set(re.findall(r"\.(gf_[a-z0-9_]+)\b", src))
+        names |= set(re.findall(r"\"(gf_[a-z0-9_]+)\": \[", src))      # the signature table of ops/_lib.py
+    names -= {"gf_cuda", "gf_host"}
+    missing = sorted(n for n in names if not hasattr(lib, n))
+    assert len(names) > 40 and not missing, missing
