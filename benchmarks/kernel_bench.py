@@ -135,7 +135,7 @@ def build(args, dev):
         M, N, K = args.m, args.n, args.k
         a, b = torch.randn(M, K, device=dev), torch.randn(K, N, device=dev)
         return (lambda: matmul_fp32_split(a, b)), 2.0 * M * N * K, 4.0 * (M * K + N * K + M * N)
-    if k in ("im2col_nhwc", "conv_nhwc"):
+    if k in ("im2col_nhwc", "conv_nhwc", "conv_unfolded", "pad_nhwc"):
         # --batch images of --rows x --rows pixels, --cols channels in and out, 3 x 3 window, stride 1
         from ghost_flow_b200.ops.render import conv2d_nhwc, im2col_nhwc, pack_conv_weight_nhwc
         B, HW, Cc = args.batch, args.rows, args.cols
@@ -145,6 +145,12 @@ def build(args, dev):
         px = B * HW * HW
         if k == "im2col_nhwc":
             return (lambda: im2col_nhwc(x, 3, 3, 1, 1)), 0.0, 2.0 * px * Cc * 10
+        if k == "pad_nhwc":
+            from ghost_flow_b200.ops.render import pad_nhwc
+            return (lambda: pad_nhwc(x, 1)), 0.0, 2.0 * Cc * (px + B * (HW + 1) * (HW + 1))
+        if k == "conv_unfolded":      # gather + GEMM even where the implicit path applies
+            from ghost_flow_b200.ops import render
+            render.IMPLICIT_CONV = False
         return (lambda: conv2d_nhwc(x, wp, bp, (3, 3), 1, 1, relu=True)), 2.0 * px * Cc * Cc * 9, \
             2.0 * (2 * px * Cc + 9 * Cc * Cc)
     if k == "layernorm":
