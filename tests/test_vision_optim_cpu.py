@@ -93,3 +93,16 @@ def test_extra_optimizers_follow_the_textbook_updates(ours, theirs, kw):
     for p, q in zip(a, b):
         assert torch.allclose(p, q, atol=1e-6)
     assert oa.get_lr() == kw["lr"]
+
+
+def test_inference_session_falls_back_without_cuda_and_maps_outputs():
+    from ghost_flow_b200.models.encoders import BertOutput
+    from ghost_flow_b200.nn.inference import _map_tensors
+
+    sess = nn.InferenceSession(nn.Sequential([nn.Linear(4, 3), nn.ReLU()]), nn.InferenceConfig(use_cuda_graph=True))
+    x = torch.randn(5, 4)
+    assert torch.equal(sess.run(x), sess.model(x))           # CPU input: plain execution, no graph
+    out = _map_tensors(BertOutput(torch.ones(2), torch.zeros(1)), lambda t: t + 1)
+    assert isinstance(out, BertOutput) and float(out.last_hidden_state.sum()) == 4.0
+    nested = _map_tensors({"a": [torch.zeros(1), (torch.ones(1),)], "n": 3}, lambda t: t + 2)
+    assert float(nested["a"][1][0]) == 3.0 and nested["n"] == 3
