@@ -111,3 +111,19 @@ def test_every_kernel_entry_point_named_in_python_is_exported():
     names -= {"gf_cuda", "gf_host"}
     missing = sorted(n for n in names if not hasattr(lib, n))
     assert len(names) > 40 and not missing, missing
+
+
+def test_alias_package_serves_every_submodule():
+    import importlib
+
+    import ghost_flow
+    import ghost_flow_b200
+
+    for sub in ("nn", "optim", "models", "ml", "ml.tree", "data", "io", "utils", "parallel", "cuda", "serve", "autograd"):
+        assert importlib.import_module(f"ghost_flow.{sub}") is importlib.import_module(f"ghost_flow_b200.{sub}")
+    from ghost_flow.ml import RandomForestClassifier  # noqa: F401
+    from ghost_flow.models import resnet18  # noqa: F401
+
+    assert ghost_flow.Tensor is ghost_flow_b200.Tensor
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("ghost_flow.no_such_module")
