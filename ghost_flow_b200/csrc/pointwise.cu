@@ -307,6 +307,33 @@ __global__ void reduce_stage1_kernel(const T* __restrict__ x, float* __restrict_
     if (threadIdx.x == 0) partial[blockIdx.x] = t;
   }
 }
+// fp32 input, four elements per load (n a multiple of 4, 16-byte aligned).
+__global__ void reduce_stage1_f32x4_kernel(const float4* __restrict__ x, float* __restrict__ partial, long long nvec,
+                                           int mode) {
+  __shared__ float red[32];
+  float acc = mode == 0 ? 0.f : -INFINITY;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+    acc = mode == 0 ? acc + ((v.x + v.y) + (v.z + v.w)) : fmaxf(acc, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float t = __shfl_xor_sync(0xffffffffu, acc, o);
+    acc = mode == 0 ? acc + t : fmaxf(acc, t);
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : (mode == 0 ? 0.f : -INFINITY);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float u = __shfl_xor_sync(0xffffffffu, t, o);
+      t = mode == 0 ? t + u : fmaxf(t, u);
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+  }
+}
 __global__ void reduce_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts,
                                      int mode) {
   __shared__ float red[32];
@@ -512,7 +539,11 @@ GF_API int gf_reduce(const void* x, float* partial, float* out, long long n, int
   if (dtype == 1)
     reduce_stage1_kernel<__nv_bfloat16><<<g, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, partial, n,
                                                                             mode);
-  else
+  else if (n % 4 == 0 && ((uintptr_t)x % 16 == 0)) {
+    g = ew_grid(n / 4, 256);
+    if (g > 1024) g = 1024;
+    reduce_stage1_f32x4_kernel<<<g, 256, 0, (cudaStream_t)stream>>>((const float4*)x, partial, n / 4, mode);
+  } else
     reduce_stage1_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)x, partial, n, mode);
   reduce_stage2_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(partial, out, g, mode);
   gf::note_extra_launches(1);
