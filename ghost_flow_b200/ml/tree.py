@@ -238,10 +238,14 @@ class _ForestBase(Estimator):
     _random_splits = False
     _classifier = True
 
-    def __init__(self, n_estimators=100):
-        self._n_estimators, self._max_depth, self._max_features = n_estimators, None, None
+    def __init__(self, n_estimators=100, max_depth=None, **params):
+        """``n_estimators`` as in the reference's constructor; every builder-style setting (``max_depth``,
+        ``max_features``, ``min_samples_split``, ...) may also be given as a keyword."""
+        self._n_estimators, self._max_depth, self._max_features = n_estimators, max_depth, None
         self._min_samples_split, self._min_samples_leaf, self._bootstrap, self._seed, self._n_jobs = 2, 1, True, 0, 8
         self._max_samples = None
+        if params:
+            self.set(**params)
 
     def _fit_members(self, X, y):
         n = len(X)
@@ -280,6 +284,9 @@ class RandomForestClassifier(_ForestBase, ClassifierMixin):
 
     def predict(self, X):
         return out(self.classes_[to_np(self.predict_proba(X)).argmax(1)])
+
+
+RandomForest = RandomForestClassifier   # the name used in the reference's README example
 
 
 class RandomForestRegressor(_ForestBase, RegressorMixin):

@@ -127,3 +127,33 @@ def test_alias_package_serves_every_submodule():
     assert ghost_flow.Tensor is ghost_flow_b200.Tensor
     with pytest.raises(ModuleNotFoundError):
         importlib.import_module("ghost_flow.no_such_module")
+
+
+def test_api_advertised_by_the_reference_readme_works():
+    """The snippets of the reference's README / PERFORMANCE.md (README.md:217-283, ghost-flow-py/PERFORMANCE.md:24,85),
+    which its own bindings do not support, run here."""
+    import numpy as np
+
+    import ghost_flow as gf
+
+    model = gf.nn.Sequential([gf.nn.Linear(10, 32), gf.nn.ReLU(), gf.nn.Linear(32, 1)])
+    x, y = gf.Tensor.randn(16, 10), gf.Tensor.zeros(16, 1)
+    opt = gf.optim.Adam(model.parameters(), lr=1e-2)
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = gf.nn.mse_loss(model(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < losses[0]
+    assert ((y - model(x)) ** 2).mean().item() >= 0.0
+    assert min((x + 1000).tolist()) > 900
+    X = np.random.default_rng(0).normal(size=(80, 4))
+    Y = (X[:, 0] > 0).astype(int)
+    rf = gf.ml.RandomForest(n_estimators=10, max_depth=4)
+    rf.fit(X, Y)
+    assert rf.score(X, Y) > 0.9 and len(rf.predict(X).tolist()) == 80
+    for name in ("LoRAConfig", "LoRALinear", "FlashAttention", "CurriculumLearning"):
+        assert hasattr(gf.nn, name)
+    assert hasattr(gf.cuda.Tensor, "randn")
