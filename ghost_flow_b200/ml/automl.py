@@ -640,11 +640,20 @@ class GPUMemoryManager:
     def __init__(self, context: GPUContext):
         self.context = context
         self.allocations: dict[int, int] = {}
+        self._peak = 0
 
     def allocate(self, nbytes: int):
         t = torch.empty(nbytes, dtype=torch.uint8, device=self.context.device)
         self.allocations[t.data_ptr()] = nbytes
+        self._peak = max(self._peak, self.allocated_bytes())
         return t
+
+    def allocated_memory(self) -> int:
+        """Bytes currently handed out (ghostflow-ml/src/gpu.rs:451-462)."""
+        return self.allocated_bytes()
+
+    def peak_memory(self) -> int:
+        return self._peak
 
     def free(self, t):
         self.allocations.pop(t.data_ptr(), None)

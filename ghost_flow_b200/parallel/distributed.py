@@ -259,6 +259,23 @@ class ZeRoConfig:
     def default(cls):
         return cls()
 
+    # presets of the reference (ghostflow-nn/src/zero_optimizer.rs:57-110)
+    @classmethod
+    def stage1(cls, world_size: int = 1, rank: int = 0):
+        return cls(stage=ZeRoStage.Stage1, world_size=world_size, rank=rank)
+
+    @classmethod
+    def stage2(cls, world_size: int = 1, rank: int = 0):
+        return cls(stage=ZeRoStage.Stage2, world_size=world_size, rank=rank)
+
+    @classmethod
+    def stage3(cls, world_size: int = 1, rank: int = 0):
+        return cls(stage=ZeRoStage.Stage3, world_size=world_size, rank=rank)
+
+    def with_offload(self, cpu: bool = True, nvme: bool = False):
+        self.cpu_offload, self.nvme_offload = cpu, nvme
+        return self
+
 
 @dataclass
 class ZeRoStats:

@@ -128,6 +128,11 @@ class ModelRegistry:
         except KeyError:
             raise ModelNotFound(mid) from None
 
+    def predict(self, mid, inputs, shape=None):
+        """Runs model ``mid`` on ``inputs`` (the reference's ``ModelRegistry::predict``, ghostflow-serve/src/models.rs:81-105,
+        echoes its input; this one executes the model)."""
+        return self.get(mid).predict(inputs, shape)
+
     def unload(self, mid):
         with self._lock:
             if self.models.pop(mid, None) is None:
