@@ -129,7 +129,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = matmul_tn(dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy2.dtype)
+            db = torch.sum(dy2, 0, dtype=torch.float32).to(dy2.dtype)   # fp32 accumulation without an fp32 copy of dy
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres
@@ -139,6 +139,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w^T (+ bias) (+ residual)`` with the bias/residual adds fused into the GEMM epilogue."""
     if _kernel_ok(x, w):
+        if not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad
+                                             or (bias is not None and bias.requires_grad)
+                                             or (residual is not None and residual.requires_grad))):
+            # inference: straight to the kernel, no autograd node
+            r2 = _as_2d(residual) if residual is not None else None
+            x2 = _as_2d(x)
+            y = gemm_raw(x2, False, w, False, x2.shape[0], w.shape[0], x2.shape[1], bias=bias, residual=r2)
+            return y.view(*x.shape[:-1], w.shape[0])
         return _LinearFn.apply(x, w, bias, residual)
     y = torch.nn.functional.linear(x, w, bias)
     if residual is not None:
