@@ -106,3 +106,15 @@ def test_inference_session_falls_back_without_cuda_and_maps_outputs():
     assert isinstance(out, BertOutput) and float(out.last_hidden_state.sum()) == 4.0
     nested = _map_tensors({"a": [torch.zeros(1), (torch.ones(1),)], "n": 3}, lambda t: t + 2)
     assert float(nested["a"][1][0]) == 3.0 and nested["n"] == 3
+
+
+def test_zero_optimizer_fused_arm_refuses_what_it_cannot_run():
+    from ghost_flow_b200.parallel.distributed import ZeRoConfig, ZeRoOptimizer
+
+    p = [torch.nn.Parameter(torch.randn(4, 4))]
+    with pytest.raises(RuntimeError, match="bf16 CUDA parameters"):
+        ZeRoOptimizer(p, ZeRoConfig.stage2(), comm="fused")        # CPU fp32 parameters, one rank
+    with pytest.raises(ValueError):
+        ZeRoOptimizer(p, ZeRoConfig.stage2(), comm="carrier-pigeon")
+    opt = ZeRoOptimizer(p, ZeRoConfig.stage3(1, 0).with_offload(False))
+    assert opt._fc is None and opt.config.stage == 3
