@@ -118,3 +118,28 @@ def test_zero_optimizer_fused_arm_refuses_what_it_cannot_run():
         ZeRoOptimizer(p, ZeRoConfig.stage2(), comm="carrier-pigeon")
     opt = ZeRoOptimizer(p, ZeRoConfig.stage3(1, 0).with_offload(False))
     assert opt._fc is None and opt.config.stage == 3
+
+
+def test_fused_ops_skip_the_graph_node_only_when_no_gradient_is_wanted():
+    from ghost_flow_b200.ops.fused import _call
+
+    class Double(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, k):
+            ctx.save_for_backward(x)
+            ctx.k = k
+            return x * k
+
+        @staticmethod
+        def backward(ctx, dy):
+            return dy * ctx.k, None
+
+    x = torch.randn(3, requires_grad=True)
+    y = _call(Double, x, 2.0)
+    assert y.grad_fn is not None
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.full((3,), 2.0))
+    with torch.no_grad():
+        assert _call(Double, x, 2.0).grad_fn is None
+    z = _call(Double, x.detach(), 3.0)
+    assert z.grad_fn is None and torch.allclose(z, x.detach() * 3.0)
