@@ -37,6 +37,7 @@ CUDA_SOURCES = [
     "xent_adamw.cu",
     "attn_fwd.cu",
     "attn_fwd2.cu",
+    "attn_fwd3.cu",
     "attn_bwd.cu",
     "attn_decode.cu",
     "comm_kernels.cu",

@@ -48,6 +48,7 @@ _SIGS = {
     "gf_grad_sumsq": [P, L, P, I, P],
     "gf_flash_attn_fwd": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
     "gf_flash_attn_fwd2": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
+    "gf_flash_attn_fwd3": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],
     "gf_attn_decode": [P, L, P, P, I, P, I, P, L, I, I, I, I, F, I, P, P],
     "gf_flash_attn_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
     "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
@@ -183,6 +184,12 @@ DEBUG_SYNC = os.environ.get("GF_DEBUG_SYNC", "0") == "1"
 
 
 def flash_fwd_fn():
-    """Forward attention launcher: the two-tile ping-pong kernel unless GF_FA_FWD=1 selects the first one."""
+    """Forward attention launcher: the kernel that keeps P in tensor memory, unless GF_FA_FWD=2 selects the
+    earlier two-tile kernel (P through shared memory) or GF_FA_FWD=1 the single-tile one."""
     lib = cuda_lib()
-    return lib.gf_flash_attn_fwd if os.environ.get("GF_FA_FWD", "2") == "1" else lib.gf_flash_attn_fwd2
+    which = os.environ.get("GF_FA_FWD", "3")
+    if which == "1":
+        return lib.gf_flash_attn_fwd
+    if which == "2":
+        return lib.gf_flash_attn_fwd2
+    return lib.gf_flash_attn_fwd3

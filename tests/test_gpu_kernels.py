@@ -238,6 +238,8 @@ def test_flash_attention_fwd(B, S, Hq, Hkv, D, causal, kernel_status):
     ref = ops.attention_ref(q, k, v, causal=causal)
     torch.cuda.synchronize()
     assert _rel_err(o, ref) < 2e-2
+    # element-wise: outputs are convex combinations of V rows (|v| < ~5), bf16 rounding of P and O
+    assert (o.float() - ref.float()).abs().max().item() < 6e-2
 
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [
@@ -265,6 +267,17 @@ def test_flash_attention_bwd(B, S, Hq, Hkv, D, causal, kernel_status):
 def test_flash_attention_fwd_first_generation_kernel(B, S, Hq, Hkv, D, causal, kernel_status, monkeypatch):
     """The single-tile forward kernel stays available (GF_FA_FWD=1) and must agree with the reference too."""
     monkeypatch.setenv("GF_FA_FWD", "1")
+    ops = _ops()
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    assert _rel_err(o, ops.attention_ref(q, k, v, causal=causal)) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 512, 2, 2, 128, True), (1, 384, 2, 1, 64, False)])
+def test_flash_attention_fwd_second_generation_kernel(B, S, Hq, Hkv, D, causal, kernel_status, monkeypatch):
+    """The two-tile kernel that passes P through shared memory stays available (GF_FA_FWD=2)."""
+    monkeypatch.setenv("GF_FA_FWD", "2")
     ops = _ops()
     qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16)
     q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
