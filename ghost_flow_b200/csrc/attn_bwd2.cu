@@ -1,0 +1,505 @@
+// FlashAttention backward, second generation. The products and tile shapes are those of attn_bwd.cu
+// (one CTA owns a 128-row KV tile of one KV head and walks the 64-row query tiles that can see it; S^T, dP^T,
+// dV, dK and dQ^T on tcgen05 with TMEM accumulators), reorganised so that no warp ever waits for work that
+// is not its own:
+//
+//   * a fourth warpgroup does nothing but drain dQ^T from tensor memory and add it to the fp32 accumulator in
+//     global memory, so the eight compute warps only turn S^T / dP^T into P^T / dS^T;
+//   * P^T and dS^T are double-buffered in shared memory: the compute warps write tile i + 1 while the tensor pipe
+//     still reads tile i;
+//   * the softmax scale is taken out of the element loop (dS^T leaves unscaled; dK is scaled once in the
+//     epilogue and dQ in the conversion kernel), and the row statistics arrive as -lse * log2(e), so one P / dS
+//     pair costs an FMA, an exponential, a subtraction, a multiplication and two conversions;
+//   * the statistics are read from shared memory sixteen bytes at a time;
+//   * Q / dO tiles sit in three stages and the MMA warp polls its two kinds of work (the S^T / dP^T pair of the next
+//     step, the dQ^T / dV / dK triple of the current one) without blocking on either, so a tile that is still
+//     in flight never holds up products whose inputs are ready.
+//
+// The reference only names a backward kernel (ghostflow-cuda/src/kernels/mod.rs:82) and has no backward for its
+// CPU flash attention (ghostflow-nn/src/flash_attention.rs).
+#include "gf_host.h"
+#include "gf_ptx.cuh"
+
+namespace gf {
+
+constexpr int B2_KV = 128;       // kv rows per CTA
+constexpr int B2_Q = 64;         // query rows per step
+constexpr int B2_QST = 3;        // Q / dO / statistics stages: a tile is requested two steps before its first use,
+                                 // because a stage is only free once the dK product that read it has completed
+constexpr int B2_THREADS = 512;  // warpgroup 0: TMA warp, MMA warp, two idle; 1 and 2: compute; 3: dQ drain
+
+struct FaBwd2Params {
+  int B, S, Hq, Hkv;
+  int causal;
+  float scale;
+  const float* nlse2;  // [B, Hq, S]  -lse * log2(e)
+  const float* delta;  // [B, Hq, S]
+  float* dq_acc;       // fp32 [B*S, Hq*HD], zero before launch; receives dQ / scale
+  __nv_bfloat16* dK;
+  long long lddk;
+  __nv_bfloat16* dV;
+  long long lddv;
+  int* status;
+};
+
+template <int HD>
+struct FaBwd2Cfg {
+  static constexpr int CH = HD / 64;
+  static constexpr int KV_BYTES = B2_KV * HD * 2;     // K or V tile
+  static constexpr int Q_BYTES = B2_Q * HD * 2;       // Q or dO tile
+  static constexpr int PT_BYTES = B2_KV * B2_Q * 2;   // P^T or dS^T tile (one 128-byte row per kv row)
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + KV_BYTES;
+  static constexpr int OFF_Q = OFF_V + KV_BYTES;            // B2_QST stages
+  static constexpr int OFF_DO = OFF_Q + B2_QST * Q_BYTES;   // B2_QST stages
+  static constexpr int OFF_P = OFF_DO + B2_QST * Q_BYTES;   // 2 buffers
+  static constexpr int OFF_DS = OFF_P + 2 * PT_BYTES;       // 2 buffers
+  static constexpr int OFF_STAT = OFF_DS + 2 * PT_BYTES;    // B2_QST stages x (nlse2[64], delta[64]) fp32
+  static constexpr int OFF_BAR = OFF_STAT + B2_QST * 2 * B2_Q * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int STAGE_TX = 2 * Q_BYTES + 2 * B2_Q * 4;
+  // TMEM columns
+  static constexpr int TM_S = 0;      // 64
+  static constexpr int TM_DP = 64;    // 64
+  static constexpr int TM_DV = 128;   // HD
+  static constexpr int TM_DK = 256;   // HD
+  static constexpr int TM_DQ = 384;   // 2 x 64
+  static constexpr int TMEM_COLS = 512;
+};
+
+__device__ __forceinline__ void bulk_load_1d_b2(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(B2_THREADS, 1)
+fa_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+               const FaBwd2Params p) {
+  using Cfg = FaBwd2Cfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + Cfg::OFF_K;
+  uint8_t* sV = smem + Cfg::OFF_V;
+  uint8_t* sQ = smem + Cfg::OFF_Q;
+  uint8_t* sDO = smem + Cfg::OFF_DO;
+  uint8_t* sP = smem + Cfg::OFF_P;
+  uint8_t* sDS = smem + Cfg::OFF_DS;
+  float* sStat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* s_full = bars + 1;
+  uint64_t* s_empty = bars + 2;
+  uint64_t* acc_full = bars + 3;
+  uint64_t* pds_full = bars + 4;    // [2]
+  uint64_t* pds_empty = bars + 6;   // [2]
+  uint64_t* dq_full = bars + 8;     // [2]
+  uint64_t* dq_empty = bars + 10;   // [2]
+  uint64_t* q_full = bars + 12;     // [B2_QST]
+  uint64_t* q_empty = q_full + B2_QST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + B2_QST);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest KV tiles first: under a causal mask tile 0 is seen by every query tile, the last one by two
+  const int j = blockIdx.y;
+  const int hk = blockIdx.x, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int n_q = p.S / B2_Q;
+  const int i_start = p.causal ? (j * B2_KV) / B2_Q : 0;
+  const int per_head = n_q - i_start;
+  const int n_iter = G * per_head;
+  const int row_base = b * p.S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < B2_QST; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&pds_full[i], 8);
+      mbar_init(&pds_empty[i], 1);
+      mbar_init(&dq_full[i], 1);
+      mbar_init(&dq_empty[i], 4);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * Cfg::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::CH; ++c) {
+        tma_load_2d(sK + c * (B2_KV * 128), &tmK, kv_full, hk * HD + c * 64, row_base + j * B2_KV);
+        tma_load_2d(sV + c * (B2_KV * 128), &tmV, kv_full, hk * HD + c * 64, row_base + j * B2_KV);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % B2_QST;
+        const uint32_t ph = (it / B2_QST) & 1;
+        const int h = hk * G + it / per_head;
+        const int i = i_start + it % per_head;
+        if (!mbar_wait(&q_empty[st], ph ^ 1)) {
+          if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_EMPTY);
+          break;
+        }
+        mbar_expect_tx(&q_full[st], Cfg::STAGE_TX);
+#pragma unroll
+        for (int c = 0; c < Cfg::CH; ++c) {
+          tma_load_2d(sQ + st * Cfg::Q_BYTES + c * (B2_Q * 128), &tmQ, &q_full[st], h * HD + c * 64,
+                      row_base + i * B2_Q);
+          tma_load_2d(sDO + st * Cfg::Q_BYTES + c * (B2_Q * 128), &tmDO, &q_full[st], h * HD + c * 64,
+                      row_base + i * B2_Q);
+        }
+        const long long soff = ((long long)b * p.Hq + h) * p.S + (long long)i * B2_Q;
+        bulk_load_1d_b2(sStat + st * 2 * B2_Q, p.nlse2 + soff, B2_Q * 4, &q_full[st]);
+        bulk_load_1d_b2(sStat + st * 2 * B2_Q + B2_Q, p.delta + soff, B2_Q * 4, &q_full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, B2_Q, 0, 0);    // S^T, dP^T
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);    // dV, dK
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, B2_Q, 1, 1);   // dQ^T
+      constexpr uint32_t K_LBO = B2_KV * 128;  // HD = 64: output rows 64..127 read the V tile, finite and never used
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      bool ok = mbar_wait(kv_full, 0);
+      if (!ok && p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_FULL);
+      // S^T(it) = K Q^T and dP^T(it) = V dO^T into the single S / dP buffers
+      auto issue_s = [&](int it) {
+        const int st = it % B2_QST;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ + st * Cfg::Q_BYTES), doa = smem_u32(sDO + st * Cfg::Q_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (B2_KV * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (B2_Q * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + Cfg::TM_S, umma_desc_sw128(ka + aoff, 16, 1024),
+                       umma_desc_sw128(qa + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (B2_KV * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (B2_Q * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + Cfg::TM_DP, umma_desc_sw128(va + aoff, 16, 1024),
+                       umma_desc_sw128(doa + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+      };
+      // dQ^T(it), dV += , dK += from P^T(it) / dS^T(it)
+      auto issue_grads = [&](int it) {
+        const int st = it % B2_QST, pb = it & 1;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ + st * Cfg::Q_BYTES), doa = smem_u32(sDO + st * Cfg::Q_BYTES);
+        const uint32_t pa = smem_u32(sP + pb * Cfg::PT_BYTES), dsa = smem_u32(sDS + pb * Cfg::PT_BYTES);
+        // dQ^T = K^T dS^T first (K = 128 kv rows -> 8 steps): the drain warps start on it while dV, dK run
+#pragma unroll
+        for (int kk = 0; kk < B2_KV / 16; ++kk)
+          umma_bf16_ss(tmem_base + Cfg::TM_DQ + pb * B2_Q, umma_desc_sw128(ka + kk * 2048, K_LBO, 1024),
+                       umma_desc_sw128(dsa + kk * 2048, B2_KV * 128, 1024), idesc_dq, kk > 0 ? 1u : 0u);
+        umma_commit(&dq_full[pb]);
+        // dV += P^T dO ; dK += dS^T Q   (K = 64 query rows -> 4 steps)
+#pragma unroll
+        for (int kk = 0; kk < B2_Q / 16; ++kk)
+          umma_bf16_ss(tmem_base + Cfg::TM_DV, umma_desc_sw128(pa + kk * 32, 16, 1024),
+                       umma_desc_sw128(doa + kk * 2048, B2_Q * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < B2_Q / 16; ++kk)
+          umma_bf16_ss(tmem_base + Cfg::TM_DK, umma_desc_sw128(dsa + kk * 32, 16, 1024),
+                       umma_desc_sw128(qa + kk * 2048, B2_Q * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&q_empty[st]);
+        umma_commit(&pds_empty[pb]);
+      };
+      // Two queues, polled in turn: S^T / dP^T of step s_next (needs its Q / dO stage and the previous step's
+      // scores loaded into registers) and the gradient products of step g_next (needs P^T / dS^T in shared memory
+      // and a drained dQ^T buffer).
+      int s_next = 0, g_next = 0;
+      uint32_t idle = 0;
+      while (ok && g_next < n_iter) {
+        bool progressed = false;
+        if (s_next < n_iter && mbar_try_wait(&q_full[s_next % B2_QST], (s_next / B2_QST) & 1) &&
+            (s_next == 0 || mbar_try_wait(s_empty, (s_next - 1) & 1))) {
+          issue_s(s_next);
+          ++s_next;
+          progressed = true;
+        }
+        if (g_next < s_next && mbar_try_wait(&pds_full[g_next & 1], (g_next >> 1) & 1) &&
+            mbar_try_wait(&dq_empty[g_next & 1], ((g_next >> 1) & 1) ^ 1)) {
+          issue_grads(g_next);
+          ++g_next;
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > GF_WAIT_LIMIT) {
+          if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_SOFTMAX);
+          ok = false;
+        } else if (idle > 64) {
+          __nanosleep(32);
+        }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else if (warp >= 12) {
+    // ---------------------------------------------------------------- dQ drain warps (12..15)
+    // Warp w owns TMEM lanes 32 * (w % 4) .. +31 = head-dim rows of dQ^T; a thread adds its 64 query columns to
+    // the fp32 accumulator, consecutive lanes to consecutive addresses.
+    const int lane_grp = warp & 3;
+    const int d = lane_grp * 32 + lane;
+    const uint32_t tlane = (uint32_t)(lane_grp * 32) << 16;
+    const long long dq_ld = (long long)p.Hq * HD;
+    for (int it = 0; it < n_iter; ++it) {
+      const int st = it & 1;
+      if (!mbar_wait_warp(&dq_full[st], (it >> 1) & 1)) {
+        if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int h = hk * G + it / per_head;
+      const int i = i_start + it % per_head;
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem_base + Cfg::TM_DQ + st * B2_Q + tlane, r0);
+      tmem_ld32(tmem_base + Cfg::TM_DQ + st * B2_Q + 32 + tlane, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_empty[st]);
+      if (d < HD) {
+        float* dst = p.dq_acc + (long long)(row_base + i * B2_Q) * dq_ld + h * HD + d;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) atomicAdd(dst + (long long)e * dq_ld, __uint_as_float(r0[e]));
+#pragma unroll
+        for (int e = 0; e < 32; ++e) atomicAdd(dst + (long long)(32 + e) * dq_ld, __uint_as_float(r1[e]));
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- compute warps (4..11)
+    // Warps 4..7 own query columns 0..31 of S^T / dP^T, warps 8..11 columns 32..63; within a group, warp w owns
+    // TMEM lanes 32 * (w % 4) .. +31, one kv row per thread.
+    const int hf = (warp >> 2) - 1;
+    const int lane_grp = warp & 3;
+    const int r = lane_grp * 32 + lane;
+    const int kv_idx = j * B2_KV + r;
+    const uint32_t tlane = (uint32_t)(lane_grp * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it % B2_QST, pb = it & 1;
+      const int i = i_start + it % per_head;
+      if (!mbar_wait_warp(s_full, it & 1)) {
+        if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_TMEM_FULL);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sv[32], dpv[32];
+      tmem_ld32(tmem_base + Cfg::TM_S + hf * 32 + tlane, sv);
+      tmem_ld32(tmem_base + Cfg::TM_DP + hf * 32 + tlane, dpv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);
+      const float4* nl4 = reinterpret_cast<const float4*>(sStat + st * 2 * B2_Q + hf * 32);
+      const float4* de4 = reinterpret_cast<const float4*>(sStat + st * 2 * B2_Q + B2_Q + hf * 32);
+      const int q0 = i * B2_Q + hf * 32;
+      const bool diag = p.causal && (q0 < j * B2_KV + B2_KV);  // these columns touch the diagonal
+      uint32_t pp[16], dd[16];
+#pragma unroll
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 nl = nl4[e4], de = de4[e4];
+        const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
+        const float des[4] = {de.x, de.y, de.z, de.w};
+        float pv[4], dv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = e4 * 4 + u;
+          float pe = ex2_approx(fmaf(__uint_as_float(sv[e]), sl2, nls[u]));
+          if (diag && q0 + e < kv_idx) pe = 0.f;
+          pv[u] = pe;
+          dv[u] = pe * (__uint_as_float(dpv[e]) - des[u]);
+        }
+        pp[e4 * 2] = pack_bf16x2(pv[0], pv[1]);
+        pp[e4 * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+        dd[e4 * 2] = pack_bf16x2(dv[0], dv[1]);
+        dd[e4 * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+      }
+      if (!mbar_wait_warp(&pds_empty[pb], ((it >> 1) & 1) ^ 1)) {
+        if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_SOFTMAX);
+        ok = false;
+        break;
+      }
+      uint8_t* sPb = sP + pb * Cfg::PT_BYTES;
+      uint8_t* sDSb = sDS + pb * Cfg::PT_BYTES;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint32_t off = sw128_offset((uint32_t)r, (uint32_t)(hf * 4 + c4));
+        *reinterpret_cast<uint4*>(sPb + off) = make_uint4(pp[c4 * 4], pp[c4 * 4 + 1], pp[c4 * 4 + 2], pp[c4 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDSb + off) = make_uint4(dd[c4 * 4], dd[c4 * 4 + 1], dd[c4 * 4 + 2], dd[c4 * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pds_full[pb]);
+    }
+    if (ok) {
+      if (!mbar_wait_warp(acc_full, 0)) {
+        if (p.status) atomicCAS(p.status, 0, GF_ERR_WAIT_TMEM_FULL);
+      } else {
+        tc_fence_after();
+        __nv_bfloat16* dkr = p.dK + (long long)(row_base + kv_idx) * p.lddk + hk * HD;
+        __nv_bfloat16* dvr = p.dV + (long long)(row_base + kv_idx) * p.lddv + hk * HD;
+        // each group writes half of the head dimension; dK gets the softmax scale here
+#pragma unroll
+        for (int cc = 0; cc < HD / 64; ++cc) {
+          const int c = hf * (HD / 64) + cc;
+          uint32_t rk[32], rv[32];
+          if (n_iter > 0) {
+            tmem_ld32(tmem_base + Cfg::TM_DK + c * 32 + tlane, rk);
+            tmem_ld32(tmem_base + Cfg::TM_DV + c * 32 + tlane, rv);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) rk[e] = rv[e] = 0u;
+          }
+          if (kv_idx < p.S) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 uk, uv;
+              uint32_t* pk = reinterpret_cast<uint32_t*>(&uk);
+              uint32_t* pv = reinterpret_cast<uint32_t*>(&uv);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int idx = q4 * 8 + e * 2;
+                pk[e] = pack_bf16x2(__uint_as_float(rk[idx]) * p.scale, __uint_as_float(rk[idx + 1]) * p.scale);
+                pv[e] = pack_bf16x2(__uint_as_float(rv[idx]), __uint_as_float(rv[idx + 1]));
+              }
+              *reinterpret_cast<uint4*>(dkr + c * 32 + q4 * 8) = uk;
+              *reinterpret_cast<uint4*>(dvr + c * 32 + q4 * 8) = uv;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) error_drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// delta[b,h,s] = sum_d O * dO and nlse2 = -lse * log2(e); one warp per (token, head).
+__global__ void attn_bwd_prep2_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                      const float* __restrict__ lse, float* __restrict__ delta,
+                                      float* __restrict__ nlse2, int B, int S, int Hq, int HD, long long ldo,
+                                      long long lddo) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * Hq;
+  if (gw >= total) return;
+  const int h = (int)(gw % Hq);
+  const long long t = gw / Hq;
+  const __nv_bfloat16* op = o + t * ldo + h * HD;
+  const __nv_bfloat16* dp = dout + t * lddo + h * HD;
+  float acc = 0.f;
+  for (int d = lane * 4; d < HD; d += 128) {
+    const uint2 a = *reinterpret_cast<const uint2*>(op + d);
+    const uint2 g = *reinterpret_cast<const uint2*>(dp + d);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
+    acc += a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const long long bb = t / S, s = t % S;
+    const long long idx = (bb * Hq + h) * S + s;
+    delta[idx] = acc;
+    nlse2[idx] = -lse[idx] * 1.4426950408889634f;
+  }
+}
+
+template <int HD>
+static int launch_fa_bwd2(const void* q, const void* k, const void* v, const void* dout, long long ldq, long long ldk,
+                          long long ldv, long long lddo, FaBwd2Params& p, cudaStream_t stream) {
+  using Cfg = FaBwd2Cfg<HD>;
+  static bool configured = false;
+  auto kern = fa_bwd2_kernel<HD>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return GFH_CUDA;
+    configured = true;
+  }
+  const uint64_t T = (uint64_t)p.B * p.S;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)p.Hq * HD, ldq * 2, B2_Q, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tdo, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)p.Hq * HD, lddo * 2, B2_Q, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)p.Hkv * HD, ldk * 2, B2_KV, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)p.Hkv * HD, ldv * 2, B2_KV, 64);
+  if (rc) return rc;
+  dim3 grid(p.Hkv, p.S / B2_KV, p.B);
+  kern<<<grid, B2_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+// delta and nlse2 are fp32 [B, Hq, S]; dq_acc (fp32 [B*S, Hq*HD]) is zeroed when given.
+GF_API int gf_attn_bwd_prep2(const void* o, const void* dout, const float* lse, float* delta, float* nlse2,
+                             float* dq_acc, int B, int S, int Hq, int HD, long long ldo, long long lddo,
+                             void* stream) {
+  gf::enter();
+  if ((HD % 4) || (ldo % 4) || (lddo % 4)) return GFH_BAD_ARG;
+  const long long warps = (long long)B * S * Hq;
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  attn_bwd_prep2_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta, nlse2, B, S, Hq, HD, ldo, lddo);
+  if (dq_acc) cudaMemsetAsync(dq_acc, 0, (size_t)B * S * Hq * HD * sizeof(float), (cudaStream_t)stream);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+// dq_acc: fp32 [B*S, Hq*HD] zero-initialised (gf_attn_bwd_prep2 does it); it receives dQ / scale, so convert
+// afterwards with gf_cast_f32_to_bf16_2d(..., scale). S must be a multiple of 128.
+GF_API int gf_flash_attn_bwd2(const void* q, const void* k, const void* v, const void* dout, const float* nlse2,
+                              const float* delta, float* dq_acc, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                              int head_dim, long long ldq, long long ldk, long long ldv, long long lddo,
+                              long long lddk, long long lddv, float scale, int causal, int* status, void* stream) {
+  gf::enter();
+  if (B <= 0 || S <= 0 || (S % B2_KV) || Hq % Hkv) return GFH_BAD_ARG;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (lddk % 8) || (lddv % 8)) return GFH_BAD_ARG;
+  FaBwd2Params p;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
+  p.nlse2 = nlse2; p.delta = delta; p.dq_acc = dq_acc;
+  p.dK = (__nv_bfloat16*)dk; p.lddk = lddk; p.dV = (__nv_bfloat16*)dv; p.lddv = lddv; p.status = status;
+  if (head_dim == 128) return launch_fa_bwd2<128>(q, k, v, dout, ldq, ldk, ldv, lddo, p, (cudaStream_t)stream);
+  if (head_dim == 64) return launch_fa_bwd2<64>(q, k, v, dout, ldq, ldk, ldv, lddo, p, (cudaStream_t)stream);
+  return GFH_BAD_ARG;
+}

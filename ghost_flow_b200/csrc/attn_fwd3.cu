@@ -79,8 +79,10 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (p.S + 2 * F3_TILE - 1) / (2 * F3_TILE);
-  const int qb = n_qb - 1 - (int)blockIdx.x;  // heaviest blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // CTAs are dispatched x-fastest: all heads of the heaviest query block first, then the next block, so the
+  // long CTAs (most KV tiles under a causal mask) start first and the short ones fill the tail.
+  const int qb = n_qb - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int n_kv_all = (p.S + F3_TILE - 1) / F3_TILE;
   const int row_base = b * p.S;
@@ -255,10 +257,15 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (kv >= p.S || (p.causal && kv > q_idx)) sv[i] = 0xff800000u;  // -inf
         }
       }
-      float mx = -INFINITY;
+      // four independent chains: a single running maximum would serialise 64 dependent instructions
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < F3_TILE; i += 2)
-        mx = fmaxf(mx, fmaxf(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])));
+      for (int i = 0; i < F3_TILE; i += 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          mx4[e] = fmaxf(mx4[e], fmaxf(__uint_as_float(sv[i + 2 * e]), __uint_as_float(sv[i + 2 * e + 1])));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // ---- reference maximum: move it (and rescale O, l) only when the row maximum grew a lot. The commit
       // behind s_full also covered P V (j - 1), so O is quiescent here.
       if (j == 0) {
@@ -365,7 +372,7 @@ static int launch_fa3(const void* q, const void* k, const void* v, long long ldq
   if (rc) return rc;
   rc = make_tmap_2d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)p.Hkv * HD, ldv * 2, F3_TILE, 64);
   if (rc) return rc;
-  dim3 grid((p.S + 2 * F3_TILE - 1) / (2 * F3_TILE), p.Hq, p.B);
+  dim3 grid(p.Hq, (p.S + 2 * F3_TILE - 1) / (2 * F3_TILE), p.B);
   kern<<<grid, F3_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }

@@ -39,6 +39,7 @@ CUDA_SOURCES = [
     "attn_fwd2.cu",
     "attn_fwd3.cu",
     "attn_bwd.cu",
+    "attn_bwd2.cu",
     "attn_decode.cu",
     "comm_kernels.cu",
     "moe_kernels.cu",

@@ -52,6 +52,8 @@ _SIGS = {
     "gf_attn_decode": [P, L, P, P, I, P, I, P, L, I, I, I, I, F, I, P, P],
     "gf_flash_attn_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
     "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
+    "gf_flash_attn_bwd2": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
+    "gf_attn_bwd_prep2": [P, P, P, P, P, P, I, I, I, I, L, L, P],
     "gf_cast_f32_to_bf16_2d": [P, P, L, I, L, L, F, P],
 }
 
@@ -193,3 +195,36 @@ def flash_fwd_fn():
     if which == "2":
         return lib.gf_flash_attn_fwd2
     return lib.gf_flash_attn_fwd3
+
+
+def flash_attn_backward(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D, ld, scale, causal) -> None:
+    """Launches the attention backward (statistics kernel, main kernel, fp32 -> bf16 conversion of dQ) on the
+    current stream. All tensors are bf16 CUDA tensors or views; ``ld`` maps ``q k v o do dq dk dv`` to their row
+    pitch in elements. ``GF_FA_BWD=1`` selects the first-generation kernel (compute warps also drain dQ)."""
+    lib = cuda_lib()
+    st = stream_ptr()
+    dev = q.device
+    status = status_word(dev).data_ptr()
+    delta = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+    dq_acc = torch.empty((B * S, Hq * D), dtype=torch.float32, device=dev)
+    c = 1 if causal else 0
+    if os.environ.get("GF_FA_BWD", "2") == "1":
+        check_rc(lib.gf_attn_bwd_prep(o.data_ptr(), do.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), B, S, Hq, D,
+                                      ld["o"], ld["do"], st), "gf_attn_bwd_prep")
+        check_rc(lib.gf_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                       delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq,
+                                       Hkv, D, ld["q"], ld["k"], ld["v"], ld["do"], ld["dk"], ld["dv"], float(scale),
+                                       c, status, st), "gf_flash_attn_bwd")
+        dq_scale = 1.0
+    else:
+        nlse2 = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        check_rc(lib.gf_attn_bwd_prep2(o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                                       nlse2.data_ptr(), dq_acc.data_ptr(), B, S, Hq, D, ld["o"], ld["do"], st),
+                 "gf_attn_bwd_prep2")
+        check_rc(lib.gf_flash_attn_bwd2(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), nlse2.data_ptr(),
+                                        delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq,
+                                        Hkv, D, ld["q"], ld["k"], ld["v"], ld["do"], ld["dk"], ld["dv"],
+                                        float(scale), c, status, st), "gf_flash_attn_bwd2")
+        dq_scale = float(scale)   # the main kernel leaves dQ / scale in the accumulator
+    check_rc(lib.gf_cast_f32_to_bf16_2d(dq_acc.data_ptr(), dq.data_ptr(), B * S, Hq * D, Hq * D, ld["dq"], dq_scale,
+                                        st), "gf_cast_f32_to_bf16_2d")

@@ -440,22 +440,12 @@ class _FlashAttnFn(torch.autograd.Function):
         if S % 128:
             raise RuntimeError("flash attention backward needs a sequence length that is a multiple of 128")
         do = do.contiguous()
-        lib = _lib.cuda_lib()
-        delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
-        dq_acc = torch.empty((B * S, Hq * D), dtype=torch.float32, device=q.device)
         # one packed gradient buffer [B,S,(Hq+2Hkv),D] so a fused QKV projection sees a single tensor
         dqkv = torch.empty((B, S, Hq + 2 * Hkv, D), dtype=q.dtype, device=q.device)
         dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
         ldg = (Hq + 2 * Hkv) * D
-        st = _lib.stream_ptr()
-        _rc(lib.gf_attn_bwd_prep(o.data_ptr(), do.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), B, S, Hq, D,
-                                 Hq * D, Hq * D, st), "gf_attn_bwd_prep")
-        _rc(lib.gf_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                                  delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq, Hkv,
-                                  D, ldq, ldk, ldv, Hq * D, ldg, ldg, float(scale), 1 if causal else 0,
-                                  _lib.status_word(q.device).data_ptr(), st), "gf_flash_attn_bwd")
-        _rc(lib.gf_cast_f32_to_bf16_2d(dq_acc.data_ptr(), dq.data_ptr(), B * S, Hq * D, Hq * D, ldg, 1.0, st),
-            "gf_cast_f32_to_bf16_2d")
+        _lib.flash_attn_backward(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D,
+                                 dict(q=ldq, k=ldk, v=ldv, o=Hq * D, do=Hq * D, dq=ldg, dk=ldg, dv=ldg), scale, causal)
         return dq, dk, dv, None, None
 
 

@@ -165,19 +165,9 @@ def attn_bwd(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D, causal=True, sca
     """Writes dq/dk/dv (row-pitched views, e.g. slices of one packed dqkv buffer)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if _k(q):
-        lib = _lib.cuda_lib()
-        st = _lib.stream_ptr()
-        delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
-        dq_acc = torch.empty((B * S, Hq * D), dtype=torch.float32, device=q.device)
-        _rc(lib.gf_attn_bwd_prep(o.data_ptr(), do.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), B, S, Hq, D,
-                                 o.stride(0), do.stride(0), st), "gf_attn_bwd_prep")
-        _rc(lib.gf_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                                  delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq, Hkv,
-                                  D, q.stride(0), k.stride(0), v.stride(0), do.stride(0), dk.stride(0),
-                                  dv.stride(0), float(scale), 1 if causal else 0,
-                                  _lib.status_word(q.device).data_ptr(), st), "gf_flash_attn_bwd")
-        _rc(lib.gf_cast_f32_to_bf16_2d(dq_acc.data_ptr(), dq.data_ptr(), B * S, Hq * D, Hq * D, dq.stride(0), 1.0,
-                                       st), "gf_cast_f32_to_bf16_2d")
+        _lib.flash_attn_backward(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D,
+                                 dict(q=q.stride(0), k=k.stride(0), v=v.stride(0), o=o.stride(0), do=do.stride(0),
+                                      dq=dq.stride(0), dk=dk.stride(0), dv=dv.stride(0)), scale, causal)
         return
     G = Hq // Hkv
     qf = q.float().reshape(B, S, Hq, D).transpose(1, 2)

@@ -244,7 +244,7 @@ def test_flash_attention_fwd(B, S, Hq, Hkv, D, causal, kernel_status):
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [
     (1, 128, 1, 1, 128, True), (1, 256, 2, 2, 128, True), (2, 512, 4, 2, 128, True), (1, 256, 2, 2, 64, True),
-    (1, 256, 2, 1, 128, False)])
+    (1, 256, 2, 1, 128, False), (1, 1024, 4, 1, 128, True), (1, 384, 2, 2, 64, False)])
 def test_flash_attention_bwd(B, S, Hq, Hkv, D, causal, kernel_status):
     ops = _ops()
     qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
@@ -261,6 +261,23 @@ def test_flash_attention_bwd(B, S, Hq, Hkv, D, causal, kernel_status):
     assert _rel_err(gv, rv) < 3e-2, "dV"
     assert _rel_err(gk, rk) < 3e-2, "dK"
     assert _rel_err(gq, rq) < 3e-2, "dQ"
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 512, 4, 2, 128, True), (1, 256, 2, 2, 64, False)])
+def test_flash_attention_bwd_first_generation_kernel(B, S, Hq, Hkv, D, causal, kernel_status, monkeypatch):
+    """The backward kernel whose compute warps also drain dQ stays available (GF_FA_BWD=1)."""
+    monkeypatch.setenv("GF_FA_BWD", "1")
+    ops = _ops()
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    g = torch.randn_like(o)
+    o.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    qr, kr, vr = ref_in[:, :, :Hq], ref_in[:, :, Hq:Hq + Hkv], ref_in[:, :, Hq + Hkv:]
+    ops.attention_ref(qr, kr, vr, causal=causal).backward(g.float())
+    torch.cuda.synchronize()
+    assert _rel_err(qkv.grad, ref_in.grad) < 3e-2
 
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 256, 2, 2, 128, True), (1, 384, 2, 1, 64, False)])
