@@ -39,6 +39,7 @@ struct Fa3Params {
   long long ldo;
   float* lse;
   int* status;
+  int head_group;   // heads whose CTAs are dispatched together (see the kernel's block decoding)
 };
 
 template <int HD>
@@ -79,10 +80,22 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (p.S + 2 * F3_TILE - 1) / (2 * F3_TILE);
-  // CTAs are dispatched x-fastest: all heads of the heaviest query block first, then the next block, so the
-  // long CTAs (most KV tiles under a causal mask) start first and the short ones fill the tail.
-  const int qb = n_qb - 1 - (int)blockIdx.y;
-  const int h = blockIdx.x, b = blockIdx.z;
+  // CTAs are dispatched in linear block order. Heads are taken in groups of head_group: inside a group the heaviest
+  // query block (most KV tiles under a causal mask) of every head comes first, then the next block, so long CTAs
+  // start first and short ones fill the tail, while the CTAs in flight at any time belong to few heads, whose K / V
+  // (re-read by every query block) stay in L2.
+  int qb, h;
+  {
+    const int H = gridDim.x, NT = gridDim.y;
+    const int lin = blockIdx.x + H * blockIdx.y;
+    const int gs = p.head_group;
+    const int g = lin / (gs * NT);
+    const int rem = lin - g * gs * NT;
+    const int gs_g = min(gs, H - g * gs);
+    qb = n_qb - 1 - rem / gs_g;
+    h = g * gs + rem % gs_g;
+  }
+  const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int n_kv_all = (p.S + F3_TILE - 1) / F3_TILE;
   const int row_base = b * p.S;
@@ -390,6 +403,7 @@ GF_API int gf_flash_attn_fwd3(const void* q, const void* k, const void* v, void*
   Fa3Params p;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
   p.O = (__nv_bfloat16*)o; p.ldo = ldo; p.lse = lse; p.status = status;
+  p.head_group = attention_head_group(Hq);
   if (head_dim == 128) return launch_fa3<128>(q, k, v, ldq, ldk, ldv, p, (cudaStream_t)stream);
   if (head_dim == 64) return launch_fa3<64>(q, k, v, ldq, ldk, ldv, p, (cudaStream_t)stream);
   return GFH_BAD_ARG;

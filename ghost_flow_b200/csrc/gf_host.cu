@@ -1,6 +1,7 @@
 // Host-side helpers: driver entry point lookup, tensor-map encoding, device facts,
 // and a per-device status word that kernels write their bounded-wait error codes to.
 #include "gf_host.h"
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -99,6 +100,18 @@ int sm_count() {
     cached[dev] = n > 0 ? n : 148;
   }
   return cached[dev];
+}
+
+int attention_head_group(int heads) {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("GF_ATT_GROUP");
+    env = e ? atoi(e) : 0;
+  }
+  int g = env > 0 ? env : 8;
+  if (g > heads) g = heads;
+  if (g < 1) g = 1;
+  return g;
 }
 
 }  // namespace gf

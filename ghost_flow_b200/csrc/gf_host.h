@@ -39,6 +39,9 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
 
 int sm_count();
 
+// Heads per dispatch group of the attention kernels: GF_ATT_GROUP when set (tuning), else 8, clamped to [1, heads].
+int attention_head_group(int heads);
+
 // Binds the calling thread to the device selected with gf_set_device (see gf_host.cu).
 void enter();
 // Launchers that start more than one kernel report the extra ones here (enter() counts one).

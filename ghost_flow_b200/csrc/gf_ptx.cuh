@@ -67,10 +67,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false when the limit ran out.
+// Non-blocking probe of a phase (try_wait may suspend the thread for a hardware time slice before it reports
+// "not yet"; a thread that serves several barriers in turn must not sit in one of them).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// try_wait already suspends the thread for a hardware-chosen slice, so the loop polls back to back; the
+// sleep only starts once a wait has clearly become a long one (a sleeping thread notices the completed phase
+// late, which puts the sleep granularity on every hand-off of a pipeline).
+#ifndef GF_SPIN_FAST_POLLS
+#define GF_SPIN_FAST_POLLS 20000u
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = GF_WAIT_LIMIT) {
   for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(32);
+    if (it > GF_SPIN_FAST_POLLS) __nanosleep(64);
   }
   return false;
 }
@@ -202,6 +221,41 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t adesc, uint
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+// ---------------------------------------------------------------- warp-uniform issue
+// The variants below are meant to be executed by ALL lanes of the issuing warp in uniform control flow, with
+// `leader` true in exactly one lane (elect_one()): the instruction itself is predicated. Descriptors and
+// addresses are then warp-uniform values, which the compiler keeps in uniform registers (where tcgen05.mma
+// wants them); issuing from inside an `if (lane == 0)` branch instead makes every operand a per-thread value
+// that has to be moved into a uniform register in front of each MMA.
+__device__ __forceinline__ void umma_bf16_ss_u(bool leader, uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"((uint32_t)leader)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts_u(bool leader, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"((uint32_t)leader)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_u(bool leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n"
+      ::"r"(smem_u32(bar)), "r"((uint32_t)leader)
+      : "memory");
 }
 
 // Load 32 consecutive fp32 columns of this warp's 32 TMEM lanes (one row per thread).

@@ -54,6 +54,7 @@ _SIGS = {
     "gf_attn_bwd_prep": [P, P, P, P, I, I, I, I, L, L, P],
     "gf_flash_attn_bwd2": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, F, I, P, P],
     "gf_attn_bwd_prep2": [P, P, P, P, P, P, I, I, I, I, L, L, P],
+    "gf_dq_tiles_to_bf16": [P, P, I, I, I, I, L, F, P],
     "gf_cast_f32_to_bf16_2d": [P, P, L, I, L, L, F, P],
 }
 
@@ -215,7 +216,8 @@ def flash_attn_backward(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D, ld, s
                                        delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq,
                                        Hkv, D, ld["q"], ld["k"], ld["v"], ld["do"], ld["dk"], ld["dv"], float(scale),
                                        c, status, st), "gf_flash_attn_bwd")
-        dq_scale = 1.0
+        check_rc(lib.gf_cast_f32_to_bf16_2d(dq_acc.data_ptr(), dq.data_ptr(), B * S, Hq * D, Hq * D, ld["dq"], 1.0,
+                                            st), "gf_cast_f32_to_bf16_2d")
     else:
         nlse2 = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
         check_rc(lib.gf_attn_bwd_prep2(o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
@@ -225,6 +227,6 @@ def flash_attn_backward(q, k, v, o, do, lse, dq, dk, dv, B, S, Hq, Hkv, D, ld, s
                                         delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq,
                                         Hkv, D, ld["q"], ld["k"], ld["v"], ld["do"], ld["dk"], ld["dv"],
                                         float(scale), c, status, st), "gf_flash_attn_bwd2")
-        dq_scale = float(scale)   # the main kernel leaves dQ / scale in the accumulator
-    check_rc(lib.gf_cast_f32_to_bf16_2d(dq_acc.data_ptr(), dq.data_ptr(), B * S, Hq * D, Hq * D, ld["dq"], dq_scale,
-                                        st), "gf_cast_f32_to_bf16_2d")
+        # the main kernel leaves dQ / scale in the accumulator, tile by tile ([B, Hq, S / 64, 64, D])
+        check_rc(lib.gf_dq_tiles_to_bf16(dq_acc.data_ptr(), dq.data_ptr(), B, S, Hq, D, ld["dq"], float(scale), st),
+                 "gf_dq_tiles_to_bf16")
