@@ -4,8 +4,11 @@
   (serialize.rs:223-456), chosen by ``fmt`` / detected by magic on load.
 * ``Checkpoint`` + ``save_checkpoint`` / ``load_checkpoint``: GFCP (ghostflow-nn/src/serialization.rs:12-284):
   parameters, optional flat optimizer state, epoch, loss and free-form ``extra`` strings.
-* ``save_sharded`` / ``load_sharded`` / ``consolidate``: one GFCP per rank for ZeRO-partitioned state
-  (``extra`` records rank, world, step) and a merge into one GHOSTFLW file.
+* ``save_sharded`` / ``load_sharded`` / ``consolidate`` / ``load_consolidated``: one GFCP per rank for
+  ZeRO-partitioned state (``extra`` records rank, world, step and the flat layout of every unit, so the shards can
+  be cut again for another world size) and a merge into one file, optionally with the optimizer moments.
+* ``training_state_extra`` / ``restore_training_state``: scheduler, loss scaler, data position and generator
+  state in the ``extra`` section.
 
 Payloads are always float32 on disk, exactly like the reference; the dtype code of GHOSTFLW records the
 tensor's original type so that ``load_state_dict(..., restore_dtype=True)`` can cast back.
@@ -188,34 +191,162 @@ def load_checkpoint(path) -> Checkpoint:
     return ck
 
 
+# ------------------------------------------------------------------------------------------- resume state
+def capture_rng_state(device=None) -> str:
+    """Generator states of the CPU and (when ``device`` is a CUDA device) that device, as one hex string for the
+    ``extra`` section of a GFCP checkpoint. The reference saves no generator state (its RNG is ``thread_rng()``
+    everywhere: ghostflow-core/src/tensor.rs:94,105), so a resumed run could not repeat an uninterrupted one."""
+    parts = [torch.get_rng_state().numpy().tobytes().hex()]
+    if device is not None and torch.device(device).type == "cuda":
+        parts.append(torch.cuda.get_rng_state(torch.device(device)).cpu().numpy().tobytes().hex())
+    return "|".join(parts)
+
+
+def restore_rng_state(state: str, device=None) -> None:
+    import numpy as np
+
+    parts = state.split("|")
+    torch.set_rng_state(torch.from_numpy(np.frombuffer(bytes.fromhex(parts[0]), dtype=np.uint8).copy()))
+    if len(parts) > 1 and device is not None and torch.device(device).type == "cuda":
+        torch.cuda.set_rng_state(torch.from_numpy(np.frombuffer(bytes.fromhex(parts[1]), dtype=np.uint8).copy()),
+                                 torch.device(device))
+
+
+def training_state_extra(scheduler=None, scaler=None, data_position: int | None = None, rng: bool = True,
+                         device=None) -> dict:
+    """Everything a run needs beyond weights and moments, as the string map that GFCP's ``extra`` section holds
+    (ghostflow-nn/src/serialization.rs:12-37 has the section but nothing writes resume state into it): learning-rate
+    scheduler, loss scaler, position in the data stream, generator states."""
+    import json
+
+    ex = {}
+    if scheduler is not None:
+        ex["lr_scheduler"] = json.dumps(scheduler.state_dict())
+    if scaler is not None:
+        ex["grad_scaler"] = json.dumps(scaler.state_dict())
+    if data_position is not None:
+        ex["data_position"] = str(int(data_position))
+    if rng:
+        ex["rng_state"] = capture_rng_state(device)
+    return ex
+
+
+def restore_training_state(extra: dict, scheduler=None, scaler=None, device=None) -> dict:
+    """Inverse of :func:`training_state_extra`; returns ``{"data_position": int}`` when one was saved."""
+    import json
+
+    out = {}
+    if scheduler is not None and "lr_scheduler" in extra:
+        scheduler.load_state_dict(json.loads(extra["lr_scheduler"]))
+    if scaler is not None and "grad_scaler" in extra:
+        scaler.load_state_dict(json.loads(extra["grad_scaler"]))
+    if "data_position" in extra:
+        out["data_position"] = int(extra["data_position"])
+    if "rng_state" in extra:
+        restore_rng_state(extra["rng_state"], device)
+    return out
+
+
 # ------------------------------------------------------------------------------------------- sharded (ZeRO)
+def _shard_path(directory, rank: int, world: int) -> str:
+    return os.path.join(directory, f"shard_{rank:05d}_of_{world:05d}.gfcp")
+
+
 def save_sharded(engine, directory, epoch: int = 0, loss: float = 0.0, extra: dict | None = None) -> str:
-    """One GFCP file per rank with that rank's fp32 master shards and Adam moments."""
+    """One GFCP file per rank with that rank's fp32 master shards and Adam moments. ``extra`` records rank,
+    world, step, ZeRO stage and, per unit, the flat layout (``flat.<unit>`` = ``numel:padded:shard_numel:lo``),
+    which is what :func:`load_sharded` needs to cut the state again for another world size. Pass
+    :func:`training_state_extra` as ``extra`` to carry scheduler / scaler / data position / generator state."""
     os.makedirs(directory, exist_ok=True)
     st = engine.shard_state()
     params = {k: v for k, v in st.items() if k.endswith(".master")}
     opt = {k: v for k, v in st.items() if k.endswith(".exp_avg") or k.endswith(".exp_avg_sq")}
-    ex = {"rank": engine.rank, "world": engine.world, "step": st["step"], "stage": 3, **(extra or {})}
-    path = os.path.join(directory, f"shard_{engine.rank:05d}_of_{engine.world:05d}.gfcp")
+    ex = {"rank": engine.rank, "world": engine.world, "step": st["step"], "stage": 3}
+    for name, lay in engine.flat_layout().items():
+        ex[f"flat.{name}"] = f"{lay['numel']}:{lay['padded']}:{lay['shard_numel']}:{lay['lo']}"
+    ex.update(extra or {})
+    path = _shard_path(directory, engine.rank, engine.world)
     save_checkpoint(Checkpoint(params, opt, epoch, loss, "zero3-shard", extra=ex), path)
     return path
 
 
+def _find_source_world(directory) -> int:
+    import re
+
+    worlds = {int(m.group(1)) for f in os.listdir(directory)
+              if (m := re.match(r"shard_\d{5}_of_(\d{5})\.gfcp$", f))}
+    if len(worlds) != 1:
+        raise IOError(f"{directory}: expected the shards of exactly one world size, found {sorted(worlds)}")
+    return worlds.pop()
+
+
+def _recut(engine, directory, src_world: int) -> tuple[dict, Checkpoint]:
+    """Builds this rank's shards from the files of another world size. Every unit is one flat buffer whose
+    logical prefix ``[0, numel)`` does not depend on the world size (only the zero padding behind it does), so a
+    new shard ``[lo, lo + shard_numel)`` is the concatenation of the overlapping pieces of the old shards."""
+    layout = engine.flat_layout()
+    keys = ("master", "exp_avg", "exp_avg_sq")
+    out = {f"{u}.{k}": torch.zeros(lay["shard_numel"], dtype=torch.float32) for u, lay in layout.items() for k in keys}
+    first = None
+    for r in range(src_world):
+        ck = load_checkpoint(_shard_path(directory, r, src_world))
+        first = first or ck
+        for u, lay in layout.items():
+            numel, _, s_shard, s_lo = (int(x) for x in ck.extra[f"flat.{u}"].split(":"))
+            if numel != lay["numel"]:
+                raise ValueError(f"unit {u}: checkpoint has {numel} elements, engine has {lay['numel']}")
+            lo = max(lay["lo"], s_lo)
+            hi = min(lay["lo"] + lay["shard_numel"], s_lo + s_shard, numel)
+            if hi <= lo:
+                continue
+            for k in keys:
+                src = ck.parameters[f"{u}.master"] if k == "master" else ck.optimizer_state[f"{u}.{k}"]
+                out[f"{u}.{k}"][lo - lay["lo"]:hi - lay["lo"]] = src.reshape(-1)[lo - s_lo:hi - s_lo]
+    return out, first
+
+
 def load_sharded(engine, directory) -> Checkpoint:
-    path = os.path.join(directory, f"shard_{engine.rank:05d}_of_{engine.world:05d}.gfcp")
-    ck = load_checkpoint(path)
-    if int(ck.extra["world"]) != engine.world:
-        raise ValueError(f"checkpoint was written with world size {ck.extra['world']}, engine has {engine.world}; "
-                         "use consolidate() and engine.load_unit() to re-shard")
-    st = {"step": int(ck.extra["step"])}
-    st.update({k: v.to(engine.device) for k, v in ck.parameters.items()})
-    st.update({k: v.to(engine.device) for k, v in (ck.optimizer_state or {}).items()})
+    """Restores the engine from :func:`save_sharded` files. With the same world size every rank reads its own
+    file; with a different one (a job restarted on fewer or more GPUs) every rank re-cuts its shards from the
+    files of the old world. Returns rank-local checkpoint metadata (``extra`` holds the saved resume state)."""
+    src_world = _find_source_world(directory)
+    if src_world == engine.world:
+        ck = load_checkpoint(_shard_path(directory, engine.rank, engine.world))
+        st = {"step": int(ck.extra["step"])}
+        st.update({k: v.to(engine.device) for k, v in ck.parameters.items()})
+        st.update({k: v.to(engine.device) for k, v in (ck.optimizer_state or {}).items()})
+    else:
+        tensors, ck = _recut(engine, directory, src_world)
+        st = {"step": int(ck.extra["step"])}
+        st.update({k: v.to(engine.device) for k, v in tensors.items()})
     engine.load_shard_state(st)
     return ck
 
 
-def consolidate(engine, path, fmt: str = "ghostflw") -> None:
-    """Gathers the full fp32 weights on every rank and lets rank 0 write one state-dict file."""
+def consolidate(engine, path, fmt: str = "ghostflw", with_optimizer: bool = False) -> None:
+    """Gathers the full fp32 weights on every rank and lets rank 0 write one file: a GHOSTFLW / safetensors
+    state dict, or with ``with_optimizer`` a GFCP checkpoint that also carries the gathered Adam moments
+    (``exp_avg.<name>``, ``exp_avg_sq.<name>``) and the step, from which :func:`load_consolidated` restores
+    an engine of any world size."""
     sd = engine.state_dict(master=True)
+    if not with_optimizer:
+        if engine.rank == 0:
+            save_state_dict(sd, path, fmt=fmt)
+        return
+    opt = {}
+    for prefix, which in (("exp_avg", "m"), ("exp_avg_sq", "v")):
+        for k, v in engine.state_dict(which=which).items():
+            opt[f"{prefix}.{k}"] = v
     if engine.rank == 0:
-        save_state_dict(sd, path, fmt=fmt)
+        save_checkpoint(Checkpoint(sd, opt, 0, 0.0, "zero3-consolidated", extra={"step": engine.step_count}), path)
+
+
+def load_consolidated(engine, path) -> Checkpoint:
+    """Restores weights, moments and step of a ZeRO engine (any world size) from :func:`consolidate`
+    ``(with_optimizer=True)`` output; every rank reads the file and keeps its own slices."""
+    ck = load_checkpoint(path)
+    engine.load_full_state(ck.parameters, {k[len("exp_avg."):]: v for k, v in ck.optimizer_state.items()
+                                           if k.startswith("exp_avg.")},
+                           {k[len("exp_avg_sq."):]: v for k, v in ck.optimizer_state.items()
+                            if k.startswith("exp_avg_sq.")}, int(ck.extra.get("step", 0)))
+    return ck

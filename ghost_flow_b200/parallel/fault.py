@@ -164,3 +164,38 @@ def bounded_device_wait(pad: torch.Tensor, index: int, world: int, value: int, l
     code = int(status.item())
     status.zero_()
     return code
+
+
+# ------------------------------------------------------------------ elastic restart
+RESTART_MARKER = "RESTART.json"
+EXIT_RESTART = 75   # EX_TEMPFAIL: the job may be started again (from the marker's checkpoint, at its world size)
+
+
+def write_restart_marker(directory, checkpoint_dir, failed_ranks, world: int, step: int, detail: str = "") -> str:
+    """Called by a surviving rank after :class:`PeerFailure` (between steps, nothing in flight): records where
+    to resume from and with how many ranks. The launcher (or the operator) reads it with
+    :func:`read_restart_marker`, starts ``new_world`` ranks, and every rank calls ``io.load_sharded``, which
+    re-cuts the shards of the old world size."""
+    import json
+    import os
+
+    os.makedirs(directory, exist_ok=True)
+    path = os.path.join(directory, RESTART_MARKER)
+    tmp = path + f".tmp{os.getpid()}"
+    with open(tmp, "w") as f:
+        json.dump({"checkpoint_dir": os.fspath(checkpoint_dir), "failed_ranks": sorted(int(r) for r in failed_ranks),
+                   "old_world": int(world), "new_world": int(world) - len(set(failed_ranks)), "step": int(step),
+                   "detail": detail}, f)
+    os.replace(tmp, path)   # atomic: several survivors may write the same content
+    return path
+
+
+def read_restart_marker(directory):
+    import json
+    import os
+
+    path = os.path.join(directory, RESTART_MARKER)
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f)

@@ -32,7 +32,9 @@ from .zero3 import Comm
 # signal-pad layout (int32 indices); writer rank r writes at [base + r] of the reader's pad
 PAD_READY = 0        # + slot * 8 + src : gradient buffer `slot` of rank src is complete (value = use count)
 PAD_CONSUMED = 16    # + slot * 8 + src : rank src has finished reading my gradient buffer `slot`
-PAD_VERSION = 64     # + unit * 8 + src : rank src's weight shard of `unit` holds the weights after `value` updates
+PAD_VERSION = 64     # + unit * 8 + src : rank src's weight shard of `unit` has been through `value` fused updates
+                     #                    of THIS process group's lifetime (not the optimizer step: a job resumed
+                     #                    from a checkpoint starts with zeroed pads and step_count = N)
 PAD_INTS = 4096
 
 
@@ -72,6 +74,9 @@ class FusedComm(Comm):
         self.rs_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.slot_use = [0, 0]
         self.ag_epoch = 0
+        # Fused updates launched so far per unit. Every rank launches the same sequence, so this local count is
+        # also the version that a gather launched now must see in the peers' shards.
+        self.unit_updates: dict[int, int] = {}
         # dry_run = True keeps every kernel of the step except the traffic between ranks (local shard copy, local
         # AdamW on the unreduced gradient slice). The numbers it produces are wrong on purpose: it exists only to
         # time the compute-only step, so that exposed communication = full step - dry step can be reported.
@@ -123,8 +128,12 @@ class FusedComm(Comm):
         return self.arena_mc + (t.data_ptr() - self.arena.data_ptr())
 
     # ------------------------------------------------------------------ collectives
-    def all_gather_unit(self, unit, unit_index: int, full: torch.Tensor, need_version: int) -> None:
-        """Pulls every rank's shard of ``unit`` into ``full`` on the current stream."""
+    def all_gather_unit(self, unit, unit_index: int, full: torch.Tensor, need_version: int | None = None) -> None:
+        """Pulls every rank's shard of ``unit`` into ``full`` on the current stream. The copy of rank r's shard
+        waits until r has published the version this rank expects: the number of fused updates of the unit
+        launched so far (``need_version`` overrides it)."""
+        if need_version is None:
+            need_version = self.unit_updates.get(unit_index, 0)
         if self.dry_run:
             full[self.rank * unit.shard_numel:(self.rank + 1) * unit.shard_numel].copy_(unit.shard)
             return
@@ -165,10 +174,12 @@ class FusedComm(Comm):
                          grad_scale=grad_scale)
             return
         use = self.slot_use[slot]
+        version = self.unit_updates.get(unit_index, 0) + 1
+        self.unit_updates[unit_index] = version
         rc = self.lib.gf_rs_adamw_fused(
             self.peer_ptrs(g_full), self.mc_ptr(g_full), self.pad_ptrs, self.world, self.rank, unit.lo,
             unit.shard_numel, unit.master.data_ptr(), unit.m.data_ptr(), unit.v.data_ptr(), unit.shard.data_ptr(),
             float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step), float(grad_scale),
-            PAD_READY + slot * 8, use, PAD_CONSUMED + slot * 8, use, PAD_VERSION + unit_index * 8, int(step),
+            PAD_READY + slot * 8, use, PAD_CONSUMED + slot * 8, use, PAD_VERSION + unit_index * 8, version,
             self.rs_counter.data_ptr(), 0, 0, _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check_rc(rc, "gf_rs_adamw_fused")

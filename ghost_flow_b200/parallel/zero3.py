@@ -159,6 +159,9 @@ class Zero3LlamaEngine:
             self.gshard = torch.empty(max(u.shard_numel for u in self.units), dtype=dtype, device=self.device)
         self._rope = None
         self.last_stats = {}
+        # kernel status word of the previous steps, copied to pinned memory without stalling the stream
+        self._status_host = None
+        self._status_event = None
 
     # ------------------------------------------------------------------ init
     def _init_params(self, seed):
@@ -191,9 +194,10 @@ class Zero3LlamaEngine:
         unit.master.copy_(sl)
         unit.shard.copy_(sl.to(self.dtype))
 
-    def gather_unit(self, unit: _Unit, master: bool = False) -> dict:
-        """Full named tensors of a unit on every rank (fp32 master copy or the bf16 weights)."""
-        src = unit.master if master else unit.shard
+    def gather_unit(self, unit: _Unit, master: bool = False, which: str | None = None) -> dict:
+        """Full named tensors of a unit on every rank: the bf16 weights, the fp32 master copy (``master``), or
+        with ``which`` = "m" / "v" the first / second Adam moment."""
+        src = {"m": unit.m, "v": unit.v}[which] if which else (unit.master if master else unit.shard)
         if self.world == 1:
             flat = src
         else:
@@ -212,7 +216,7 @@ class Zero3LlamaEngine:
             st.comm.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(st.comm):
                 if self.comm.fused:
-                    self.comm.all_gather_unit(unit, unit.index, full, self.step_count - 1)
+                    self.comm.all_gather_unit(unit, unit.index, full)
                 else:
                     self.comm.all_gather(unit.shard, full)
                 ev = st.event()
@@ -324,6 +328,7 @@ class Zero3LlamaEngine:
         c = self.cfg
         B, S = tokens.shape
         T = B * S
+        self._poll_status(force=(self.step_count % 8 == 7))
         self.step_count += 1
         L = len(self.layers)
         tok = tokens.reshape(-1)
@@ -386,7 +391,53 @@ class Zero3LlamaEngine:
             self._wait(e)
         if self.world > 1:
             loss = self.comm.all_reduce_scalar(loss.clone()) / self.world
+        self._post_status()
         return loss
+
+    # ------------------------------------------------------------------ learning-rate hook
+    def get_lr(self) -> float:
+        return self.opt.lr
+
+    def set_lr(self, lr: float) -> None:
+        """The engine can be handed to a learning-rate scheduler in place of an optimizer
+        (``CosineAnnealingLR(engine, ...)``): schedulers only need ``get_lr`` / ``set_lr``."""
+        self.opt.lr = float(lr)
+
+    # ------------------------------------------------------------------ kernel status
+    def _post_status(self):
+        """Queues a copy of the per-device kernel status word (bounded waits that ran out write a code there)
+        into pinned host memory behind this step's kernels; costs no synchronisation."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import _lib
+
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(_lib.status_word(self.device), non_blocking=True)
+        self._status_event.record()
+
+    def _poll_status(self, force: bool = False):
+        """Raises :class:`KernelStatusError` if an earlier step recorded an expired wait (a peer flag that never
+        arrived, a pipeline stage that never filled). Reads the copy posted by the previous step when it has landed;
+        ``force`` waits for it (done every eighth step, so that a step on stale data is noticed soon)."""
+        if self._status_event is None:
+            return
+        if not force and not self._status_event.query():
+            return
+        self._status_event.synchronize()
+        code = int(self._status_host[0])
+        if code != 0:
+            from ..ops import _lib
+
+            _lib.check_status(self.device)   # raises with the code's meaning and clears the word
+
+    def check_status(self):
+        """Synchronises and raises if any kernel of the steps so far recorded an error code."""
+        if self.device.type == "cuda":
+            from ..ops import _lib
+
+            _lib.check_status(self.device)
 
     # ------------------------------------------------------------------ inference-style forward (no grad state)
     @torch.no_grad()
@@ -409,17 +460,41 @@ class Zero3LlamaEngine:
         return K.gemm(hF, False, hw["lm_head"], True).view(B, S, -1)
 
     # ------------------------------------------------------------------ state
-    def state_dict(self, master: bool = True) -> dict:
-        """Full (gathered) named tensors with PyTorch-style dotted names."""
+    def state_dict(self, master: bool = True, which: str | None = None) -> dict:
+        """Full (gathered) named tensors with PyTorch-style dotted names (``which`` = "m" / "v": Adam moments)."""
         out = {}
-        out["embed_tokens.weight"] = self.gather_unit(self.embed, master)["tok_emb"]
+        out["embed_tokens.weight"] = self.gather_unit(self.embed, master, which)["tok_emb"]
         for i, u in enumerate(self.layers):
-            for k, v in self.gather_unit(u, master).items():
+            for k, v in self.gather_unit(u, master, which).items():
                 out[f"layers.{i}.{k}"] = v
-        h = self.gather_unit(self.head, master)
+        h = self.gather_unit(self.head, master, which)
         out["norm.weight"] = h["final_norm"]
         out["lm_head.weight"] = h["lm_head"]
         return out
+
+    def _unit_named(self, unit: _Unit, full: dict) -> dict:
+        if unit is self.embed:
+            return {"tok_emb": full["embed_tokens.weight"]}
+        if unit is self.head:
+            return {"final_norm": full["norm.weight"], "lm_head": full["lm_head.weight"]}
+        i = self.layers.index(unit)
+        return {p: full[f"layers.{i}.{p}"] for p, _, _ in unit.specs}
+
+    def load_full_state(self, params: dict, exp_avg: dict | None = None, exp_avg_sq: dict | None = None,
+                        step: int = 0) -> None:
+        """Restores the engine from full named fp32 tensors (as :meth:`state_dict` returns them): every rank
+        keeps its own slice of weights and, when given, of the Adam moments. Collective when ``world > 1``."""
+        st = {"step": step}
+        for u in self.units:
+            for key, full in (("master", params), ("exp_avg", exp_avg), ("exp_avg_sq", exp_avg_sq)):
+                if full is None:
+                    st[f"{u.name}.{key}"] = torch.zeros(u.shard_numel, dtype=torch.float32, device=self.device)
+                    continue
+                flat = torch.zeros(u.padded, dtype=torch.float32)
+                for pname, off, shape in u.specs:
+                    flat[off:off + math.prod(shape)] = self._unit_named(u, full)[pname].to(torch.float32).reshape(-1)
+                st[f"{u.name}.{key}"] = flat[u.lo:u.lo + u.shard_numel].to(self.device)
+        self.load_shard_state(st)
 
     def shard_state(self) -> dict:
         """This rank's shards (weights, master, moments) for sharded checkpoints."""
@@ -431,12 +506,25 @@ class Zero3LlamaEngine:
         return st
 
     def load_shard_state(self, st: dict) -> None:
+        """Restores this rank's shards (fp32 master, moments) and the step count; the low-precision shard is
+        recomputed from the master copy. Collective when ``world > 1``: no rank returns before every rank has
+        its new weights in place, because the next step's gathers read the peers' shards directly."""
         self.step_count = int(st["step"])
         for u in self.units:
             u.master.copy_(st[f"{u.name}.master"])
             u.m.copy_(st[f"{u.name}.exp_avg"])
             u.v.copy_(st[f"{u.name}.exp_avg_sq"])
             u.shard.copy_(u.master.to(self.dtype))
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.comm.group)
+
+    def flat_layout(self) -> dict:
+        """Per unit: logical length, padded length, shard length and this rank's offset in the flat unit
+        (what a sharded checkpoint needs to be cut again for another world size)."""
+        return {u.name: {"numel": u.numel, "padded": u.padded, "shard_numel": u.shard_numel, "lo": u.lo}
+                for u in self.units}
 
     def memory_summary(self) -> dict:
         per_rank = sum(u.shard_numel for u in self.units)
