@@ -23,12 +23,32 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     cfg = LLaMAConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512)
-    comm = make_comm(kind, dev)
-    eng = Zero3LlamaEngine(cfg, dev, optim=OptimConfig(lr=2e-3), comm=comm, seed=5)
+    base = kind.split("_")[0]
+    persist = None if "nopersist" not in kind else False
+    comm = make_comm(base, dev)
+    eng = Zero3LlamaEngine(cfg, dev, optim=OptimConfig(lr=2e-3), comm=comm, seed=5, persist_gathered=persist)
     g = torch.Generator().manual_seed(99)
     tok = torch.randint(0, cfg.vocab_size, (world, 257), generator=g)
     mine = tok[rank:rank + 1].to(dev)
-    losses = [float(eng.step(mine[:, :-1], mine[:, 1:])) for _ in range(steps)]
+    if "resume" in kind:
+        # half of the steps, a sharded checkpoint, then a NEW communicator and engine in the same job (fresh signal
+        # pads and counters, as in a restarted process) that loads it and continues: the step counter starts
+        # at steps / 2 while every flag of the new pads is zero
+        from ghost_flow_b200 import io as gio
+
+        ckdir = out + ".ck"
+        losses = [float(eng.step(mine[:, :-1], mine[:, 1:])) for _ in range(steps // 2)]
+        gio.save_sharded(eng, ckdir)
+        torch.cuda.synchronize()
+        dist.barrier()
+        del eng
+        comm = make_comm(base, dev)
+        eng = Zero3LlamaEngine(cfg, dev, optim=OptimConfig(lr=2e-3), comm=comm, seed=1234, persist_gathered=persist)
+        gio.load_sharded(eng, ckdir)
+        assert eng.step_count == steps // 2
+        losses += [float(eng.step(mine[:, :-1], mine[:, 1:])) for _ in range(steps - steps // 2)]
+    else:
+        losses = [float(eng.step(mine[:, :-1], mine[:, 1:])) for _ in range(steps)]
     torch.cuda.synchronize()
     _lib.check_status(dev)
     w = eng.gather_unit(eng.layers[2], master=True)["w_gate_up"].cpu()

@@ -26,25 +26,40 @@ def _run(kind, out, n, steps=4, port=29741):
     return torch.load(out)
 
 
-def test_fused_collectives_match_nccl_and_single_gpu(tmp_path):
-    _need(2)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_collectives_match_nccl_and_single_gpu(tmp_path, world):
+    """Every world size exercises other code: two batches of four peer loads in the fused reducer only at 8 ranks,
+    the second batch half full at more than 4."""
+    _need(world)
     from ghost_flow_b200.models.configs import LLaMAConfig
     from ghost_flow_b200.parallel.zero3 import OptimConfig, Zero3LlamaEngine
 
-    fused = _run("fused", str(tmp_path / "f.pt"), 2, port=29741)
-    nccl = _run("nccl", str(tmp_path / "n.pt"), 2, port=29743)
+    fused = _run("fused", str(tmp_path / "f.pt"), world, port=29741)
+    nccl = _run("nccl", str(tmp_path / "n.pt"), world, port=29743)
     assert fused["fused"], "the peer-memory path was not taken"
     cfg = LLaMAConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512)
     eng = Zero3LlamaEngine(cfg, "cuda", optim=OptimConfig(lr=2e-3), seed=5)
     g = torch.Generator().manual_seed(99)
-    tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=g).cuda()
+    tok = torch.randint(0, cfg.vocab_size, (world, 257), generator=g).cuda()
     single = [float(eng.step(tok[:, :-1], tok[:, 1:])) for _ in range(4)]
     for a, b, c in zip(fused["losses"], nccl["losses"], single):
         assert abs(a - b) < 2e-2 and abs(a - c) < 3e-2, (fused["losses"], nccl["losses"], single)
     w1 = eng.gather_unit(eng.layers[2], master=True)["w_gate_up"].cpu()
     assert (fused["w"] - nccl["w"]).norm() / nccl["w"].norm() < 1e-2
     assert (fused["w"] - w1).norm() / w1.norm() < 1e-2
+
+
+def test_fused_path_resumes_from_a_sharded_checkpoint(tmp_path):
+    """Save after two steps, load into a new engine with a new communicator (zeroed flags, step counter = 2) and
+    continue: the loss curve must be the uninterrupted one. Also with the rotating (non-persistent) weight buffers."""
+    _need(2)
+    plain = _run("fused", str(tmp_path / "f.pt"), 2, port=29745)
+    resumed = _run("fused_resume", str(tmp_path / "r.pt"), 2, port=29747)
+    rotating = _run("fused_resume_nopersist", str(tmp_path / "q.pt"), 2, port=29749)
+    for a, b, c in zip(plain["losses"], resumed["losses"], rotating["losses"]):
+        assert abs(a - b) < 2e-3 and abs(a - c) < 2e-3, (plain["losses"], resumed["losses"], rotating["losses"])
+    assert (plain["w"] - resumed["w"]).norm() / plain["w"].norm() < 1e-3
 
 
 def test_fused_tensor_parallel_kernels_match_nccl(tmp_path):

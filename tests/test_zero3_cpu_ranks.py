@@ -18,7 +18,9 @@ WORKER = textwrap.dedent("""
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     cfg = LLaMAConfig.llama_tiny()
-    eng = Zero3LlamaEngine(cfg, "cpu", optim=OptimConfig(lr=1e-2), dtype=torch.float32, seed=7, comm=Comm())
+    eng = Zero3LlamaEngine(cfg, "cpu", optim=OptimConfig(lr=1e-2), dtype=torch.float32, seed=7, comm=Comm(),
+                           persist_gathered={persist})
+    assert eng.persist == {persist}
     g = torch.Generator().manual_seed(11)
     tok = torch.randint(0, cfg.vocab_size, (world, 33), generator=g)
     mine = tok[rank:rank + 1]
@@ -31,16 +33,22 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_two_cpu_ranks_match_single_rank(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("persist", [True, False])
+def test_two_cpu_ranks_match_single_rank(tmp_path, persist):
+    """Both weight-buffer policies: gathered copies kept from the forward to the backward pass, or two rotating
+    buffers with a second gather in the backward pass."""
     from ghost_flow_b200.models.configs import LLaMAConfig
     from ghost_flow_b200.parallel.zero3 import OptimConfig, Zero3LlamaEngine
 
     out = str(tmp_path / "r0.pt")
     script = tmp_path / "worker.py"
-    script.write_text(WORKER.format(repo=REPO, out=out))
+    script.write_text(WORKER.format(repo=REPO, out=out, persist=persist))
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29731", str(script)],
+                        "--master-addr", "127.0.0.1", "--master-port", str(29731 + int(persist)), str(script)],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     got = torch.load(out)
