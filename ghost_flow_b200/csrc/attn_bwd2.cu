@@ -279,8 +279,8 @@ fa_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         } else if (++idle > GF_WAIT_LIMIT) {
           if (p.status && leader) atomicCAS(p.status, 0, GF_ERR_WAIT_SOFTMAX);
           ok = false;
-        } else if (idle > GF_SPIN_FAST_POLLS) {
-          __nanosleep(64);
+        } else if (idle > 64) {
+          __nanosleep(32);
         }
       }
       if (ok) umma_commit_u(leader, acc_full);

@@ -32,6 +32,7 @@ NVCC_FLAGS = [
 CUDA_SOURCES = [
     "gf_host.cu",
     "gemm_bf16.cu",
+    "gemm2sm_bf16.cu",
     "norm.cu",
     "pointwise.cu",
     "xent_adamw.cu",

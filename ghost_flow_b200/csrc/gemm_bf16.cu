@@ -915,6 +915,14 @@ static float* splitk_workspace(size_t floats) {
 }
 }  // namespace gf
 
+namespace gf {
+// CTA-pair kernel for plain GEMMs (gemm2sm_bf16.cu)
+int gemm2sm_wanted(int M, int N, int K);
+int gemm2sm_run(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
+                int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate, const void* bias,
+                const void* residual, long long ldr, float alpha, int* status, int activation, cudaStream_t stream);
+}  // namespace gf
+
 static void no_gather(gf::GemmParams& p) {
   p.g_operand = -1; p.g_copy_ctas = 0; p.g_world = 1; p.g_rank = 0; p.g_first_shard = 0;
   for (int i = 0; i < 8; ++i) p.g_src[i] = nullptr;
@@ -971,6 +979,10 @@ GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
       }
     }
   }
+  // large plain products run on CTA pairs (256 x 256 tiles, half the operand bytes per SM and flop)
+  if (bn_hint == 0 && max_ctas == 0 && gf::gemm2sm_wanted(M, N, K))
+    return gf::gemm2sm_run(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias,
+                           residual, ldr, alpha, status, activation, st);
   return gemm_core(A, B, C, M, N, K, a_mn_major, lda, b_mn_major, ldb, ldc, out_fp32, accumulate, bias, residual, ldr,
                    alpha, status, bn_hint, max_ctas, p, st);
 }

@@ -66,7 +66,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false when the limit ran out.
 // Non-blocking probe of a phase (try_wait may suspend the thread for a hardware time slice before it reports
 // "not yet"; a thread that serves several barriers in turn must not sit in one of them).
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -80,16 +79,12 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// try_wait already suspends the thread for a hardware-chosen slice, so the loop polls back to back; the
-// sleep only starts once a wait has clearly become a long one (a sleeping thread notices the completed phase
-// late, which puts the sleep granularity on every hand-off of a pipeline).
-#ifndef GF_SPIN_FAST_POLLS
-#define GF_SPIN_FAST_POLLS 20000u
-#endif
+// Bounded wait. Returns false when the limit ran out. After a short burst of back-to-back polls the thread
+// sleeps between polls: spinning warps take issue slots and power from the warps that do the work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = GF_WAIT_LIMIT) {
   for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > GF_SPIN_FAST_POLLS) __nanosleep(64);
+    if (it > 64) __nanosleep(32);
   }
   return false;
 }
