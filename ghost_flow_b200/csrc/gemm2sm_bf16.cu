@@ -36,21 +36,27 @@ struct Gemm2Params {
   long long ldr;
   float alpha;
   int* status;
-  int tiles_m, tiles_n;     // 256 x 256 tiles
+  int tiles_m, tiles_n;     // 256 x BN tiles
   int band;                 // rows of tiles walked together (keeps one wave's A and B panels in L2)
   int act;                  // 0 none, 1 ReLU
 };
 
 constexpr int G2_BM = 128;        // rows of A per CTA
-constexpr int G2_BNH = 128;       // rows of B (output columns) per CTA
-constexpr int G2_BN = 256;        // output columns of the pair's tile
 constexpr int G2_BK = 64;
 constexpr int G2_THREADS = 192;   // TMA warp, MMA warp, 4 epilogue warps
-constexpr int G2_STAGES = 7;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;
-constexpr int G2_B_BYTES = G2_BNH * G2_BK * 2;
-constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+
+// BNH = rows of B (output columns) per CTA: 128 (256 x 256 tiles, seven stages) or 64 (256 x 128 tiles, nine
+// stages; twice as many tiles, for problems whose last wave of 256-wide tiles would leave most pairs idle).
+template <int BNH>
+struct G2Cfg {
+  static constexpr int BN = 2 * BNH;
+  static constexpr int B_BYTES = BNH * G2_BK * 2;
+  static constexpr int STAGE_BYTES = G2_A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BNH == 128) ? 7 : 9;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -120,10 +126,15 @@ __device__ __forceinline__ void g2_tile_coords(const Gemm2Params& p, int tile, i
   tn = r / rows;
 }
 
-template <bool A_MN, bool B_MN>
+template <int BNH, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2sm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const Gemm2Params p) {
+  using Cfg = G2Cfg<BNH>;
+  constexpr int G2_BNH = BNH;
+  constexpr int G2_BN = Cfg::BN;
+  constexpr int G2_STAGES = Cfg::STAGES;
+  constexpr int G2_STAGE_BYTES = Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + G2_STAGES * G2_STAGE_BYTES);
@@ -154,7 +165,7 @@ gemm2sm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc_2sm(tmem_slot, 512);
+    tmem_alloc_2sm(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish_2sm();
   }
   tc_fence_before();
@@ -373,15 +384,18 @@ gemm2sm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc_2sm(tmem_base, 512);
+    tmem_dealloc_2sm(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <int BNH, bool A_MN, bool B_MN>
 static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm2Params& p, cudaStream_t stream) {
+  using Cfg = G2Cfg<BNH>;
+  constexpr int G2_SMEM_BYTES = Cfg::SMEM_BYTES;
+  constexpr int G2_BN = Cfg::BN;
   static bool configured = false;
   static int max_pairs = 0;
-  auto kern = gemm2sm_bf16_kernel<A_MN, B_MN>;
+  auto kern = gemm2sm_bf16_kernel<BNH, A_MN, B_MN>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess)
       return GFH_CUDA;
@@ -427,16 +441,31 @@ int gemm2sm_wanted(int M, int N, int K) {
   return tiles >= (sm_count() / 2) && K >= 256;
 }
 
+// Width of the pair's tile for this problem. 256 x 128 tiles measure 1.28x slower per flop than 256 x 256 ones
+// (8192^3: 0.898 vs 0.699 ms), more than a fuller last wave can win back on the shapes tried (4096^3: 0.116 vs
+// 0.095 ms), so they are only used for narrow outputs. GF_GEMM_2SM_BN=128|256 forces one.
+static int g2_pick_bn(int M, int N) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("GF_GEMM_2SM_BN");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 128 || forced == 256) return forced;
+  (void)M;
+  return N <= 128 ? 128 : 256;
+}
+
 int gemm2sm_run(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
                 int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate, const void* bias,
                 const void* residual, long long ldr, float alpha, int* status, int activation, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return GFH_BAD_ARG;
+  const int bn = g2_pick_bn(M, N);
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn_major) rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, G2_BM, G2_BK);
   else rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda * 2, G2_BK, 64);
   if (rc) return rc;
-  if (!b_mn_major) rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, G2_BNH, G2_BK);
+  if (!b_mn_major) rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, bn / 2, G2_BK);
   else rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb * 2, G2_BK, 64);
   if (rc) return rc;
   Gemm2Params p;
@@ -444,10 +473,14 @@ int gemm2sm_run(const void* A, const void* B, void* C, int M, int N, int K, int 
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr; p.alpha = alpha; p.status = status; p.act = activation == 1 ? 1 : 0;
-  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(tmA, tmB, p, stream);
-  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(tmA, tmB, p, stream);
-  if (a_mn_major && !b_mn_major) return launch_gemm2<true, false>(tmA, tmB, p, stream);
-  return launch_gemm2<true, true>(tmA, tmB, p, stream);
+#define GF_G2_DISPATCH(BNH_)                                                                        \
+  if (!a_mn_major && !b_mn_major) return launch_gemm2<BNH_, false, false>(tmA, tmB, p, stream);     \
+  if (!a_mn_major && b_mn_major) return launch_gemm2<BNH_, false, true>(tmA, tmB, p, stream);       \
+  if (a_mn_major && !b_mn_major) return launch_gemm2<BNH_, true, false>(tmA, tmB, p, stream);       \
+  return launch_gemm2<BNH_, true, true>(tmA, tmB, p, stream);
+  if (bn == 256) { GF_G2_DISPATCH(128) }
+  GF_G2_DISPATCH(64)
+#undef GF_G2_DISPATCH
 }
 
 }  // namespace gf
