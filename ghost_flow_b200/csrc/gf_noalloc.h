@@ -13,6 +13,9 @@
 // Limits and rules
 //  * D (row length) must be a multiple of 8 and at most GF_NOALLOC_MAX_D; T (rows) is unlimited.
 //    Larger D is rejected with GFH_TOO_LARGE and a message on stderr; nothing is launched.
+//  * x, w, dy, dres and dx must be 16-byte aligned (rows move as 16-byte vectors), rstd 4-byte, dw 2-byte aligned.
+//    A call with a null, misaligned or otherwise invalid argument returns GFH_BAD_ARG before it touches the device:
+//    nothing is launched and the calling thread's current device is left alone.
 //  * The scratch array takes GF_NOALLOC_MAX_PARTS * GF_NOALLOC_MAX_D * 4 bytes (about 4.6 MiB) on every
 //    GPU that loads the library, from load until the process exits.
 //  * The first call on each device looks up the device address of that array (one runtime query, no

@@ -154,9 +154,15 @@ extern "C" int gf_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* 
   using namespace gf;
   // Bind this thread to the process's device in this library's runtime (no allocation involved). A plain
   // C caller that never selected a device simply uses the runtime's current device.
-  const int want = process_device();
-  if (want >= 0 && cudaSetDevice(want) != cudaSuccess) return GFH_CUDA;
+  // Arguments first: a call that is refused must not touch the device state of the calling thread.
   if (T <= 0 || D <= 0 || (D % 8) != 0 || !x || !w || !dy || !rstd || !dx || !dw) return GFH_BAD_ARG;
+  // The kernels move rows as 16-byte vectors; a pointer into the middle of a buffer that is not 16-byte aligned
+  // would fault on the device instead of failing here. rstd is read as fp32, dw written as bf16.
+  const uintptr_t vec = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+                        reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dres) |
+                        reinterpret_cast<uintptr_t>(dx);
+  if ((vec & 15) || (reinterpret_cast<uintptr_t>(rstd) & 3) || (reinterpret_cast<uintptr_t>(dw) & 1))
+    return GFH_BAD_ARG;
   if (D > GF_NOALLOC_MAX_D) {
     fprintf(stderr,
             "[ghost_flow_b200] gf_rmsnorm_bwd_noalloc: D = %d exceeds the built-in scratch (max D = %d); "
@@ -164,6 +170,8 @@ extern "C" int gf_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* 
             D, GF_NOALLOC_MAX_D);
     return GFH_TOO_LARGE;
   }
+  const int want = process_device();
+  if (want >= 0 && cudaSetDevice(want) != cudaSuccess) return GFH_CUDA;
   int err = GFH_OK;
   float* scratch = scratch_address(&err);
   if (!scratch) return err;

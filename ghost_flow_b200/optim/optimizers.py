@@ -86,27 +86,60 @@ class Optimizer:
         master = torch.zeros(n, dtype=torch.float32, device=dev)
         for p, o in zip(ps, offs):
             master[o:o + p.numel()] = p.detach().reshape(-1).float()
+            if p.dtype == torch.float32 and p.is_contiguous():
+                # fp32 parameters need no second copy: they become views of the flat buffer, so whatever else writes
+                # them (load_state_dict, clamping, an EMA swap) writes the optimizer's copy too
+                p.data = master[o:o + p.numel()].view(p.shape)
         f = {"params": ps, "offs": offs, "n": n, "master": master,
              "state": [torch.zeros(n, dtype=torch.float32, device=dev) for _ in range(n_state)],
-             "grad": torch.zeros(n, dtype=torch.float32, device=dev)}
+             "grad": torch.zeros(n, dtype=torch.float32, device=dev),
+             "is_view": [p.dtype == torch.float32 and p.data_ptr() == master[o:o + 1].data_ptr()
+                         for p, o in zip(ps, offs)],
+             "versions": [p._version for p in ps]}
         self._flat[gi] = f
         return f
 
     @staticmethod
+    def _sync_master(f):
+        """Low-precision parameters keep an fp32 master copy in the flat buffer. If such a parameter was written
+        from outside since the last step (``load_state_dict``, ``p.copy_``, ``p.clamp_`` under ``no_grad``: anything
+        that bumps its version counter), the master copy is refreshed from it; otherwise the next step would put
+        the old value back. Writes through ``p.data`` leave no trace and are not seen."""
+        for i, (p, o) in enumerate(zip(f["params"], f["offs"])):
+            if f["is_view"][i]:
+                continue
+            if p._version != f["versions"][i]:
+                f["master"][o:o + p.numel()] = p.detach().reshape(-1).float()
+                f["versions"][i] = p._version
+
+    @staticmethod
     def _gather_grads(f):
+        """Copies the gradients into the flat buffer and returns it with the element ranges ``[(lo, hi), ...]``
+        that have one. A parameter without a gradient in this step is left out of the update altogether (no
+        weight decay, no decay of its moments), like the per-tensor path and the reference's loop do."""
         g = f["grad"]
+        runs, lo, hi = [], None, None
         for p, o in zip(f["params"], f["offs"]):
             if p.grad is None:
-                g[o:o + p.numel()].zero_()
-            else:
-                g[o:o + p.numel()].copy_(p.grad.reshape(-1))
-        return g
+                if lo is not None:
+                    runs.append((lo, hi))
+                    lo = None
+                continue
+            g[o:o + p.numel()].copy_(p.grad.reshape(-1))
+            end = o + (p.numel() + 3) // 4 * 4
+            if lo is None:
+                lo = o
+            hi = end
+        if lo is not None:
+            runs.append((lo, hi))
+        return g, runs
 
     @staticmethod
     def _scatter_params(f):
         m = f["master"]
-        for p, o in zip(f["params"], f["offs"]):
-            p.data.copy_(m[o:o + p.numel()].view_as(p))
+        for i, (p, o) in enumerate(zip(f["params"], f["offs"])):
+            if not f["is_view"][i]:
+                p.data.copy_(m[o:o + p.numel()].view_as(p))
 
     def state_dict(self):
         return {"step": self.step_count, "param_groups": [{k: v for k, v in g.items() if k != "params"}
@@ -155,11 +188,13 @@ class SGD(Optimizer):
             if f is not None:
                 from ..ops.optim_kernels import sgd_flat
 
-                grads = self._gather_grads(f)
+                self._sync_master(f)
+                grads, runs = self._gather_grads(f)
                 with torch.cuda.device(f["master"].device):
-                    sgd_flat(f["master"], f["state"][0], grads, None, lr=g["lr"], momentum=g["momentum"],
-                             dampening=g["dampening"], weight_decay=g["weight_decay"], nesterov=g["nesterov"],
-                             first_step=(self.step_count == 1))
+                    for lo, hi in runs:
+                        sgd_flat(f["master"][lo:hi], f["state"][0][lo:hi], grads[lo:hi], None, lr=g["lr"],
+                                 momentum=g["momentum"], dampening=g["dampening"], weight_decay=g["weight_decay"],
+                                 nesterov=g["nesterov"], first_step=(self.step_count == 1))
                 self._scatter_params(f)
             for p in g["params"]:
                 if p.is_cuda or p.grad is None:
@@ -210,10 +245,13 @@ class Adam(Optimizer):
             if f is not None:
                 from ..ops.optim_kernels import adam_flat
 
-                grads = self._gather_grads(f)
+                self._sync_master(f)
+                grads, runs = self._gather_grads(f)
                 with torch.cuda.device(f["master"].device):
-                    adam_flat(f["master"], f["state"][0], f["state"][1], grads, None, lr=g["lr"], beta1=b1, beta2=b2,
-                              eps=g["eps"], weight_decay=g["weight_decay"], step=t, decoupled=self.decoupled)
+                    for lo, hi in runs:
+                        adam_flat(f["master"][lo:hi], f["state"][0][lo:hi], f["state"][1][lo:hi], grads[lo:hi], None,
+                                  lr=g["lr"], beta1=b1, beta2=b2, eps=g["eps"], weight_decay=g["weight_decay"], step=t,
+                                  decoupled=self.decoupled)
                 self._scatter_params(f)
             for p in g["params"]:
                 if p.is_cuda or p.grad is None:

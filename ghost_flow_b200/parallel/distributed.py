@@ -186,6 +186,7 @@ class DistributedDataParallel(torch.nn.Module):
             self.buckets.append(flat)
             self._pending.append(len(ps))
         self._sizes = list(self._pending)
+        self._next = 0
         if self.world > 1:
             DataParallel(module, group=group).broadcast_parameters(0)
 
@@ -193,7 +194,15 @@ class DistributedDataParallel(torch.nn.Module):
         bi = self._bucket_of[id(p)]
         self._pending[bi] -= 1
         if self._pending[bi] == 0 and self._sync and self.world > 1:
-            self._works.append(dist.all_reduce(self.buckets[bi], group=self.group, async_op=True))
+            self._launch_ready()
+
+    def _launch_ready(self, everything: bool = False):
+        """Collectives must be issued in the same order on every rank, and the order in which hooks fire is not
+        the same everywhere (a parameter may get no gradient on one rank only). Buckets are therefore launched
+        strictly by index: a complete bucket waits until all buckets before it have been launched."""
+        while self._next < len(self.buckets) and (everything or self._pending[self._next] <= 0):
+            self._works.append(dist.all_reduce(self.buckets[self._next], group=self.group, async_op=True))
+            self._next += 1
 
     @contextlib.contextmanager
     def no_sync(self):
@@ -204,18 +213,31 @@ class DistributedDataParallel(torch.nn.Module):
         finally:
             self._sync = old
 
-    def forward(self, *a, **k):
+    def _reset_counts(self):
         self._pending = list(self._sizes)
+        self._next = 0      # first bucket whose all-reduce has not been launched in this backward
+
+    def forward(self, *a, **k):
+        self._reset_counts()
         return self.module(*a, **k)
 
     def finish(self):
-        """Wait for the bucket all-reduces of the last backward and turn sums into means."""
+        """Wait for the bucket all-reduces of the last backward and turn sums into means. A bucket whose
+        all-reduce no hook launched is reduced here: that happens when one of its parameters (or of a bucket before
+        it) got no gradient in this backward (unused in the forward pass, a branch not taken), because the hook of
+        such a parameter never fires; its slice of the bucket holds zeros (or the accumulated value) and takes part
+        like any other.
+        Without this the ranks would keep their local gradients, scaled by 1 / world, and drift apart."""
+        if self.world > 1 and self._sync:
+            self._launch_ready(everything=True)
         for w in self._works:
             w.wait()
         self._works = []
-        if self.world > 1:
+        if self.world > 1 and self._sync:
             for b in self.buckets:
                 b.div_(self.world)
+        # a second backward without a forward in between (two losses) starts from fresh counts as well
+        self._reset_counts()
 
     def zero_grad(self):
         for b in self.buckets:
@@ -225,6 +247,7 @@ class DistributedDataParallel(torch.nn.Module):
         """The reference's entry point: backward, all-reduce, accumulate; True when an optimizer step is due."""
         self._micro += 1
         last = self._micro % self.accumulation_steps == 0
+        self._reset_counts()
         if last:
             (loss / self.accumulation_steps).backward()
             self.finish()

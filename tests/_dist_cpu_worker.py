@@ -37,7 +37,36 @@ def case_ddp(rank, world, out):
     halves_x, halves_y = xs[rank].chunk(2), ys[rank].chunk(2)
     due = [m2.backward(torch.nn.functional.mse_loss(m2(a), b)) for a, b in zip(halves_x, halves_y)]
     err2 = max((p.grad - q.grad).abs().max().item() for p, q in zip(m2.module.parameters(), ref.parameters()))
-    return {"ddp_grad_err": err, "ddp_accum_err": err2, "due": due}
+    # a parameter that takes no part in the forward pass on ANY rank, and one used only on rank 0: their hooks
+    # never fire (everywhere / on rank 1), yet after finish() every rank must hold the same averaged gradients
+    class Branchy(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(3)
+            self.a = torch.nn.Linear(12, 4)
+            self.unused = torch.nn.Linear(12, 4)
+            self.sometimes = torch.nn.Linear(12, 4)
+
+        def forward(self, x, use_branch):
+            y = self.a(x)
+            return y + self.sometimes(x) if use_branch else y
+
+    ref3 = Branchy()
+    l_ref = sum(torch.nn.functional.mse_loss(ref3(xs[r], r == 0), ys[r]) for r in range(world)) / world
+    l_ref.backward()
+    m3 = DistributedDataParallel(Branchy(), bucket_mb=0.0001)
+    torch.nn.functional.mse_loss(m3(xs[rank], rank == 0), ys[rank]).backward()
+    m3.finish()
+    err3 = 0.0
+    for (n, p_), (_, q) in zip(m3.module.named_parameters(), ref3.named_parameters()):
+        want = q.grad if q.grad is not None else torch.zeros_like(q)
+        err3 = max(err3, (p_.grad - want).abs().max().item())
+    # two backward passes after one forward each, without an intervening reset by hand
+    m3.zero_grad()
+    for _ in range(2):
+        torch.nn.functional.mse_loss(m3(xs[rank], rank == 0), ys[rank]).backward()
+        m3.finish()
+    return {"ddp_grad_err": err, "ddp_accum_err": err2, "due": due, "ddp_unused_err": err3}
 
 
 def case_zero(rank, world, out):

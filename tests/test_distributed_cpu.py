@@ -28,6 +28,8 @@ def test_ddp_bucketed_allreduce_matches_full_batch(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     for d in res:
         assert d["ddp_grad_err"] < 1e-6 and d["ddp_accum_err"] < 1e-6 and d["due"] == [False, True]
+        # buckets that hold a parameter without a gradient (unused everywhere, or on one rank only) are still reduced
+        assert d["ddp_unused_err"] < 1e-6, d
 
 
 def test_zero_stages_match_adamw(tmp_path):

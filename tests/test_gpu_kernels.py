@@ -389,3 +389,47 @@ def test_fp32_matmul_on_tensor_cores_is_close_to_fp32(kernel_status):
         assert err < 3e-5 and err < bf16_err / 20, (M, K, N, float(err), float(bf16_err))
         yt = gf.Tensor(a).matmul(gf.Tensor(b.t().contiguous()).t()).data  # strided right operand
         assert torch.allclose(yt, y, atol=1e-4 * float(scale))
+
+
+# ----------------------------------------------------------------------------------------- flat optimizers
+@pytest.mark.parametrize("opt_name", ["AdamW", "SGD"])
+def test_flat_optimizer_matches_cpu_path_with_missing_grads_and_external_writes(opt_name, kernel_status):
+    """The CUDA path (flat fp32 buffers, one fused kernel per run of parameters) against the per-tensor CPU path:
+    a parameter without a gradient is left alone (no weight decay, no moment decay), and parameters written from
+    outside between steps (load_state_dict-style copy_) keep the new value instead of being reset from a stale
+    master copy, for fp32 parameters (views of the flat buffer) and bf16 ones (version check)."""
+    from ghost_flow_b200 import optim
+
+    def make(device, dtype):
+        g = torch.Generator().manual_seed(0)
+        return [torch.nn.Parameter(torch.randn(33, 7, generator=g).to(device=device, dtype=dtype)),
+                torch.nn.Parameter(torch.randn(50, generator=g).to(device=device, dtype=dtype)),
+                torch.nn.Parameter(torch.randn(16, 16, generator=g).to(device=device, dtype=dtype))]
+
+    def make_opt(ps):
+        if opt_name == "AdamW":
+            return optim.AdamW(ps, lr=1e-2, weight_decay=0.1)
+        return optim.SGD(ps, lr=1e-2, momentum=0.9, weight_decay=0.1)
+
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        pc, pg = make("cpu", torch.float32), make(DEV, dtype)
+        oc, og = make_opt(pc), make_opt(pg)
+        gen = torch.Generator().manual_seed(1)
+        for step in range(4):
+            for i, (a, b) in enumerate(zip(pc, pg)):
+                if i == 1 and step != 2:
+                    a.grad, b.grad = None, None          # no gradient in most steps
+                    continue
+                gr = torch.randn(a.shape, generator=gen)
+                a.grad, b.grad = gr.clone(), gr.to(device=DEV, dtype=dtype)
+            oc.step()
+            og.step()
+            if step == 1:                                # an external write after the first steps
+                new = torch.full_like(pc[2], 0.25)
+                with torch.no_grad():
+                    pc[2].copy_(new)
+                    pg[2].copy_(new.to(device=DEV, dtype=dtype))
+        torch.cuda.synchronize()
+        for a, b in zip(pc, pg):
+            assert torch.allclose(a, b.float().cpu(), rtol=tol, atol=tol), (opt_name, dtype)
+        # the untouched steps of the grad-less parameter left it exactly where it was after its one update
