@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--comm", default=None, choices=[None, "nccl", "fused"],
                     help="collective path at N > 1 (default: fused when available)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="skip the fused-versus-NCCL parity step that follows the timed regions at N > 1")
     return ap.parse_args()
 
 
@@ -221,6 +223,32 @@ def main():
         ms_dry = g0.elapsed_time(g1) / args.steps
         eng.comm.dry_run = False
 
+    # ---- correctness evidence at this world size, outside every timed region: a second engine on the NCCL
+    # communicator takes over the trained state (weights, moments, step), both engines run ONE step on the same
+    # batch, and the losses and one gathered master weight are compared.
+    parity = None
+    if world > 1 and getattr(eng.comm, "fused", False) and not args.no_parity:
+        try:
+            eng_b = Zero3LlamaEngine(cfg, device, optim=OptimConfig(lr=3e-4, weight_decay=0.01),
+                                     comm=make_comm("nccl", device), seed=1, persist_gathered=False)
+            eng_b.load_shard_state(eng.shard_state())
+            tb = dev_tok[0]
+            loss_a = float(eng.step(tb[:, :-1], tb[:, 1:]))
+            loss_b = float(eng_b.step(tb[:, :-1], tb[:, 1:]))
+            wa = eng.gather_unit(eng.layers[0], master=True)["wqkv"]
+            wb = eng_b.gather_unit(eng_b.layers[0], master=True)["wqkv"]
+            rel = float((wa - wb).norm() / wb.norm())
+            upd = float((wa - wb).abs().max())
+            sync_all()
+            _lib.check_status(device)
+            parity = {"what": "one step from the same state: fused (peer-memory kernels) vs NCCL collectives",
+                      "ranks": world, "loss_fused": loss_a, "loss_nccl": loss_b,
+                      "abs_loss_diff": abs(loss_a - loss_b), "wqkv_layer0_rel_diff": rel,
+                      "wqkv_layer0_max_abs_diff": upd}
+            del eng_b, wa, wb
+        except Exception as e:   # the timing above stands on its own; report why the comparison is missing
+            parity = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     t = torch.tensor([ms, ms_e2e, ms_dry], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -253,6 +281,8 @@ def main():
             "exposed_comm_ms": max(0.0, ms - ms_dry) if world > 1 else 0.0,
             "compute_only_ms_per_step": ms_dry,
         }
+        if parity is not None:
+            out["parity"] = parity
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
