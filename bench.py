@@ -228,6 +228,15 @@ def main():
     # batch, and the losses and one gathered master weight are compared.
     parity = None
     if world > 1 and getattr(eng.comm, "fused", False) and not args.no_parity:
+        # every rank must take the same decision (the second engine's collectives need all of them): the smallest
+        # free memory of the job against what the second engine holds plus a margin for its gather buffers
+        torch.cuda.empty_cache()
+        free = torch.tensor([torch.cuda.mem_get_info(device)[0]], device=device, dtype=torch.float64)
+        dist.all_reduce(free, op=dist.ReduceOp.MIN)
+        need = sum(u.shard_numel for u in eng.units) * 14 + 24 * (1 << 30)
+        if float(free[0]) < need:
+            parity = {"skipped": f"needs {need >> 30} GiB free on every rank, smallest is {int(free[0]) >> 30} GiB"}
+    if parity is None and world > 1 and getattr(eng.comm, "fused", False) and not args.no_parity:
         try:
             eng_b = Zero3LlamaEngine(cfg, device, optim=OptimConfig(lr=3e-4, weight_decay=0.01),
                                      comm=make_comm("nccl", device), seed=1, persist_gathered=False)
