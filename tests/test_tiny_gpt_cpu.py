@@ -60,3 +60,21 @@ def test_tiny_gpt_20_adamw_steps_match_oracle():
     assert ours[-1] < ours[0]
     for a, b in zip(ours, ref):
         assert abs(a - b) < 2e-4, (ours, ref)
+
+
+def test_timed_cpu_baseline_script_agrees_on_the_first_loss():
+    """benchmarks/tiny_gpt_cpu_bench.py times this package's CPU training step against the C++ restatement of the
+    reference's forward / loss / AdamW loops; both arms must start from the same loss."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "benchmarks", "tiny_gpt_cpu_bench.py"), "--steps", "3"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    assert d["first_loss_agreement"] < 1e-4
+    assert d["ours"]["ms_per_step_median"] > 0 and d["reference_formulas"]["ms_per_step_median"] > 0
+    assert d["ours"]["loss_last"] < d["ours"]["loss_first"]
