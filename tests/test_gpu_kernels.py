@@ -20,6 +20,18 @@ def _ops():
     return ops
 
 
+def _assert_gemm_elementwise(out, ref, K, what=""):
+    """A norm ratio hides a wrong tail row or column (one row of a 4096-row product moves it by 1e-4). Element by
+    element: inputs are exact bf16 values accumulated in fp32, so an entry is off by its bf16 rounding (2^-9
+    relative) plus noise far below sqrt(K) * 2^-7; an entry that was never written, or written from the wrong
+    tile, is off by about sqrt(K)."""
+    err = (out.float() - ref.float()).abs()
+    bound = ref.float().abs() * 2.0 ** -7 + math.sqrt(K) * 2.0 ** -7
+    bad = err > bound
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} entries off, worst {float((err - bound).max()):.3g} " \
+                                f"at {tuple(torch.nonzero(bad)[0].tolist())}"
+
+
 # ----------------------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (384, 256, 192), (200, 136, 72),
                                    (1024, 4096, 1024), (4096, 1024, 512)])
@@ -40,6 +52,7 @@ def test_gemm_layouts(M, N, K, layout, kernel_status):
     torch.cuda.synchronize()
     assert out.shape == (M, N)
     assert _rel_err(out, ref) < 1e-2, f"{layout} {M}x{N}x{K}"
+    _assert_gemm_elementwise(out, ref, K, f"{layout} {M}x{N}x{K}")
 
 
 @pytest.mark.parametrize("bn", [128, 256])
@@ -69,6 +82,46 @@ def test_gemm_persistent_many_tiles(kernel_status):
     out = ops.matmul_nt(a, w)
     ref = a.float() @ w.float().t()
     assert _rel_err(out, ref) < 1e-2
+    _assert_gemm_elementwise(out, ref, K)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 512), (1000, 4104, 328), (4096, 2304, 1024), (304, 9000, 200)])
+@pytest.mark.parametrize("mode", ["pairs", "single"])
+def test_gemm_cta_pairs_and_single_cta_agree_elementwise(M, N, K, mode, kernel_status, monkeypatch):
+    """Large products run on CTA pairs (256 x 256 tiles); GF_GEMM_2SM=0 keeps the single-CTA kernel. Both must
+    be right in every entry, tails included (rows and columns that do not fill the last tile), with bias, residual
+    and accumulation into an fp32 output."""
+    import subprocess, sys, os, json
+    # the switch is read once per process, so each mode runs in its own interpreter
+    code = f"""
+import math, sys, torch
+sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})
+from ghost_flow_b200 import ops
+from ghost_flow_b200.ops import _lib
+torch.manual_seed(0)
+M, N, K = {M}, {N}, {K}
+a = torch.randn(M, K, device='cuda', dtype=torch.bfloat16)
+w = torch.randn(N, K, device='cuda', dtype=torch.bfloat16)
+bias = torch.randn(N, device='cuda', dtype=torch.bfloat16)
+res = torch.randn(M, N, device='cuda', dtype=torch.bfloat16)
+ref = a.float() @ w.float().t() + bias.float() + res.float()
+out = ops.gemm_raw(a, False, w, False, M, N, K, bias=bias, residual=res)
+err = (out.float() - ref).abs(); bound = ref.abs() * 2.0 ** -7 + math.sqrt(K) * 2.0 ** -7
+acc = torch.randn(M, N, device='cuda', dtype=torch.float32)
+ref2 = acc + 0.5 * (a.float() @ w.float().t())
+out2 = ops.gemm_raw(a, False, w, False, M, N, K, out=acc.clone(), accumulate=True, alpha=0.5)
+err2 = (out2 - ref2).abs(); bound2 = math.sqrt(K) * 2.0 ** -10 + ref2.abs() * 2.0 ** -12
+at = a.t().contiguous(); wt = w.t().contiguous()
+out3 = ops.matmul_tt(at, w)          # A stored [K, M], B stored [N, K]
+ref3 = a.float() @ w.float().t()
+err3 = (out3.float() - ref3).abs(); bound3 = ref3.abs() * 2.0 ** -7 + math.sqrt(K) * 2.0 ** -7
+torch.cuda.synchronize(); _lib.check_status()
+print(int((err > bound).sum()), int((err2 > bound2).sum()), int((err3 > bound3).sum()))
+"""
+    env = dict(os.environ, GF_GEMM_2SM="1" if mode == "pairs" else "0")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split()[-3:] == ["0", "0", "0"], r.stdout
 
 
 def test_linear_autograd(kernel_status):
