@@ -39,16 +39,26 @@ class LLaMAAttention(Module):
             kc, vc = cache
             kc[:, start_pos:start_pos + S] = k
             vc[:, start_pos:start_pos + S] = v
-            kk, vv = kc[:, :start_pos + S], vc[:, :start_pos + S]
-            G = H // Hk
-            qf = q.transpose(1, 2).float()
-            kf = kk.transpose(1, 2).float().repeat_interleave(G, 1)
-            vf = vv.transpose(1, 2).float().repeat_interleave(G, 1)
-            s = qf @ kf.transpose(-1, -2) / (D ** 0.5)
-            T = start_pos + S
-            mask = torch.ones(S, T, dtype=torch.bool, device=x.device).tril(T - S)
-            s = s.masked_fill(~mask, float("-inf"))
-            o = (torch.softmax(s, -1) @ vf).transpose(1, 2).to(x.dtype)
+            kernels = x.is_cuda and x.dtype == torch.bfloat16 and D in (64, 128) and not torch.is_grad_enabled()
+            if kernels and S == 1:
+                # one new token per sequence: the decode kernel streams the cache once (GQA groups share the reads)
+                from ..ops import raw
+
+                o = raw.attn_decode(q.reshape(B, H * D), kc.view(B, kc.shape[1], Hk * D), vc.view(B, vc.shape[1], Hk * D),
+                                    start_pos + 1, B, H, Hk, D).view(B, 1, H, D)
+            elif kernels and start_pos == 0:
+                o = ops.flash_attention(q, k, v, causal=True)        # prompt: nothing older than itself to attend to
+            else:
+                kk, vv = kc[:, :start_pos + S], vc[:, :start_pos + S]
+                G = H // Hk
+                qf = q.transpose(1, 2).float()
+                kf = kk.transpose(1, 2).float().repeat_interleave(G, 1)
+                vf = vv.transpose(1, 2).float().repeat_interleave(G, 1)
+                s = qf @ kf.transpose(-1, -2) / (D ** 0.5)
+                T = start_pos + S
+                mask = torch.ones(S, T, dtype=torch.bool, device=x.device).tril(T - S)
+                s = s.masked_fill(~mask, float("-inf"))
+                o = (torch.softmax(s, -1) @ vf).transpose(1, 2).to(x.dtype)
         else:
             o = ops.flash_attention(q, k, v, causal=True)
         return self.wo(o.reshape(B, S, H * D), residual)

@@ -22,3 +22,31 @@ def test_attn_decode_matches_reference(B, Hq, Hkv, D, n, splits):
     got2 = raw.attn_decode(q, kc, vc, lens, B, Hq, Hkv, D, splits=splits)
     ref2 = raw.attn_decode(q.cpu(), kc.cpu(), vc.cpu(), lens.cpu(), B, Hq, Hkv, D)
     assert ((got2.cpu().float() - ref2.float()).norm() / ref2.float().norm()) < 1e-2
+
+
+def test_llama_cached_generation_uses_the_decode_kernel_and_matches_full_forward(kernel_status):
+    """``LLaMAForCausalLM.generate`` on a GPU: the prompt goes through FlashAttention, every new token through the
+    decode-attention kernel over the KV cache. The logits of the cached path must agree with a full forward pass
+    over the same tokens (no cache), for grouped-query heads too."""
+    from ghost_flow_b200.models import LLaMAConfig, LLaMAForCausalLM
+    from ghost_flow_b200.ops import _lib
+
+    torch.manual_seed(0)
+    cfg = LLaMAConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+    model = LLaMAForCausalLM(cfg, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, cfg.vocab_size, (3, 40), device="cuda")
+    with torch.no_grad():
+        n0 = _lib.launch_count()
+        out = model.generate(ids, max_new_tokens=6)
+        assert _lib.launch_count() > n0
+        full = model(out[:, :-1])                       # logits of every position without a cache
+        caches = model.new_caches(3, 64)
+        step_logits = [model(out[:, :40], caches=caches, start_pos=0)[:, -1]]
+        for t in range(40, 45):
+            step_logits.append(model(out[:, t:t + 1], caches=caches, start_pos=t)[:, -1])
+    cached = torch.stack(step_logits, 1).float()        # [3, 6, vocab]
+    ref = full[:, 39:45].float()
+    rel = ((cached - ref).norm() / ref.norm()).item()
+    assert rel < 3e-2, rel
+    assert out.shape == (3, 46)
