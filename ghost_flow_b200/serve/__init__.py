@@ -11,6 +11,8 @@ hard-codes 784 -> 10), :81-105 (``predict`` echoes its input). Here ``POST /mode
     GET  /models/{id}           one model's description
     POST /models/load           {name, path[, kind]} -> {id, status}
     POST /models/{id}/predict   {inputs: [[f32]], shape} -> {outputs, shape, inference_time_ms}
+                                (a LLaMA checkpoint: inputs = token ids, optional max_new_tokens -> generated ids;
+                                 concurrent requests are batched by ``GenerationBatcher``)
     POST /models/{id}/unload    -> {id, status}
 
 The control plane is the standard library's threading HTTP server; ``ModelRegistry`` can be used without HTTP.
@@ -18,6 +20,7 @@ The control plane is the standard library's threading HTTP server; ``ModelRegist
 from __future__ import annotations
 
 import json
+import os
 import re
 import threading
 import time
@@ -69,6 +72,156 @@ def _build_from_state(state: dict, kind: str | None):
     raise ValueError(f"cannot infer an architecture from tensors {names[:6]}...; pass kind=")
 
 
+def _llama_config_from_state(state: dict, extra: dict | None = None):
+    """LLaMA hyper-parameters from tensor shapes (``extra`` may override: ``num_attention_heads``,
+    ``num_key_value_heads``, ``rope_theta``...; the head count cannot be read from shapes, head_dim 128 is assumed
+    for hidden sizes that allow it, else 64)."""
+    from ..models.configs import LLaMAConfig
+
+    emb = state["model.embed_tokens.weight"]
+    vocab, hidden = emb.shape
+    n_layers = 1 + max(int(m.group(1)) for n in state if (m := re.match(r"^model\.layers\.(\d+)\.", n)))
+    qkv_out = state["model.layers.0.attn.wqkv.weight"].shape[0]
+    inter = state["model.layers.0.mlp.w_gate_up.weight"].shape[0] // 2 if "model.layers.0.mlp.w_gate_up.weight" in state \
+        else state["model.layers.0.mlp.gate_up.weight"].shape[0] // 2
+    ex = dict(extra or {})
+    heads = int(ex.pop("num_attention_heads", hidden // (128 if hidden % 128 == 0 and hidden >= 512 else 64)))
+    hd = hidden // heads
+    kv = int(ex.pop("num_key_value_heads", (qkv_out // hd - heads) // 2))
+    return LLaMAConfig(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=n_layers,
+                       num_attention_heads=heads, num_key_value_heads=kv, **ex)
+
+
+class GenerationBatcher:
+    """Batching queue in front of a causal LM: requests wait up to ``max_wait_ms`` for company, compatible ones
+    (same prompt length and number of new tokens) are stacked with :class:`~ghost_flow_b200.nn.inference.BatchInference`
+    and run as ONE ``generate`` call; each request gets its own row back. The reference has the batching helper
+    (ghostflow-nn/src/inference.rs:151-215) but its server never executes a model (ghostflow-serve/src/models.rs:81-105)."""
+
+    def __init__(self, model, device, batch_size: int = 16, max_wait_ms: float = 4.0):
+        from ..nn.inference import BatchInference
+
+        self.model, self.device = model, device
+        self.batch_size, self.max_wait_ms = batch_size, max_wait_ms
+        self._mk = lambda: BatchInference(batch_size, max_wait_ms)
+        self._queues: dict = {}            # (prompt_len, new_tokens) -> (BatchInference, [waiters])
+        self._cv = threading.Condition()
+        self._stop = False
+        self.batches_run = 0
+        self.requests_run = 0
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+
+    def submit(self, ids: torch.Tensor, max_new_tokens: int):
+        """ids: 1-D int64 prompt. Blocks until the continuation is there; returns the full token row."""
+        slot = {"done": threading.Event(), "out": None, "err": None}
+        key = (int(ids.numel()), int(max_new_tokens))
+        with self._cv:
+            q = self._queues.get(key)
+            if q is None:
+                q = self._queues[key] = (self._mk(), [])
+            q[0].add(ids)
+            q[1].append(slot)
+            self._cv.notify()
+        slot["done"].wait()
+        if slot["err"] is not None:
+            raise slot["err"]
+        return slot["out"]
+
+    def _loop(self):
+        while True:
+            with self._cv:
+                while not self._stop and not any(b.is_ready() for b, _ in self._queues.values()):
+                    self._cv.wait(timeout=self.max_wait_ms / 1e3 if self._queues else None)
+                if self._stop:
+                    return
+                key = next(k for k, (b, _) in self._queues.items() if b.is_ready())
+                b, waiters = self._queues[key]
+                batch = b.get_batch()
+                mine, rest = waiters[:batch.shape[0]], waiters[batch.shape[0]:]
+                if rest:
+                    self._queues[key] = (b, rest)
+                else:
+                    del self._queues[key]
+            try:
+                with torch.no_grad():
+                    out = self.model.generate(batch.to(self.device), key[1]).cpu()
+                for i, w in enumerate(mine):
+                    w["out"] = out[i]
+            except Exception as e:       # hand the failure to every request of the batch
+                for w in mine:
+                    w["err"] = e
+            self.batches_run += 1
+            self.requests_run += len(mine)
+            for w in mine:
+                w["done"].set()
+
+    def close(self):
+        with self._cv:
+            self._stop = True
+            self._cv.notify_all()
+
+
+def _build_llama(state: dict, device, extra: dict | None = None):
+    from ..models.llama import LLaMAForCausalLM
+
+    cfg = _llama_config_from_state(state, extra)
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    model = LLaMAForCausalLM(cfg, device=device, dtype=dtype)
+    own = model.state_dict()
+    missing = [k for k in own if k not in state]
+    if missing:
+        raise ValueError(f"LLaMA checkpoint lacks {missing[:4]}")
+    with torch.no_grad():
+        for k, v in own.items():
+            v.copy_(state[k].to(device=device, dtype=dtype))
+    model.eval()
+    desc = {"architecture": "llama", "layers": cfg.num_hidden_layers, "hidden_size": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "vocab_size": cfg.vocab_size,
+            "input_shape": ["prompt_len"], "output_shape": ["prompt_len + max_new_tokens"]}
+    return model, desc
+
+
+class LoadedLlama:
+    """A LLaMA checkpoint behind the generation batcher. ``predict`` takes token ids (one prompt per row) and
+    ``max_new_tokens`` and returns the greedy continuation."""
+
+    def __init__(self, mid, name, path, model, desc, device, batch_size=16, max_wait_ms=4.0):
+        self.id, self.name, self.path, self.desc, self.device = mid, name, path, desc, device
+        self.model = model
+        self.batcher = GenerationBatcher(model, device, batch_size, max_wait_ms)
+        self.loaded_at = time.time()
+        self.requests = 0
+
+    def describe(self):
+        return {"id": self.id, "name": self.name, "path": self.path, "device": str(self.device),
+                "requests": self.requests, "loaded_at": self.loaded_at, "batches_run": self.batcher.batches_run,
+                **self.desc}
+
+    def predict(self, inputs, shape=None, max_new_tokens: int = 16):
+        ids = torch.tensor(inputs, dtype=torch.int64)
+        if shape:
+            ids = ids.reshape(shape)
+        if ids.ndim == 1:
+            ids = ids[None]
+        if int(ids.min()) < 0 or int(ids.max()) >= self.desc["vocab_size"]:
+            raise ValueError("token id out of range")
+        t0 = time.perf_counter()
+        rows = [None] * ids.shape[0]
+        threads = [threading.Thread(target=lambda i=i: rows.__setitem__(i, self.batcher.submit(ids[i], max_new_tokens)))
+                   for i in range(ids.shape[0])]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        self.requests += 1
+        out = torch.stack(rows)
+        return {"outputs": out.tolist(), "shape": list(out.shape), "inference_time_ms": (time.perf_counter() - t0) * 1e3}
+
+    def close(self):
+        self.batcher.close()
+
+
 class LoadedModel:
     def __init__(self, mid, name, path, run, to_dev, desc, device):
         self.id, self.name, self.path, self.desc, self.device = mid, name, path, desc, device
@@ -108,8 +261,19 @@ class ModelRegistry:
     def load_model(self, name: str, path: str, kind: str | None = None) -> str:
         from .. import io as gf_io
         state = gf_io.load_state_dict(path)
-        run, to_dev, desc = _build_from_state(state, kind)
         mid = uuid.uuid4().hex[:12]
+        if kind == "llama" or (kind is None and "model.embed_tokens.weight" in state):
+            # decoder checkpoints (the names of models.llama.LLaMAForCausalLM.state_dict()) run behind the
+            # generation batcher; an optional JSON file beside the checkpoint carries what shapes cannot tell
+            extra = None
+            if os.path.exists(os.fspath(path) + ".json"):
+                with open(os.fspath(path) + ".json") as f:
+                    extra = json.load(f)
+            model, desc = _build_llama(state, self.device, extra)
+            with self._lock:
+                self.models[mid] = LoadedLlama(mid, name, path, model, desc, self.device)
+            return mid
+        run, to_dev, desc = _build_from_state(state, kind)
         with self._lock:
             self.models[mid] = LoadedModel(mid, name, path, run, to_dev, desc, self.device)
         return mid
@@ -135,8 +299,11 @@ class ModelRegistry:
 
     def unload(self, mid):
         with self._lock:
-            if self.models.pop(mid, None) is None:
+            m = self.models.pop(mid, None)
+            if m is None:
                 raise ModelNotFound(mid)
+        if hasattr(m, "close"):
+            m.close()
 
     def list(self):
         return [m.describe() for m in self.models.values()]
@@ -197,7 +364,10 @@ def make_handler(registry: ModelRegistry):
                     registry.unload(m.group(1))
                     return self._send(200, {"id": m.group(1), "status": "unloaded"})
                 b = self._body()
-                self._send(200, registry.get(m.group(1)).predict(b["inputs"], b.get("shape")))
+                model = registry.get(m.group(1))
+                if isinstance(model, LoadedLlama):
+                    return self._send(200, model.predict(b["inputs"], b.get("shape"), int(b.get("max_new_tokens", 16))))
+                self._send(200, model.predict(b["inputs"], b.get("shape")))
             except ModelNotFound as e:
                 self._send(404, {"error": f"model {e.args[0]} not found"})
             except (KeyError, ValueError, RuntimeError, OSError) as e:
