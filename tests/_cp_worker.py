@@ -8,7 +8,8 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from ghost_flow_b200.ops import _lib, raw  # noqa: E402
-from ghost_flow_b200.parallel.context import ContextParallelAttention, UlyssesAttention  # noqa: E402
+from ghost_flow_b200.parallel.context import (ContextParallelAttention, UlyssesAttention,  # noqa: E402
+                                               ZigZagContextParallelAttention, zigzag_rows)
 
 
 def rel(a, b):
@@ -41,6 +42,15 @@ def main():
     dq2, dk2, dv2 = ul.backward(ctx, dol)
     res.update(ulysses_o=rel(o2, o_ref[sl]), ulysses_dq=rel(dq2, dq_r[sl]), ulysses_dk=rel(dk2, dk_r[sl]),
                ulysses_dv=rel(dv2, dv_r[sl]))
+    # load-balanced (zig-zag) assignment; with 512 local rows the halves are 256-row blocks, a size both
+    # attention kernels take
+    rows = zigzag_rows(S * world, world, rank).to(dev)
+    qz, kz, vz, doz = (t[rows].contiguous() for t in (q, k, v, do))
+    zz = ZigZagContextParallelAttention(B, S, H, Hkv, D)
+    oz, lz = zz.forward(qz, kz, vz)
+    dqz, dkz, dvz = zz.backward(qz, kz, vz, oz, lz, doz)
+    res.update(zigzag_o=rel(oz, o_ref[rows]), zigzag_dq=rel(dqz, dq_r[rows]), zigzag_dk=rel(dkz, dk_r[rows]),
+               zigzag_dv=rel(dvz, dv_r[rows]))
     torch.cuda.synchronize()
     _lib.check_status(dev)
     worst = torch.tensor([max(res.values())], device=dev)

@@ -145,6 +145,19 @@ def case_context(rank, world, out):
     res["ulysses_o"] = (o2 - o_ref[sl]).abs().max().item()
     res["ulysses_dq"] = (dq2 - dq_r[sl]).abs().max().item()
     res["ulysses_dk"] = (dk2 - dk_r[sl]).abs().max().item()
+    # zig-zag assignment: rank r holds chunks r and 2 * world - 1 - r of the sequence
+    from ghost_flow_b200.parallel.context import ZigZagContextParallelAttention, causal_work_per_rank, zigzag_rows
+    rows = zigzag_rows(S * world, world, rank)
+    zz = ZigZagContextParallelAttention(B, S, H, Hkv, D)
+    qz, kz, vz, doz = (t[rows].contiguous() for t in (q, k, v, do))
+    oz, lz = zz.forward(qz, kz, vz)
+    dqz, dkz, dvz = zz.backward(qz, kz, vz, oz, lz, doz)
+    res["zigzag_o"] = (oz - o_ref[rows]).abs().max().item()
+    res["zigzag_dq"] = (dqz - dq_r[rows]).abs().max().item()
+    res["zigzag_dk"] = (dkz - dk_r[rows]).abs().max().item()
+    res["zigzag_dv"] = (dvz - dv_r[rows]).abs().max().item()
+    res["balance_contiguous"] = max(causal_work_per_rank(world, False)) * world
+    res["balance_zigzag"] = max(causal_work_per_rank(world, True)) * world
     return res
 
 
