@@ -95,15 +95,22 @@ struct RsAdamArgs {
   int* done_counter;        // local int, zero before launch; reset by the last block
   uint32_t wait_limit;
   int* status;
+  // reduce-only mode (gradient clipping / overflow check need the global norm before any update): the reduced,
+  // scaled gradient of the shard goes to grad_out (fp32) and its sum of squares is added to *sumsq; master, moments
+  // and weights are left alone and no version flag is published
+  float* grad_out;
+  float* sumsq;
 };
 
 // Register budget: at most 64 per thread (4 CTAs of 256 threads per SM) and one CTA per SM in the launch, so
 // that the persistent GEMM / all-gather CTAs of the other streams always find room beside it. With a larger
 // footprint those kernels cannot start until this one has drained, and the "overlapped" update serialises.
-template <bool USE_MC>
+template <bool USE_MC, bool REDUCE_ONLY = false>
 __global__ void __launch_bounds__(256, 4)
 rs_adamw_kernel(const RsAdamArgs a) {
   __shared__ int s_ok;
+  __shared__ float s_sq[8];
+  float sq = 0.f;
   if (threadIdx.x < 32) {
     bool ok = true;
     if (threadIdx.x < a.world) ok = wait_flag_ge(a.local_pad + a.ready_idx + threadIdx.x, a.ready_val, a.wait_limit);
@@ -158,6 +165,16 @@ rs_adamw_kernel(const RsAdamArgs a) {
           }
         }
       }
+      if (REDUCE_ONLY) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          g[j] *= a.grad_scale;
+          sq += g[j] * g[j];
+        }
+        reinterpret_cast<float4*>(a.grad_out)[i * 2] = *reinterpret_cast<float4*>(g);
+        reinterpret_cast<float4*>(a.grad_out)[i * 2 + 1] = *reinterpret_cast<float4*>(g + 4);
+        continue;
+      }
       float pv[8], mv[8], vv[8];
       *reinterpret_cast<float4*>(pv) = reinterpret_cast<const float4*>(a.master)[i * 2];
       *reinterpret_cast<float4*>(pv + 4) = reinterpret_cast<const float4*>(a.master)[i * 2 + 1];
@@ -185,6 +202,17 @@ rs_adamw_kernel(const RsAdamArgs a) {
         o.z = pack_bf16x2(pv[4], pv[5]); o.w = pack_bf16x2(pv[6], pv[7]);
         reinterpret_cast<uint4*>(a.p_lp)[i] = o;
       }
+    }
+  }
+  if (REDUCE_ONLY) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+    if ((threadIdx.x & 31) == 0) s_sq[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += s_sq[w];
+      atomicAdd(a.sumsq, t);
     }
   }
   // last block to finish tells every rank that their gradient buffer has been consumed by this rank and
@@ -286,6 +314,8 @@ static void configure_comm_kernels() {
   prefer_max_smem(wait_flags_kernel);
   prefer_max_smem(rs_adamw_kernel<true>);
   prefer_max_smem(rs_adamw_kernel<false>);
+  prefer_max_smem(rs_adamw_kernel<true, true>);
+  prefer_max_smem(rs_adamw_kernel<false, true>);
   prefer_max_smem(allgather_pull_kernel);
   prefer_max_smem(fill_int_kernel);
   done = true;
@@ -349,6 +379,7 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
   a.ready_idx = ready_idx; a.ready_val = ready_val; a.consumed_idx = consumed_idx; a.consumed_val = consumed_val;
   a.version_idx = version_idx; a.version_val = version_val;
   a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
+  a.grad_out = nullptr; a.sumsq = nullptr;
   long long want = ((n >> 3) + 255) / 256;
   int grid = max_ctas > 0 ? max_ctas : sm_count();
   if (want < grid) grid = (int)(want > 0 ? want : 1);
@@ -356,6 +387,42 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
     rs_adamw_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
   else
     rs_adamw_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+// Reduce-scatter alone, for steps that need the global gradient norm before they may update (clipping, overflow
+// check): this rank's slice of every rank's gradient buffer is summed in fp32, multiplied by grad_scale and written
+// to grad_out (fp32 [n]); the sum of its squares is ADDED to *sumsq (zero it once per step). Flags as in
+// gf_rs_adamw_fused, except that no weight version is published.
+GF_API int gf_rs_reduce_only(const unsigned long long* grad_ptrs, unsigned long long mc_grads,
+                             const unsigned long long* pads, int world, int my_rank, long long shard_lo, long long n,
+                             float* grad_out, float* sumsq, float grad_scale, int ready_idx, int ready_val,
+                             int consumed_idx, int consumed_val, int* done_counter, int max_ctas, long long wait_limit,
+                             int* status, void* stream) {
+  gf::enter();
+  configure_comm_kernels();
+  if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_lo & 7) || !grad_out || !sumsq) return GFH_BAD_ARG;
+  RsAdamArgs a;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    a.grads.p[r] = r < world ? reinterpret_cast<const void*>(grad_ptrs[r]) : nullptr;
+    a.pads.p[r] = r < world ? reinterpret_cast<int*>(pads[r]) : nullptr;
+  }
+  a.mc_grads = reinterpret_cast<const void*>(mc_grads);
+  a.shard_lo = shard_lo; a.n = n; a.master = nullptr; a.m = nullptr; a.v = nullptr; a.p_lp = nullptr;
+  a.lr = 0.f; a.beta1 = 0.f; a.beta2 = 0.f; a.eps = 0.f; a.wd = 0.f; a.grad_scale = grad_scale; a.bc1 = 1.f; a.bc2 = 1.f;
+  a.world = world; a.my_rank = my_rank;
+  a.local_pad = a.pads.p[my_rank];
+  a.ready_idx = ready_idx; a.ready_val = ready_val; a.consumed_idx = consumed_idx; a.consumed_val = consumed_val;
+  a.version_idx = -1; a.version_val = 0;
+  a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
+  a.grad_out = grad_out; a.sumsq = sumsq;
+  long long want = ((n >> 3) + 255) / 256;
+  int grid = max_ctas > 0 ? max_ctas : sm_count();
+  if (want < grid) grid = (int)(want > 0 ? want : 1);
+  if (mc_grads)
+    rs_adamw_kernel<true, true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  else
+    rs_adamw_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
 

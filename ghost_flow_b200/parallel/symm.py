@@ -92,7 +92,9 @@ class FusedComm(Comm):
         lib.gf_rs_adamw_fused.argtypes = [P, ctypes.c_ulonglong, P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F,
                                           I, I, I, I, I, I, P, I, L, P, P]
         lib.gf_allgather_pull.argtypes = [P, P, L, I, I, P, I, I, P, I, P, I, L, P, P]
-        for fn in (lib.gf_signal_peers, lib.gf_wait_flags, lib.gf_rs_adamw_fused, lib.gf_allgather_pull):
+        lib.gf_rs_reduce_only.argtypes = [P, ctypes.c_ulonglong, P, I, I, L, L, P, P, F, I, I, I, I, P, I, L, P, P]
+        for fn in (lib.gf_signal_peers, lib.gf_wait_flags, lib.gf_rs_adamw_fused, lib.gf_allgather_pull,
+                   lib.gf_rs_reduce_only):
             fn.restype = I
 
     # ------------------------------------------------------------------ arena
@@ -183,3 +185,32 @@ class FusedComm(Comm):
             PAD_READY + slot * 8, use, PAD_CONSUMED + slot * 8, use, PAD_VERSION + unit_index * 8, version,
             self.rs_counter.data_ptr(), 0, 0, _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check_rc(rc, "gf_rs_adamw_fused")
+
+    def reduce_only(self, unit, unit_index: int, g_full: torch.Tensor, slot: int, grad_out: torch.Tensor,
+                    sumsq: torch.Tensor, grad_scale: float = 1.0) -> None:
+        """Reduce-scatter without the update: this rank's slice of every rank's gradient buffer, summed in fp32,
+        lands in ``grad_out`` (fp32 [shard_numel]) and the sum of its squares is added to ``sumsq`` (a device
+        float). Used when the step needs the global gradient norm before it may touch the weights."""
+        if self.dry_run:
+            grad_out.copy_(g_full[unit.lo:unit.lo + unit.shard_numel].float() * grad_scale)
+            sumsq.add_(grad_out.square().sum())
+            return
+        use = self.slot_use[slot]
+        rc = self.lib.gf_rs_reduce_only(
+            self.peer_ptrs(g_full), self.mc_ptr(g_full), self.pad_ptrs, self.world, self.rank, unit.lo,
+            unit.shard_numel, grad_out.data_ptr(), sumsq.data_ptr(), float(grad_scale), PAD_READY + slot * 8, use,
+            PAD_CONSUMED + slot * 8, use, self.rs_counter.data_ptr(), 0, 0,
+            _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "gf_rs_reduce_only")
+
+    def publish_version(self, unit_index: int) -> None:
+        """After an update of this rank's shard of ``unit_index`` that was NOT done by the fused reducer (the
+        deferred AdamW of a clipped step): tells every peer that the shard holds the next version, on the current
+        stream, behind the kernels that wrote it."""
+        version = self.unit_updates.get(unit_index, 0) + 1
+        self.unit_updates[unit_index] = version
+        if self.dry_run:
+            return
+        rc = self.lib.gf_signal_peers(self.pad_ptrs, self.world, self.rank, PAD_VERSION + unit_index * 8, version,
+                                      _lib.stream_ptr())
+        _lib.check_rc(rc, "gf_signal_peers")

@@ -37,6 +37,13 @@ class OptimConfig:
     beta2: float = 0.95
     eps: float = 1e-8
     weight_decay: float = 0.01
+    # Global-norm gradient clipping. When set, a step first reduces all gradients (keeping each rank's reduced fp32
+    # shard), forms the global norm with one scalar all-reduce, and only then updates, with the clip coefficient
+    # folded into the AdamW kernel; a non-finite norm skips the update altogether (the step count does not advance).
+    # Without it the update of a layer runs inside the reducer while the backward pass is still going.
+    # (The reference scans for inf/nan and skips the step in its GradScaler, ghostflow-nn/src/mixed_precision.rs:115-180,
+    # and advertises clipping without implementing it.)
+    max_grad_norm: float | None = None
 
 
 class _Unit:
@@ -57,6 +64,7 @@ class _Unit:
         self.shard_numel = self.padded // world
         self.lo = rank * self.shard_numel
         self.shard = None   # allocated by the engine (from the communicator's arena when it has one)
+        self.gred = None    # reduced fp32 gradient shard, only with gradient clipping (allocated on first use)
         self.master = None
         self.m = None
         self.v = None
@@ -177,6 +185,8 @@ class Zero3LlamaEngine:
                 self.full_layers = [torch.empty(u.padded, dtype=dtype, device=self.device) for u in self.layers]
         self._rope = None
         self.last_stats = {}
+        self.skipped_steps = 0
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         # kernel status word of the previous steps, copied to pinned memory without stalling the stream
         self._status_host = None
         self._status_event = None
@@ -257,14 +267,30 @@ class Zero3LlamaEngine:
 
     def _reduce_and_update(self, unit, slot):
         """Gradient reduce-scatter + AdamW on this rank's shard, off the compute stream.
-        Returns an event that marks when gradient buffer ``slot`` may be overwritten."""
+        Returns an event that marks when gradient buffer ``slot`` may be overwritten. With gradient clipping the
+        update is deferred: only the reduction runs here (see :meth:`_finish_clipped_step`)."""
         st = self.streams
         g_full = self.gfull[slot][:unit.padded]
         o = self.opt
         kw = dict(lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay,
                   step=self.step_count)
+        deferred = o.max_grad_norm is not None
 
         def run():
+            if deferred:
+                if unit.gred is None:
+                    unit.gred = torch.zeros(unit.shard_numel, dtype=torch.float32, device=self.device)
+                if self.comm.fused:
+                    self.comm.reduce_only(unit, unit.index, g_full, slot, unit.gred, self._sumsq)
+                    return
+                if self.world == 1:
+                    unit.gred.copy_(g_full[:unit.shard_numel].float())
+                else:
+                    g = self.gshard[:unit.shard_numel]
+                    self.comm.reduce_scatter(g_full, g)
+                    unit.gred.copy_(g.float())
+                self._sumsq.add_(unit.gred.square().sum())
+                return
             if self.comm.fused:
                 self.comm.reduce_scatter_adamw(unit, unit.index, g_full, slot, **kw)
                 return
@@ -287,6 +313,33 @@ class Zero3LlamaEngine:
             return ev
         run()
         return None
+
+    def _finish_clipped_step(self):
+        """Second half of a step with ``max_grad_norm``: global norm from the per-shard sums of squares (one scalar
+        all-reduce), clip coefficient, AdamW on every shard. Returns False when the norm was not finite and the
+        update was skipped."""
+        o = self.opt
+        if self.streams.cuda:
+            torch.cuda.current_stream().wait_stream(self.streams.opt)
+            torch.cuda.current_stream().wait_stream(self.streams.comm)
+        total = self._sumsq.clone()
+        if self.world > 1:
+            self.comm.all_reduce_scalar(total)
+        norm = float(total.sqrt())                      # one host read per step: the decision to skip is the host's
+        finite = math.isfinite(norm)
+        coef = min(1.0, o.max_grad_norm / (norm + 1e-6)) if finite else 0.0
+        self.last_stats = {"grad_norm": norm, "clip_coef": coef, "skipped": not finite}
+        self._sumsq.zero_()
+        if not finite:
+            self.step_count -= 1                        # bias correction continues from the last applied step
+            self.skipped_steps += 1
+            return False
+        for u in self.units:
+            K.adamw_flat(u.master, u.m, u.v, u.gred, u.shard, lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
+                         weight_decay=o.weight_decay, step=self.step_count, grad_scale=coef)
+            if self.comm.fused:
+                self.comm.publish_version(u.index)
+        return True
 
     # ------------------------------------------------------------------ layer math
     def _rope_tables(self, S):
@@ -416,6 +469,8 @@ class Zero3LlamaEngine:
         grad_free[gslot] = self._reduce_and_update(self.embed, gslot)
         for e in grad_free:
             self._wait(e)
+        if self.opt.max_grad_norm is not None:
+            self._finish_clipped_step()
         if self.world > 1:
             loss = self.comm.all_reduce_scalar(loss.clone()) / self.world
         self._post_status()
