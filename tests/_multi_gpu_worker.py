@@ -26,7 +26,9 @@ def main():
     base = kind.split("_")[0]
     persist = None if "nopersist" not in kind else False
     comm = make_comm(base, dev)
-    eng = Zero3LlamaEngine(cfg, dev, optim=OptimConfig(lr=2e-3), comm=comm, seed=5, persist_gathered=persist)
+    clip = 0.5 if "clip" in kind else None      # well under the first steps' gradient norm: the bound bites
+    eng = Zero3LlamaEngine(cfg, dev, optim=OptimConfig(lr=2e-3, max_grad_norm=clip), comm=comm, seed=5,
+                           persist_gathered=persist)
     g = torch.Generator().manual_seed(99)
     tok = torch.randint(0, cfg.vocab_size, (world, 257), generator=g)
     mine = tok[rank:rank + 1].to(dev)
@@ -53,7 +55,8 @@ def main():
     _lib.check_status(dev)
     w = eng.gather_unit(eng.layers[2], master=True)["w_gate_up"].cpu()
     if rank == 0:
-        torch.save({"losses": losses, "w": w, "fused": bool(getattr(comm, "fused", False))}, out)
+        torch.save({"losses": losses, "w": w, "fused": bool(getattr(comm, "fused", False)),
+                    "stats": dict(eng.last_stats)}, out)
     dist.barrier()
     dist.destroy_process_group()
 

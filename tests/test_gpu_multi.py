@@ -65,6 +65,19 @@ def test_fused_path_resumes_from_a_sharded_checkpoint(tmp_path):
     assert rel < 1e-2, rel
 
 
+def test_clipped_steps_fused_reduce_only_matches_nccl(tmp_path):
+    """Gradient clipping on the peer-memory path: the reducer runs in its reduce-only mode (fp32 shard + sum of
+    squares), AdamW follows once the global norm is known, version flags are published after it."""
+    _need(2)
+    fused = _run("fused_clip", str(tmp_path / "f.pt"), 2, port=29765)
+    nccl = _run("nccl_clip", str(tmp_path / "n.pt"), 2, port=29767)
+    assert fused["fused"] and fused["stats"]["clip_coef"] < 1.0 and not fused["stats"]["skipped"]
+    assert abs(fused["stats"]["grad_norm"] - nccl["stats"]["grad_norm"]) < 2e-2 * nccl["stats"]["grad_norm"]
+    for a, b in zip(fused["losses"], nccl["losses"]):
+        assert abs(a - b) < 2e-2, (fused["losses"], nccl["losses"])
+    assert (fused["w"] - nccl["w"]).norm() / nccl["w"].norm() < 1e-2
+
+
 def test_fused_tensor_parallel_kernels_match_nccl(tmp_path):
     """all-gather + GEMM and GEMM + reduce-scatter as single kernels against NCCL followed / preceded by the GEMM."""
     _need(2)
