@@ -57,8 +57,10 @@ def test_fused_path_resumes_from_a_sharded_checkpoint(tmp_path):
     plain = _run("fused", str(tmp_path / "f.pt"), 2, port=29745)
     resumed = _run("fused_resume", str(tmp_path / "r.pt"), 2, port=29747)
     rotating = _run("fused_resume_nopersist", str(tmp_path / "q.pt"), 2, port=29749)
+    # independent bf16 runs drift apart by a few 1e-3 in the loss within four AdamW steps (see below); a resume
+    # on stale or zero weights would be off by whole units
     for a, b, c in zip(plain["losses"], resumed["losses"], rotating["losses"]):
-        assert abs(a - b) < 2e-3 and abs(a - c) < 2e-3, (plain["losses"], resumed["losses"], rotating["losses"])
+        assert abs(a - b) < 1e-2 and abs(a - c) < 1e-2, (plain["losses"], resumed["losses"], rotating["losses"])
     # two runs of the same job already differ in the last bits (the attention backward adds dQ tiles in arrival
     # order) and AdamW turns that into differences of a few 1e-3 after four steps at this learning rate
     rel = ((plain["w"] - resumed["w"]).norm() / plain["w"].norm()).item()
