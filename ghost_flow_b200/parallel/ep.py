@@ -93,6 +93,10 @@ class MoEContext:
     src_start: torch.Tensor
     h: torch.Tensor
     a: torch.Tensor
+    # copies of the workspaces the backward pass reads, taken when the layer object is shared between layers:
+    comb: torch.Tensor = None     # per-slot expert outputs [T * k, d]
+    xs: torch.Tensor = None       # the rows this rank's experts received [rows_cap, d]
+    ret: torch.Tensor = None      # their return addresses (source rank, slot) [rows_cap, 2]
 
 
 class ExpertParallelMoE:
@@ -137,8 +141,20 @@ class ExpertParallelMoE:
                       "w2": torch.zeros_like(self.w2)}
         self.epoch = 0
         self.last_counts = None
+        # One instance can serve every MoE layer of a model (its buffers are workspaces; the weights are swapped
+        # with set_weights): then the per-slot outputs, which the backward pass needs, must be copied out of the
+        # workspace into the layer's context.
+        self.keep_slot_outputs = False
+        self.aux_coef = 0.0
         if self.device.type == "cuda":
             self._alloc()
+
+    def set_weights(self, gate_pad, w13, w2, gate_grad_pad, g13, g2):
+        """Points the layer at another set of parameters and gradient buffers (same shapes)."""
+        self.gate_pad, self.gate = gate_pad, gate_pad[:self.E]
+        self.w13, self.w2 = w13, w2
+        self.gate_grad_pad = gate_grad_pad
+        self.grads = {"gate": gate_grad_pad[:self.E], "w13": g13, "w2": g2}
 
     # ------------------------------------------------------------------ buffers
     def _alloc(self):
@@ -212,6 +228,10 @@ class ExpertParallelMoE:
         h = torch.empty(R, 2 * f, dtype=torch.bfloat16, device=dev)
         grouped_gemm(self.xs, self.w13, h, 1, seg, self.el, rows_cap=R, N=2 * f, K=d,
                      wait=(src_start, self.flags[FLAG_DISPATCH * 8:], W, ep))
+        # Copies for a backward pass that runs after other layers reused the workspace. They are taken here, before
+        # the second GEMM: a peer starts its next dispatch into xs / ret only after its combine, which waits for this
+        # rank's second GEMM, so everything submitted before that GEMM reads the rows of this call.
+        keep_in = (self.xs.clone(), self.ret.clone()) if self.keep_slot_outputs else (None, None)
         a = raw.swiglu_fwd(h)
         grouped_gemm(a, self.w2, self.comb, 1, seg, self.el, rows_cap=R, N=d, K=f,
                      scatter=(self.ret, self.p["comb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
@@ -221,7 +241,9 @@ class ExpertParallelMoE:
                                          self.flags.data_ptr(), FLAG_COMBINE, ep, W, None, None, status, st()),
                       "gf_moe_combine")
         self.last_counts = self.counts.clone()
-        return y, MoEContext(x, idx, w, probs, dest_row, seg, src_start, h, a)
+        # comb is written by the peers' second GEMM of a call, which needs this rank's dispatch of that call: later
+        keep_out = self.comb.clone() if self.keep_slot_outputs else None
+        return y, MoEContext(x, idx, w, probs, dest_row, seg, src_start, h, a, keep_out, *keep_in)
 
     def _flag_ptrs(self, row):
         """Every rank's flag row ``row`` (the kernels index it by source rank)."""
@@ -239,7 +261,10 @@ class ExpertParallelMoE:
         dy = dy.contiguous()
         # d(weights): <dy[t], expert output of slot s>; the per-slot outputs are still in comb
         dots = torch.empty(T, k, dtype=torch.float32, device=dev)
-        _lib.check_rc(lib.gf_moe_combine(self.comb.data_ptr(), None, None, None, T, k, d, None, 0, 0, W, dy.data_ptr(),
+        comb = ctx.comb if ctx.comb is not None else self.comb
+        xs = ctx.xs if ctx.xs is not None else self.xs
+        ret = ctx.ret if ctx.ret is not None else self.ret
+        _lib.check_rc(lib.gf_moe_combine(comb.data_ptr(), None, None, None, T, k, d, None, 0, 0, W, dy.data_ptr(),
                                          dots.data_ptr(), status, st()), "gf_moe_combine(dots)")
         # gradient of the combine = dispatch of w * dy to the forward rows
         self.epoch += 1
@@ -256,16 +281,16 @@ class ExpertParallelMoE:
         grouped_gemm(self.dys, ctx.a, self.grads["w2"], 2, seg, self.el, rows_cap=R, M=d, N=f, K=R, accumulate=True)
         dh = raw.swiglu_bwd(ctx.h, da)
         # padding rows of h are zero, so dh is zero there as well and the weight gradient ignores them
-        grouped_gemm(dh, self.xs, self.grads["w13"], 2, seg, self.el, rows_cap=R, M=2 * f, N=d, K=R, accumulate=True)
+        grouped_gemm(dh, xs, self.grads["w13"], 2, seg, self.el, rows_cap=R, M=2 * f, N=d, K=R, accumulate=True)
         grouped_gemm(dh, self.w13, self.dcomb, 1, seg, self.el, rows_cap=R, N=d, K=2 * f, b_mn=True,
-                     scatter=(self.ret, self.p["dcomb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
+                     scatter=(ret, self.p["dcomb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
                               self.done[1:]))
         dx = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
         _lib.check_rc(lib.gf_moe_combine(self.dcomb.data_ptr(), None, None, dx.data_ptr(), T, k, d,
                                          self.flags.data_ptr(), FLAG_COMBINE, ep, W, None, None, status, st()),
                       "gf_moe_combine(dx)")
         # router: weights -> probabilities -> logits (small [T, E] tensors)
-        dlogits = self._router_backward(ctx, dots)
+        dlogits = self._router_backward(ctx, dots, self.aux_coef, self.E)
         dl = torch.zeros(T, self.gate_pad.shape[0], dtype=torch.bfloat16, device=dev)
         dl[:, :E] = dlogits
         raw.gemm(dl, False, self.gate_pad, False, out=dx, accumulate=True)
@@ -273,7 +298,10 @@ class ExpertParallelMoE:
         return dx
 
     @staticmethod
-    def _router_backward(ctx: MoEContext, dw: torch.Tensor) -> torch.Tensor:
+    def _router_backward(ctx: MoEContext, dw: torch.Tensor, aux_coef: float = 0.0, E: int = 0) -> torch.Tensor:
+        """Gradient of the routing weights (and, with ``aux_coef``, of ``aux_coef * aux_loss``) w.r.t. the router
+        logits. The load-balance loss ``E * sum_e f_e * P_e`` is differentiated through the mean probabilities
+        ``P_e`` only; the token fractions ``f_e`` are counts."""
         p = ctx.probs
         idx = ctx.idx.long()
         psel = p.gather(1, idx)
@@ -281,6 +309,9 @@ class ExpertParallelMoE:
         wn = psel / s
         dpsel = (dw - (dw * wn).sum(1, keepdim=True)) / s
         dp = torch.zeros_like(p).scatter_(1, idx, dpsel)
+        if aux_coef:
+            frac = torch.bincount(idx.flatten(), minlength=E).float() / idx.numel()
+            dp = dp + (aux_coef * E / p.shape[0]) * frac[None, :]
         return p * (dp - (dp * p).sum(1, keepdim=True))
 
     # ------------------------------------------------------------------ statistics / auxiliary loss
@@ -304,12 +335,13 @@ class ExpertParallelMoE:
         dist.all_gather_into_tensor(w2, self.w2, group=self.group)
         return w13, w2
 
-    def dense_reference(self, x, w13=None, w2=None, residual=None):
+    def dense_reference(self, x, w13=None, w2=None, residual=None, gate=None):
         """fp32 PyTorch restatement: every token through its top-k experts, differentiable."""
         w13 = self.w13 if w13 is None else w13
         w2 = self.w2 if w2 is None else w2
+        gate = self.gate if gate is None else gate
         xf = x.float()
-        probs = torch.softmax(xf @ self.gate.float().t(), -1)
+        probs = torch.softmax(xf @ gate.float().t(), -1)
         top, idx = probs.topk(self.k, -1)
         wts = top / top.sum(-1, keepdim=True)
         y = torch.zeros_like(xf)
@@ -328,20 +360,23 @@ class ExpertParallelMoE:
     def _forward_ref(self, x, residual):
         assert self.world == 1, "the CPU path holds all experts in one process"
         xr = x.detach().clone().requires_grad_(True)
-        leaves = [self.gate, self.w13, self.w2]
-        for t in leaves:
-            t.requires_grad_(True)
-        y = self.dense_reference(xr, residual=residual)
-        return y.to(x.dtype).detach(), (xr, y)
+        # leaves that share storage with the current weights; the context keeps them, so the backward pass still
+        # differentiates this call's weights after set_weights pointed the layer somewhere else
+        gate, w13, w2 = (t.detach().requires_grad_(True) for t in (self.gate, self.w13, self.w2))
+        y = self.dense_reference(xr, w13, w2, residual=residual, gate=gate)
+        probs = torch.softmax(xr.float() @ gate.float().t(), -1)
+        idx = probs.topk(self.k, -1).indices
+        frac = torch.bincount(idx.flatten(), minlength=self.E).float() / idx.numel()
+        aux = self.E * (frac * probs.mean(0)).sum()
+        return y.to(x.dtype).detach(), (xr, y, aux, (gate, w13, w2))
 
     def _backward_ref(self, ctx, dy):
-        xr, y = ctx
-        gx, gg, g13, g2 = torch.autograd.grad(y, [xr, self.gate, self.w13, self.w2], dy.float())
-        self.grads["gate"] += gg.to(self.gate.dtype)
-        self.grads["w13"] += g13.to(self.w13.dtype)
-        self.grads["w2"] += g2.to(self.w2.dtype)
-        for t in (self.gate, self.w13, self.w2):
-            t.requires_grad_(False)
+        xr, y, aux, leaves = ctx
+        total = (y * dy.float()).sum() + self.aux_coef * aux
+        gx, gg, g13, g2 = torch.autograd.grad(total, [xr, *leaves])
+        self.grads["gate"] += gg.to(self.grads["gate"].dtype)
+        self.grads["w13"] += g13.to(self.grads["w13"].dtype)
+        self.grads["w2"] += g2.to(self.grads["w2"].dtype)
         return gx.to(dy.dtype)
 
     # ------------------------------------------------------------------ autograd wrapper

@@ -145,8 +145,7 @@ class Zero3LlamaEngine:
         d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
         hd = cfg.head_dim
         self.qkv_out = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * hd
-        layer_specs = [("attn_norm", (d,)), ("wqkv", (self.qkv_out, d)), ("wo", (d, cfg.num_attention_heads * hd)),
-                       ("ffn_norm", (d,)), ("w_gate_up", (2 * f, d)), ("w_down", (d, f))]
+        layer_specs = self._layer_specs()
         mk = lambda name, specs, idx: _Unit(name, specs, self.world, self.rank, self.device, dtype, index=idx)
         self.embed = mk("embed", [("tok_emb", (v, d))], 0)
         self.layers = [mk(f"layer{i}", layer_specs, i + 1) for i in range(cfg.num_hidden_layers)]
@@ -190,6 +189,13 @@ class Zero3LlamaEngine:
         # kernel status word of the previous steps, copied to pinned memory without stalling the stream
         self._status_host = None
         self._status_event = None
+
+    def _layer_specs(self):
+        """Named tensors of one decoder layer's flat unit (subclasses with another MLP override this)."""
+        c = self.cfg
+        d, f, hd = c.hidden_size, c.intermediate_size, c.head_dim
+        return [("attn_norm", (d,)), ("wqkv", (self.qkv_out, d)), ("wo", (d, c.num_attention_heads * hd)),
+                ("ffn_norm", (d,)), ("w_gate_up", (2 * f, d)), ("w_down", (d, f))]
 
     # ------------------------------------------------------------------ init
     def _init_params(self, seed):
@@ -347,7 +353,8 @@ class Zero3LlamaEngine:
             self._rope = rope_tables(S, self.cfg.head_dim, self.cfg.rope_theta, self.device)
         return self._rope
 
-    def _layer_fwd(self, w, x, B, S):
+    def _attn_fwd(self, w, x, B, S):
+        """x -> x + attention(rmsnorm(x)); returns (x2, saved)."""
         c = self.cfg
         Hq, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         cos, sin = self._rope_tables(S)
@@ -358,29 +365,16 @@ class Zero3LlamaEngine:
         q, k, v = qkv[:, :Hq * hd], qkv[:, Hq * hd:(Hq + Hkv) * hd], qkv[:, (Hq + Hkv) * hd:]
         attn, lse = K.attn_fwd(q, k, v, B, S, Hq, Hkv, hd, causal=True)
         x2 = K.gemm(attn, False, w["wo"], True, residual=x)
-        h2, rstd2, _ = K.rmsnorm_fwd(x2, w["ffn_norm"], c.rms_norm_eps)
-        gu = K.gemm(h2, False, w["w_gate_up"], True)
-        act = K.swiglu_fwd(gu)
-        out = K.gemm(act, False, w["w_down"], True, residual=x2)
-        saved = (x, rstd1, h1, qkv, attn, lse, x2, rstd2, h2, gu, act)
-        return out, saved
+        return x2, (x, rstd1, h1, qkv, attn, lse)
 
-    def _layer_bwd(self, w, g, saved, dout, B, S):
+    def _attn_bwd(self, w, g, saved, dx2, B, S):
+        """Backward of :meth:`_attn_fwd`: ``dx2`` is the gradient of its output (residual branch included);
+        writes the weight gradients into ``g`` and returns the gradient of its input."""
         c = self.cfg
         Hq, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         cos, sin = self._rope_tables(S)
-        x, rstd1, h1, qkv, attn, lse, x2, rstd2, h2, gu, act = saved
+        x, rstd1, h1, qkv, attn, lse = saved
         T = x.shape[0]
-        # MLP
-        dact = K.gemm(dout, False, w["w_down"], False)
-        K.gemm(dout, True, act, False, out=g["w_down"])
-        dgu = K.swiglu_bwd(gu, dact)
-        del dact
-        dh2 = K.gemm(dgu, False, w["w_gate_up"], False)
-        K.gemm(dgu, True, h2, False, out=g["w_gate_up"])
-        del dgu
-        dx2, _ = K.rmsnorm_bwd(x2, w["ffn_norm"], dh2, rstd2, dres=dout, dw_out=g["ffn_norm"])
-        # attention
         dattn = K.gemm(dx2, False, w["wo"], False)
         K.gemm(dx2, True, attn, False, out=g["wo"])
         dqkv = torch.empty_like(qkv)
@@ -392,6 +386,28 @@ class Zero3LlamaEngine:
         K.gemm(dqkv, True, h1, False, out=g["wqkv"])
         dx, _ = K.rmsnorm_bwd(x, w["attn_norm"], dh1, rstd1, dres=dx2, dw_out=g["attn_norm"])
         return dx
+
+    def _layer_fwd(self, w, x, B, S, layer_index: int = 0):
+        c = self.cfg
+        x2, sa = self._attn_fwd(w, x, B, S)
+        h2, rstd2, _ = K.rmsnorm_fwd(x2, w["ffn_norm"], c.rms_norm_eps)
+        gu = K.gemm(h2, False, w["w_gate_up"], True)
+        act = K.swiglu_fwd(gu)
+        out = K.gemm(act, False, w["w_down"], True, residual=x2)
+        return out, (sa, x2, rstd2, h2, gu, act)
+
+    def _layer_bwd(self, w, g, saved, dout, B, S, layer_index: int = 0):
+        sa, x2, rstd2, h2, gu, act = saved
+        # MLP
+        dact = K.gemm(dout, False, w["w_down"], False)
+        K.gemm(dout, True, act, False, out=g["w_down"])
+        dgu = K.swiglu_bwd(gu, dact)
+        del dact
+        dh2 = K.gemm(dgu, False, w["w_gate_up"], False)
+        K.gemm(dgu, True, h2, False, out=g["w_gate_up"])
+        del dgu
+        dx2, _ = K.rmsnorm_bwd(x2, w["ffn_norm"], dh2, rstd2, dres=dout, dw_out=g["ffn_norm"])
+        return self._attn_bwd(w, g, sa, dx2, B, S)
 
     # ------------------------------------------------------------------ one training step
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -426,7 +442,7 @@ class Zero3LlamaEngine:
             nxt = (self._gather_async(self.layers[i + 1], layer_buf(i + 1)) if i + 1 < L
                    else self._gather_async(self.head, head_buf))
             self._wait(ev)
-            x, sv = self._layer_fwd(unit.views(w_full), x, B, S)
+            x, sv = self._layer_fwd(unit.views(w_full), x, B, S, i)
             saved.append(sv)
         head_full, ev = nxt
         self._wait(ev)
@@ -458,7 +474,7 @@ class Zero3LlamaEngine:
             self._wait(ev)
             self._acquire_grad_slot(gslot, grad_free[gslot])
             g = unit.views(self.gfull[gslot][:unit.padded])
-            dx = self._layer_bwd(unit.views(w_full), g, saved.pop(), dx, B, S)
+            dx = self._layer_bwd(unit.views(w_full), g, saved.pop(), dx, B, S, i)
             grad_free[gslot] = self._reduce_and_update(unit, gslot)
         # embedding gradient: scatter-add of dx rows
         gslot = 1 - gslot
@@ -533,7 +549,7 @@ class Zero3LlamaEngine:
         for unit in self.layers:
             w_full, ev = self._gather_async(unit, slot)
             self._wait(ev)
-            x, _ = self._layer_fwd(unit.views(w_full), x, B, S)
+            x, _ = self._layer_fwd(unit.views(w_full), x, B, S, self.layers.index(unit))
             slot = 1 - slot
         head_full, ev = self._gather_async(self.head, slot)
         self._wait(ev)
