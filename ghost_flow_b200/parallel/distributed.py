@@ -624,39 +624,58 @@ class PipelineParallel:
     def is_last(self):
         return self.stage_index == self.num_stages - 1
 
-    def _recv(self, src, rows):
-        t = torch.empty(self.activation_shape(rows), dtype=self.dtype, device=self.device)
-        dist.recv(t, src, group=self.group)
-        return t
-
-    def _send(self, t, dst):
-        """Non-blocking: in 1F1B a stage sends an activation forward while its neighbour sends a gradient back, so
-        two blocking sends would wait for each other. The tensor is kept alive until the transfer is done."""
-        self._sends.append((dist.isend(t, dst, group=self.group), t))
-
-    def _forward_one(self, i, micro_inputs, rows, saved):
-        if self.is_first:
-            x = micro_inputs[i]
-            inp = None
+    # -- point-to-point plumbing ------------------------------------------------------------------------------
+    # Every exchange with a neighbour goes out as ONE batch of sends and receives. On NCCL the operations of a batch
+    # run as one grouped kernel, so "send the activation forward, receive a gradient back" cannot deadlock against the
+    # neighbour's mirrored pair the way two ordered blocking kernels on one stream would for messages larger than
+    # NCCL's staging buffers. A batch that only sends is not waited for until the end of the step (the tensor is kept
+    # alive), so the transfer overlaps the next micro-batch's compute; a batch that receives is waited for right
+    # where its tensor is needed.
+    def _exchange(self, send_fwd=None, send_bwd=None, recv_fwd=False, recv_bwd=False, rows=0):
+        ops, got_f, got_b = [], None, None
+        r = self.stage_index
+        rank_of = (lambda i: dist.get_global_rank(self.group, i)) if self.group is not None else (lambda i: i)
+        if send_fwd is not None:
+            ops.append(dist.P2POp(dist.isend, send_fwd, rank_of(r + 1), self.group))
+        if send_bwd is not None:
+            ops.append(dist.P2POp(dist.isend, send_bwd, rank_of(r - 1), self.group))
+        if recv_fwd:
+            got_f = torch.empty(self.activation_shape(rows), dtype=self.dtype, device=self.device)
+            ops.append(dist.P2POp(dist.irecv, got_f, rank_of(r - 1), self.group))
+        if recv_bwd:
+            got_b = torch.empty(self.activation_shape(rows), dtype=self.dtype, device=self.device)
+            ops.append(dist.P2POp(dist.irecv, got_b, rank_of(r + 1), self.group))
+        if not ops:
+            return None, None
+        works = dist.batch_isend_irecv(ops)
+        if recv_fwd or recv_bwd:
+            for w in works:
+                w.wait()
+            self.p2p_batches_waited += 1
         else:
-            inp = self._recv(self.stage_index - 1, rows).requires_grad_(True)
+            self._sends.append((works, send_fwd, send_bwd))
+        self.p2p_batches += 1
+        return got_f, got_b
+
+    def _forward(self, x_in, i, micro_inputs, saved):
+        if self.is_first:
+            inp, x = None, micro_inputs[i]
+        else:
+            inp = x_in.requires_grad_(True)
             x = inp
         out = self.stage(x)
         saved.append((inp, out))
-        if not self.is_last:
-            self._send(out.detach().contiguous(), self.stage_index + 1)
+        return None if self.is_last else out.detach().contiguous()
 
-    def _backward_one(self, saved, loss_fn, targets, losses, j, rows):
+    def _backward(self, g_in, saved, loss_fn, targets, losses, j):
         inp, out = saved.pop(0)
         if self.is_last:
             loss = loss_fn(out, targets[j]) / self.num_micro_batches
             losses.append(loss.detach() * self.num_micro_batches)
             loss.backward()
         else:
-            g = self._recv(self.stage_index + 1, rows)
-            out.backward(g)
-        if not self.is_first:
-            self._send(inp.grad.contiguous(), self.stage_index - 1)
+            out.backward(g_in)
+        return None if self.is_first else inp.grad.contiguous()
 
     def run(self, micro_inputs=None, loss_fn=None, targets=None, rows: int | None = None):
         m, s, r = self.num_micro_batches, self.num_stages, self.stage_index
@@ -664,6 +683,7 @@ class PipelineParallel:
             rows = micro_inputs[0].shape[0]
         saved, losses = [], []
         self._sends = []
+        self.p2p_batches = self.p2p_batches_waited = 0
         if s == 1:
             for i in range(m):
                 out = self.stage(micro_inputs[i])
@@ -671,20 +691,34 @@ class PipelineParallel:
                 loss.backward()
                 losses.append(loss.detach() * m)
             return torch.stack(losses).mean()
+        first, last = self.is_first, self.is_last
         warm = min(m, s - 1 - r)
+        steady = m - warm
         f = b = 0
-        for _ in range(warm):                 # warm-up forwards
-            self._forward_one(f, micro_inputs, rows, saved)
+        # warm-up forwards: receive, compute, send on
+        for _ in range(warm):
+            x, _ = self._exchange(recv_fwd=not first, rows=rows)
+            act = self._forward(x, f, micro_inputs, saved)
             f += 1
-        while f < m:                          # steady state: one forward, one backward
-            self._forward_one(f, micro_inputs, rows, saved)
+            self._exchange(send_fwd=act)
+        x = self._exchange(recv_fwd=not first, rows=rows)[0] if steady else None
+        # steady state: forward, (send activation | receive gradient), backward, (send gradient | receive activation)
+        for k in range(steady):
+            act = self._forward(x, f, micro_inputs, saved)
             f += 1
-            self._backward_one(saved, loss_fn, targets, losses, b, rows)
+            _, g = self._exchange(send_fwd=act, recv_bwd=not last, rows=rows)
+            dx = self._backward(g, saved, loss_fn, targets, losses, b)
             b += 1
-        while b < m:                          # cool-down backwards
-            self._backward_one(saved, loss_fn, targets, losses, b, rows)
+            more = k + 1 < steady
+            x, _ = self._exchange(send_bwd=dx, recv_fwd=more and not first, rows=rows)
+        # cool-down backwards
+        for _ in range(warm):
+            _, g = self._exchange(recv_bwd=not last, rows=rows)
+            dx = self._backward(g, saved, loss_fn, targets, losses, b)
             b += 1
-        for w, _ in self._sends:
-            w.wait()
+            self._exchange(send_bwd=dx)
+        for works, *_ in self._sends:
+            for w in works:
+                w.wait()
         self._sends = []
         return torch.stack(losses).mean() if self.is_last else None

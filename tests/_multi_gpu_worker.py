@@ -56,7 +56,7 @@ def main():
     w = eng.gather_unit(eng.layers[2], master=True)["w_gate_up"].cpu()
     if rank == 0:
         torch.save({"losses": losses, "w": w, "fused": bool(getattr(comm, "fused", False)),
-                    "stats": dict(eng.last_stats)}, out)
+                    "stats": dict(eng.last_stats), "multimem": bool(getattr(comm, "arena_mc", 0))}, out)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -41,8 +41,9 @@ def test_zero_stages_match_adamw(tmp_path):
         assert d["zero3_savings"] > d["zero2_savings"] > d["zero1_savings"] > 1.0
 
 
-def test_pipeline_1f1b_matches_single_process(tmp_path):
-    r, res = _run("pipeline", tmp_path)
+@pytest.mark.parametrize("world", [2, 3])
+def test_pipeline_1f1b_matches_single_process(tmp_path, world):
+    r, res = _run("pipeline", tmp_path, world=world)
     assert r.returncode == 0, r.stderr[-2000:]
     assert all(d["pp_grad_err"] < 1e-6 for d in res)
     assert any("pp_loss_err" in d and d["pp_loss_err"] < 1e-6 for d in res)

@@ -16,8 +16,8 @@ def _need(n):
         pytest.skip(f"needs {n} GPUs")
 
 
-def _run(kind, out, n, steps=4, port=29741):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+def _run(kind, out, n, steps=4, port=29741, **extra_env):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", **extra_env)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                         "--master-addr", "127.0.0.1", "--master-port", str(port),
                         os.path.join(HERE, "_multi_gpu_worker.py"), kind, out, str(steps)],
@@ -191,3 +191,33 @@ def test_mixtral_expert_parallel_engine_matches_cpu_fp32(tmp_path, world):
         assert rel < 2e-2, (name, rel)
     wq = ref.gather_unit(ref.layers[1], master=True)["wqkv"]
     assert ((got["wqkv"] - wq).norm() / wq.norm()).item() < 2e-2
+
+
+def test_pipeline_1f1b_over_nccl_matches_whole_model(tmp_path):
+    """Two stages on two GPUs, four micro-batches, activations and their gradients over NCCL send/recv (each exchange
+    with a neighbour is one grouped batch): loss and every stage's gradients against the whole model on one GPU."""
+    _need(2)
+    out = str(tmp_path / "pp.pt")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29773",
+                        os.path.join(HERE, "_pp_worker.py"), out], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    res = [torch.load(f"{out}.{i}") for i in range(2)]
+    for d in res:
+        assert d["n_grads"] > 0 and d["grad_rel"] < 2e-2, res
+    assert res[1]["loss_err"] < 1e-2, res
+
+
+def test_in_switch_reduction_variant_of_the_fused_reducer_matches_peer_loads(tmp_path):
+    """``GF_MULTIMEM=1``: the reducer reads the gradient with ``multimem.ld_reduce`` (one load, summed inside the
+    NVSwitch) instead of one load per peer. Same job as the default path, same losses and weights."""
+    _need(2)
+    plain = _run("fused", str(tmp_path / "p.pt"), 2, port=29775)
+    mm = _run("fused", str(tmp_path / "m.pt"), 2, port=29777, GF_MULTIMEM="1")
+    if not mm["multimem"]:
+        pytest.skip("no multicast mapping on this system")
+    assert mm["fused"] and not plain["multimem"]
+    for a, b in zip(plain["losses"], mm["losses"]):
+        assert abs(a - b) < 1e-2, (plain["losses"], mm["losses"])
+    assert (plain["w"] - mm["w"]).norm() / plain["w"].norm() < 1e-2
