@@ -53,7 +53,7 @@ def main():
         cfg = MixtralConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_attention_heads=4,
                             num_key_value_heads=2, max_position_embeddings=max(512, a.seq))
     cfg.num_hidden_layers = a.layers
-    comm = FusedComm() if world > 1 else Comm()
+    comm = FusedComm(dev) if world > 1 else Comm()
     T = a.micro_batch * a.seq
     eng = MixtralEngine(cfg, dev, tokens_per_rank=T, optim=OptimConfig(lr=1e-4, weight_decay=0.1), comm=comm, seed=0,
                         capacity_factor=a.capacity_factor)

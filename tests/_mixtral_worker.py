@@ -34,8 +34,8 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     cfg = config()
-    comm = FusedComm() if (kind == "fused" and world > 1) else Comm()
-    eng = MixtralEngine(cfg, dev, tokens_per_rank=2 * 256, optim=OptimConfig(lr=2e-3, weight_decay=0.0), comm=comm,
+    comm = FusedComm(dev) if (kind == "fused" and world > 1) else Comm()
+    eng = MixtralEngine(cfg, dev, tokens_per_rank=2 * 256, optim=OptimConfig(lr=5e-4, weight_decay=0.0), comm=comm,
                         seed=5, capacity_factor=float(world))
     tok = batch(world)[2 * rank:2 * rank + 2].to(dev)
     init = {k: v.cpu() for k, v in eng.state_dict(master=True).items() if ".moe." not in k}

@@ -178,17 +178,22 @@ def test_mixtral_expert_parallel_engine_matches_cpu_fp32(tmp_path, world):
     assert got["fused"] == (world > 1)
     cfg = mw.config()
     tok = mw.batch(world)
-    ref = MixtralEngine(cfg, "cpu", tokens_per_rank=tok.shape[0] * 256, optim=OptimConfig(lr=2e-3, weight_decay=0.0),
+    # a small learning rate: the first Adam steps move every weight by lr whatever its gradient's size, so elements
+    # whose bf16 gradient has the other sign than the fp32 one separate the two runs in proportion to lr
+    ref = MixtralEngine(cfg, "cpu", tokens_per_rank=tok.shape[0] * 256, optim=OptimConfig(lr=5e-4, weight_decay=0.0),
                         dtype=torch.float32, seed=5)
     ref.load_full_state(got["init"])     # the dense weights are drawn on the device; the experts on the host
     want = [float(ref.step(tok[:, :-1], tok[:, 1:])) for _ in range(4)]
     assert want[-1] < want[0]
+    assert abs(got["losses"][0] - want[0]) < 5e-3 and abs(got["losses"][1] - want[1]) < 1e-2, (got["losses"], want)
     for a, b in zip(got["losses"], want):
         assert abs(a - b) < 3e-2, (got["losses"], want)
     e = ref.experts[1]
     for name, w in (("w13_e0", e.master["w13"][0]), ("w2_e0", e.master["w2"][0]), ("gate", e.master["gate"])):
         rel = ((got[name] - w).norm() / w.norm()).item()
-        assert rel < 2e-2, (name, rel)
+        # the router sees the smallest gradients, and at world > 1 its load-balancing term uses each rank's own token
+        # fractions where the one-rank run uses the whole batch's
+        assert rel < (5e-2 if name == "gate" else 2e-2), (name, rel)
     wq = ref.gather_unit(ref.layers[1], master=True)["wqkv"]
     assert ((got["wqkv"] - wq).norm() / wq.norm()).item() < 2e-2
 
