@@ -38,6 +38,9 @@ def main():
     ap.add_argument("--stage", type=int, default=2)
     ap.add_argument("--comm", default="nccl", choices=["nccl", "fused"],
                     help="fused: gradient reduce-scatter + AdamW in one peer-memory kernel, pull all-gather")
+    ap.add_argument("--graph", action="store_true",
+                    help="record zero_grad + forward + backward + optimizer step once in a CUDA graph and replay it")
+    ap.add_argument("--no-overlap", action="store_true", help="run the collectives after backward, not from hooks")
     a = ap.parse_args()
     cuda = torch.cuda.is_available()
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -56,7 +59,8 @@ def main():
     model = model.to(dev, torch.bfloat16 if cuda else torch.float32)
     opt = ZeRoOptimizer(model.parameters(), ZeRoConfig(stage=ZeRoStage(a.stage), world_size=world, rank=rank, lr=3e-4,
                                                        betas=(0.9, 0.95), weight_decay=0.1, bucket_size=50_000_000),
-                        comm=a.comm if (cuda and world > 1) else "nccl")
+                        comm=a.comm if (cuda and world > 1) else "nccl", overlap=False if a.no_overlap else None,
+                        capturable=a.graph)
     mb = a.global_batch // world
     g = torch.Generator().manual_seed(1 + rank)
 
@@ -64,14 +68,21 @@ def main():
         ids = torch.randint(0, cfg.vocab_size, (mb, a.seq + 1), generator=g)
         return ids[:, :-1].to(dev), ids[:, 1:].to(dev)
 
-    def step():
-        x, y = batch()
+    def train(x, y):
         opt.zero_grad()
         out = model(x, labels=y)
         loss = out[0] if isinstance(out, tuple) else out
         loss.backward()
         opt.step()
-        return loss
+        return loss.detach()
+
+    if a.graph:
+        from ghost_flow_b200.utils import GraphedStep
+
+        train = GraphedStep(train, batch(), warmup=3)
+
+    def step():
+        return train(*batch())
 
     for _ in range(a.warmup):
         loss = step()
@@ -100,7 +111,8 @@ def main():
     if rank == 0:
         n_params = sum(p.numel() for p in model.parameters())
         print(json.dumps({"metric": "GPT-2 ZeRO-%d train tokens/s" % a.stage, "model": a.model, "params": n_params, "n_gpus": world,
-                          "global_batch": a.global_batch, "seq_len": a.seq, "comm": a.comm if world > 1 else "none", "ms_per_step": round(float(t), 3),
+                          "global_batch": a.global_batch, "seq_len": a.seq, "comm": a.comm if world > 1 else "none", "cuda_graph": bool(a.graph),
+                          "overlap": bool(opt.overlap), "ms_per_step": round(float(t), 3),
                           "value": round(a.global_batch * a.seq / float(t) * 1e3), "unit": "tokens/s",
                           "loss": round(float(loss), 4), "dtype": "bf16" if cuda else "fp32",
                           "memory_savings_ratio": round(opt.memory_savings_ratio(), 2),

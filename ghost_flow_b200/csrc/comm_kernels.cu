@@ -54,8 +54,12 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int value, uint32_
 
 // ------------------------------------------------------------------ flags
 // Thread r writes `value` into rank r's pad at index idx_base + my_rank.
-__global__ void signal_peers_kernel(PeerFlagPtrs pads, int idx_base, int my_rank, int world, int value) {
+// `epoch` (may be null) points to a device counter whose value is added to the flag value: launches recorded
+// once in a CUDA graph then publish / expect a new value on every replay.
+__global__ void signal_peers_kernel(PeerFlagPtrs pads, int idx_base, int my_rank, int world, int value,
+                                    const int* epoch) {
   const int r = threadIdx.x;
+  if (epoch) value += *epoch;
   if (r < world) {
     __threadfence_system();
     st_release_sys(pads.p[r] + idx_base + my_rank, value);
@@ -64,8 +68,9 @@ __global__ void signal_peers_kernel(PeerFlagPtrs pads, int idx_base, int my_rank
 
 // Thread r waits for local_pad[idx_base + r] >= value.
 __global__ void wait_flags_kernel(const int* local_pad, int idx_base, int world, int value, uint32_t limit,
-                                  int* status) {
+                                  int* status, const int* epoch) {
   const int r = threadIdx.x;
+  if (epoch) value += *epoch;
   if (r < world) {
     if (!wait_flag_ge(local_pad + idx_base + r, value, limit) && status) atomicCAS(status, 0, GF_ERR_WAIT_PEER);
   }
@@ -100,6 +105,10 @@ struct RsAdamArgs {
   // and weights are left alone and no version flag is published
   float* grad_out;
   float* sumsq;
+  // optional device counter (graph replays): added to ready_val / consumed_val / version_val, and, when
+  // step_from_epoch is set, the bias corrections are computed from it (Adam step = *epoch)
+  const int* epoch;
+  int step_from_epoch;
 };
 
 // Register budget: at most 64 per thread (4 CTAs of 256 threads per SM) and one CTA per SM in the launch, so
@@ -111,9 +120,16 @@ rs_adamw_kernel(const RsAdamArgs a) {
   __shared__ int s_ok;
   __shared__ float s_sq[8];
   float sq = 0.f;
+  const int ep = a.epoch ? *a.epoch : 0;
+  float bc1 = a.bc1, bc2 = a.bc2;
+  if (a.step_from_epoch) {
+    bc1 = 1.f - powf(a.beta1, (float)ep);
+    bc2 = 1.f - powf(a.beta2, (float)ep);
+  }
   if (threadIdx.x < 32) {
     bool ok = true;
-    if (threadIdx.x < a.world) ok = wait_flag_ge(a.local_pad + a.ready_idx + threadIdx.x, a.ready_val, a.wait_limit);
+    if (threadIdx.x < a.world)
+      ok = wait_flag_ge(a.local_pad + a.ready_idx + threadIdx.x, a.ready_val + ep, a.wait_limit);
     ok = __all_sync(0xffffffffu, ok);
     if (threadIdx.x == 0) {
       s_ok = ok ? 1 : 0;
@@ -187,7 +203,7 @@ rs_adamw_kernel(const RsAdamArgs a) {
         const float gj = g[j] * a.grad_scale;
         mv[j] = a.beta1 * mv[j] + (1.f - a.beta1) * gj;
         vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
-        const float mh = mv[j] / a.bc1, vh = vv[j] / a.bc2;
+        const float mh = mv[j] / bc1, vh = vv[j] / bc2;
         pv[j] = pv[j] * (1.f - a.lr * a.wd) - a.lr * mh / (sqrtf(vh) + a.eps);
       }
       reinterpret_cast<float4*>(a.master)[i * 2] = *reinterpret_cast<float4*>(pv);
@@ -226,8 +242,8 @@ rs_adamw_kernel(const RsAdamArgs a) {
   __syncthreads();
   if (s_ok && threadIdx.x < a.world) {
     __threadfence_system();
-    st_release_sys(a.pads.p[threadIdx.x] + a.consumed_idx + a.my_rank, a.consumed_val);
-    if (a.version_idx >= 0) st_release_sys(a.pads.p[threadIdx.x] + a.version_idx + a.my_rank, a.version_val);
+    st_release_sys(a.pads.p[threadIdx.x] + a.consumed_idx + a.my_rank, a.consumed_val + ep);
+    if (a.version_idx >= 0) st_release_sys(a.pads.p[threadIdx.x] + a.version_idx + a.my_rank, a.version_val + ep);
     if (threadIdx.x == 0) *a.done_counter = 0;
   }
 }
@@ -247,6 +263,7 @@ struct AgArgs {
   int blocks_per_shard;
   uint32_t wait_limit;
   int* status;
+  const int* epoch;         // optional device counter added to version_val (graph replays)
 };
 
 // grid = world * blocks_per_shard; block b copies a slice of shard (my_rank + 1 + b / blocks_per_shard) % world,
@@ -260,7 +277,8 @@ allgather_pull_kernel(const AgArgs a) {
   if (src >= a.world) src -= a.world;
   if (threadIdx.x == 0) {
     bool ok = true;
-    if (src != a.my_rank) ok = wait_flag_ge(a.local_pad + a.version_idx + src, a.version_val, a.wait_limit);
+    if (src != a.my_rank)
+      ok = wait_flag_ge(a.local_pad + a.version_idx + src, a.version_val + (a.epoch ? *a.epoch : 0), a.wait_limit);
     s_ok = ok ? 1 : 0;
     if (!ok && a.status) atomicCAS(a.status, 0, GF_ERR_WAIT_PEER);
   }
@@ -298,6 +316,8 @@ allgather_pull_kernel(const AgArgs a) {
   }
 }
 
+__global__ void counter_add_kernel(int* p, int delta) { *p += delta; }
+
 __global__ void fill_int_kernel(int* p, int n, int v) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = v;
@@ -318,6 +338,7 @@ static void configure_comm_kernels() {
   prefer_max_smem(rs_adamw_kernel<false, true>);
   prefer_max_smem(allgather_pull_kernel);
   prefer_max_smem(fill_int_kernel);
+  prefer_max_smem(counter_add_kernel);
   done = true;
 }
 
@@ -326,25 +347,46 @@ static inline uint32_t limit_or_default(long long wait_limit) {
 }
 
 // pads: device pointers (as uint64) of every rank's signal pad, world entries.
-GF_API int gf_signal_peers(const unsigned long long* pads, int world, int my_rank, int idx_base, int value,
-                           void* stream) {
+// The *_ep variants take `epoch`, a device int (or null) whose current value is added to every flag value of the
+// launch. A training step recorded once in a CUDA graph bumps that counter with gf_counter_add at its start, so
+// every replay publishes and expects new flag values although the launch arguments are frozen.
+GF_API int gf_signal_peers_ep(const unsigned long long* pads, int world, int my_rank, int idx_base, int value,
+                              const int* epoch, void* stream) {
   gf::enter();
   configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS) return GFH_BAD_ARG;
   PeerFlagPtrs pp;
   for (int r = 0; r < MAX_RANKS; ++r) pp.p[r] = r < world ? reinterpret_cast<int*>(pads[r]) : nullptr;
-  signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pp, idx_base, my_rank, world, value);
+  signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pp, idx_base, my_rank, world, value, epoch);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_signal_peers(const unsigned long long* pads, int world, int my_rank, int idx_base, int value,
+                           void* stream) {
+  return gf_signal_peers_ep(pads, world, my_rank, idx_base, value, nullptr, stream);
+}
+
+GF_API int gf_counter_add(int* counter, int delta, void* stream) {
+  gf::enter();
+  configure_comm_kernels();
+  if (!counter) return GFH_BAD_ARG;
+  counter_add_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(counter, delta);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_wait_flags_ep(const int* local_pad, int idx_base, int world, int value, long long wait_limit,
+                            int* status, const int* epoch, void* stream) {
+  gf::enter();
+  configure_comm_kernels();
+  if (world < 1 || world > 32) return GFH_BAD_ARG;
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_pad, idx_base, world, value,
+                                                        limit_or_default(wait_limit), status, epoch);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
 
 GF_API int gf_wait_flags(const int* local_pad, int idx_base, int world, int value, long long wait_limit, int* status,
                          void* stream) {
-  gf::enter();
-  configure_comm_kernels();
-  if (world < 1 || world > 32) return GFH_BAD_ARG;
-  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_pad, idx_base, world, value,
-                                                        limit_or_default(wait_limit), status);
-  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+  return gf_wait_flags_ep(local_pad, idx_base, world, value, wait_limit, status, nullptr, stream);
 }
 
 GF_API int gf_fill_int(int* p, int n, int v, void* stream) {
@@ -355,12 +397,14 @@ GF_API int gf_fill_int(int* p, int n, int v, void* stream) {
 }
 
 // grad_ptrs / pads: world device pointers each. mc_grads: multicast pointer of the gradient buffer or 0.
-GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long long mc_grads,
-                             const unsigned long long* pads, int world, int my_rank, long long shard_lo, long long n,
-                             float* master, float* m, float* v, void* p_lp, float lr, float beta1, float beta2,
-                             float eps, float wd, int step, float grad_scale, int ready_idx, int ready_val,
-                             int consumed_idx, int consumed_val, int version_idx, int version_val, int* done_counter,
-                             int max_ctas, long long wait_limit, int* status, void* stream) {
+// With `epoch` the Adam step number is *epoch (bias corrections computed on the device) and `step` is ignored.
+GF_API int gf_rs_adamw_fused_ep(const unsigned long long* grad_ptrs, unsigned long long mc_grads,
+                                const unsigned long long* pads, int world, int my_rank, long long shard_lo, long long n,
+                                float* master, float* m, float* v, void* p_lp, float lr, float beta1, float beta2,
+                                float eps, float wd, int step, float grad_scale, int ready_idx, int ready_val,
+                                int consumed_idx, int consumed_val, int version_idx, int version_val,
+                                int* done_counter, int max_ctas, long long wait_limit, int* status, const int* epoch,
+                                void* stream) {
   gf::enter();
   configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_lo & 7)) return GFH_BAD_ARG;
@@ -380,6 +424,7 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
   a.version_idx = version_idx; a.version_val = version_val;
   a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
   a.grad_out = nullptr; a.sumsq = nullptr;
+  a.epoch = epoch; a.step_from_epoch = epoch ? 1 : 0;
   long long want = ((n >> 3) + 255) / 256;
   int grid = max_ctas > 0 ? max_ctas : sm_count();
   if (want < grid) grid = (int)(want > 0 ? want : 1);
@@ -388,6 +433,17 @@ GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long 
   else
     rs_adamw_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_rs_adamw_fused(const unsigned long long* grad_ptrs, unsigned long long mc_grads,
+                             const unsigned long long* pads, int world, int my_rank, long long shard_lo, long long n,
+                             float* master, float* m, float* v, void* p_lp, float lr, float beta1, float beta2,
+                             float eps, float wd, int step, float grad_scale, int ready_idx, int ready_val,
+                             int consumed_idx, int consumed_val, int version_idx, int version_val, int* done_counter,
+                             int max_ctas, long long wait_limit, int* status, void* stream) {
+  return gf_rs_adamw_fused_ep(grad_ptrs, mc_grads, pads, world, my_rank, shard_lo, n, master, m, v, p_lp, lr, beta1,
+                              beta2, eps, wd, step, grad_scale, ready_idx, ready_val, consumed_idx, consumed_val,
+                              version_idx, version_val, done_counter, max_ctas, wait_limit, status, nullptr, stream);
 }
 
 // Reduce-scatter alone, for steps that need the global gradient norm before they may update (clipping, overflow
@@ -416,6 +472,7 @@ GF_API int gf_rs_reduce_only(const unsigned long long* grad_ptrs, unsigned long 
   a.version_idx = -1; a.version_val = 0;
   a.done_counter = done_counter; a.wait_limit = limit_or_default(wait_limit); a.status = status;
   a.grad_out = grad_out; a.sumsq = sumsq;
+  a.epoch = nullptr; a.step_from_epoch = 0;
   long long want = ((n >> 3) + 255) / 256;
   int grid = max_ctas > 0 ? max_ctas : sm_count();
   if (want < grid) grid = (int)(want > 0 ? want : 1);
@@ -427,10 +484,10 @@ GF_API int gf_rs_reduce_only(const unsigned long long* grad_ptrs, unsigned long 
 }
 
 // shard_ptrs: every rank's shard (world pointers). ready_flags / block_counters: local int[world].
-GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, long long shard_elems, int world,
-                             int my_rank, const int* local_pad, int version_idx, int version_val, int* ready_flags,
-                             int ready_val, int* block_counters, int blocks_per_shard, long long wait_limit,
-                             int* status, void* stream) {
+GF_API int gf_allgather_pull_ep(const unsigned long long* shard_ptrs, void* full, long long shard_elems, int world,
+                                int my_rank, const int* local_pad, int version_idx, int version_val,
+                                int* ready_flags, int ready_val, int* block_counters, int blocks_per_shard,
+                                long long wait_limit, int* status, const int* epoch, void* stream) {
   gf::enter();
   configure_comm_kernels();
   if (world < 1 || world > MAX_RANKS || (shard_elems & 7) || blocks_per_shard < 1) return GFH_BAD_ARG;
@@ -440,8 +497,18 @@ GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, l
   a.local_pad = local_pad; a.version_idx = version_idx; a.version_val = version_val;
   a.ready_flags = ready_flags; a.ready_val = ready_val; a.block_counters = block_counters;
   a.blocks_per_shard = blocks_per_shard; a.wait_limit = limit_or_default(wait_limit); a.status = status;
+  a.epoch = epoch;
   allgather_pull_kernel<<<world * blocks_per_shard, 256, 0, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_allgather_pull(const unsigned long long* shard_ptrs, void* full, long long shard_elems, int world,
+                             int my_rank, const int* local_pad, int version_idx, int version_val, int* ready_flags,
+                             int ready_val, int* block_counters, int blocks_per_shard, long long wait_limit,
+                             int* status, void* stream) {
+  return gf_allgather_pull_ep(shard_ptrs, full, shard_elems, world, my_rank, local_pad, version_idx, version_val,
+                              ready_flags, ready_val, block_counters, blocks_per_shard, wait_limit, status, nullptr,
+                              stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------

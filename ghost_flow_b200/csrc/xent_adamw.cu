@@ -102,8 +102,13 @@ struct AdamArgs {
 template <typename G>
 __global__ void adam_flat_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
                                  const G* __restrict__ g, __nv_bfloat16* __restrict__ p_lp, long long n, AdamArgs a,
-                                 const int* __restrict__ skip) {
+                                 const int* __restrict__ skip, const int* __restrict__ step_dev) {
   if (skip && *skip) return;
+  if (step_dev) {   // step number kept on the device (a launch recorded in a CUDA graph is replayed with frozen arguments)
+    const float t = (float)*step_dev;
+    a.bc1 = 1.f - powf(a.beta1, t);
+    a.bc2 = 1.f - powf(a.beta2, t);
+  }
   const long long nvec = n >> 2;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -240,9 +245,10 @@ GF_API int gf_xent_fused(const void* logits, const long long* targets, float* lo
 }
 
 // grad_dtype: 0 fp32, 1 bf16. p_lp may be null. skip may be null.
-GF_API int gf_adam_flat(float* p, float* m, float* v, const void* g, void* p_lp, long long n, float lr, float beta1,
-                        float beta2, float eps, float wd, int step, float grad_scale, int decoupled, int grad_dtype,
-                        const int* skip, void* stream) {
+// step_dev (may be null): device int holding the step number; when given, `step` is ignored.
+GF_API int gf_adam_flat_dev(float* p, float* m, float* v, const void* g, void* p_lp, long long n, float lr, float beta1,
+                            float beta2, float eps, float wd, int step, float grad_scale, int decoupled,
+                            int grad_dtype, const int* skip, const int* step_dev, void* stream) {
   gf::enter();
   if (n <= 0) return GFH_OK;
   static bool configured = false;
@@ -258,11 +264,18 @@ GF_API int gf_adam_flat(float* p, float* m, float* v, const void* g, void* p_lp,
   a.decoupled = decoupled;
   if (grad_dtype == 1)
     adam_flat_kernel<__nv_bfloat16><<<flat_grid(n), 256, 0, (cudaStream_t)stream>>>(
-        p, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)p_lp, n, a, skip);
+        p, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)p_lp, n, a, skip, step_dev);
   else
-    adam_flat_kernel<float><<<flat_grid(n), 256, 0, (cudaStream_t)stream>>>(p, m, v, (const float*)g,
-                                                                           (__nv_bfloat16*)p_lp, n, a, skip);
+    adam_flat_kernel<float><<<flat_grid(n), 256, 0, (cudaStream_t)stream>>>(
+        p, m, v, (const float*)g, (__nv_bfloat16*)p_lp, n, a, skip, step_dev);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+GF_API int gf_adam_flat(float* p, float* m, float* v, const void* g, void* p_lp, long long n, float lr, float beta1,
+                        float beta2, float eps, float wd, int step, float grad_scale, int decoupled, int grad_dtype,
+                        const int* skip, void* stream) {
+  return gf_adam_flat_dev(p, m, v, g, p_lp, n, lr, beta1, beta2, eps, wd, step, grad_scale, decoupled, grad_dtype,
+                          skip, nullptr, stream);
 }
 
 GF_API int gf_sgd_flat(float* p, float* buf, const void* g, void* p_lp, long long n, float lr, float momentum,

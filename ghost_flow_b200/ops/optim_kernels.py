@@ -20,14 +20,17 @@ def _gd(g: torch.Tensor) -> int:
 
 
 def adam_flat(p, m, v, g, p_lp=None, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1,
-              grad_scale=1.0, decoupled=True, skip_flag=None):
-    """In-place Adam/AdamW on fp32 ``p, m, v`` (1-D, contiguous) with gradient ``g`` (fp32 or bf16)."""
+              grad_scale=1.0, decoupled=True, skip_flag=None, step_dev=None):
+    """In-place Adam/AdamW on fp32 ``p, m, v`` (1-D, contiguous) with gradient ``g`` (fp32 or bf16). ``step_dev``:
+    int32 device tensor holding the step number (then ``step`` is ignored and the launch can be replayed from a
+    CUDA graph)."""
     assert p.is_cuda and p.dtype == torch.float32 and p.is_contiguous()
     n = p.numel()
-    rc = _lib.cuda_lib().gf_adam_flat(
+    rc = _lib.cuda_lib().gf_adam_flat_dev(
         p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), p_lp.data_ptr() if p_lp is not None else None, n,
         float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step), float(grad_scale),
-        1 if decoupled else 0, _gd(g), skip_flag.data_ptr() if skip_flag is not None else None, _lib.stream_ptr())
+        1 if decoupled else 0, _gd(g), skip_flag.data_ptr() if skip_flag is not None else None,
+        step_dev.data_ptr() if step_dev is not None else None, _lib.stream_ptr())
     _lib.check_rc(rc, "gf_adam_flat")
 
 

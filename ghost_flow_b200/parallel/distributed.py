@@ -333,8 +333,20 @@ class ZeRoOptimizer:
     # signal-pad layout of the fused path (int32 indices, 8 per bucket, one slot per writer rank)
     _PAD_READY, _PAD_CONSUMED, _PAD_VERSION, _MAX_FUSED_BUCKETS = 1024, 2048, 3072, 128
 
-    def __init__(self, params, config: ZeRoConfig | None = None, group=None, comm: str = "nccl"):
-        """``comm="fused"`` (bf16 CUDA parameters, 2 to 8 ranks of one NVSwitch box): the gradient buckets live
+    def __init__(self, params, config: ZeRoConfig | None = None, group=None, comm: str = "nccl",
+                 overlap: bool | None = None, capturable: bool = False):
+        """``overlap`` (default: on for CUDA parameters and more than one rank): a bucket's reduce-scatter, AdamW and
+        all-gather are launched on a side stream from a gradient hook as soon as the backward pass has produced the
+        bucket's last gradient, so they run under the rest of the backward pass; ``step()`` then only launches
+        what is left and joins the side stream. With gradient accumulation over several backward passes wrap all
+        but the last in ``no_sync()``.
+
+        ``capturable``: the step number lives in a device counter that ``step()`` bumps with a one-thread kernel,
+        Adam's bias corrections and the flag values of the fused path are computed from it on the device, and
+        nothing in ``zero_grad()`` / backward hooks / ``step()`` reads device memory on the host: forward, backward
+        and ``step()`` can be recorded once in a CUDA graph and replayed (``ghost_flow_b200.utils.GraphedStep``).
+
+        ``comm="fused"`` (bf16 CUDA parameters, 2 to 8 ranks of one NVSwitch box): the gradient buckets live
         in symmetric memory and ``step()`` runs, per bucket, ONE kernel that reads this rank's slice of every
         rank's gradients over NVLink, averages it and applies AdamW to the owned shard (``gf_rs_adamw_fused``),
         then a pull all-gather of the updated bf16 shards (``gf_allgather_pull``); ranks order themselves with
@@ -348,6 +360,15 @@ class ZeRoOptimizer:
         self.params = [p for p in params if p.requires_grad]
         self.step_count = 0
         self.buckets = []
+        cuda = bool(self.params) and self.params[0].is_cuda
+        self.overlap = (cuda and self.world > 1) if overlap is None else (bool(overlap) and cuda)
+        self.capturable = bool(capturable) and cuda
+        self._sync_hooks = True
+        self._open = False
+        self._launched: set = set()
+        self._side = torch.cuda.Stream(self.params[0].device) if self.overlap else None
+        self._step_dev = (torch.zeros(1, dtype=torch.int32, device=self.params[0].device) if self.capturable
+                          else None)
         groups, cur, n = [], [], 0
         for p in self.params:
             if cur and (n + p.numel() > self.config.bucket_size or cur[0].dtype != p.dtype):
@@ -377,6 +398,90 @@ class ZeRoOptimizer:
         for g in groups:
             self._make_bucket(g)
         self._offloaded = False
+        self._pending = [len(b["params"]) for b in self.buckets]
+        if self.overlap:
+            for i, b in enumerate(self.buckets):
+                for prm in b["params"]:
+                    prm.register_post_accumulate_grad_hook(self._grad_hook(i))
+
+    # ---- overlap: gradient hooks
+    def _grad_hook(self, bucket_index: int):
+        def hook(_param):
+            if not self._sync_hooks or self._offloaded:
+                return
+            self._pending[bucket_index] -= 1
+            if self._pending[bucket_index] == 0:
+                self._launch_bucket(bucket_index)
+        return hook
+
+    def no_sync(self):
+        """Context manager: backward passes inside it only accumulate gradients (no per-bucket launches)."""
+        opt = self
+
+        class _NoSync:
+            def __enter__(self):
+                opt._sync_hooks = False
+
+            def __exit__(self, *exc):
+                opt._sync_hooks = True
+        return _NoSync()
+
+    def _begin_step(self):
+        if self._open:
+            return
+        self._open = True
+        self.step_count += 1
+        if self.capturable:
+            from ..ops import _lib
+
+            _lib.check_rc(_lib.cuda_lib().gf_counter_add(self._step_dev.data_ptr(), 1, _lib.stream_ptr()),
+                          "gf_counter_add")
+
+    def _launch_bucket(self, i: int):
+        """Everything bucket ``i`` needs after its gradients are complete, on the side stream when overlapping."""
+        self._begin_step()
+        if self._side is not None:
+            self._side.wait_event(torch.cuda.current_stream().record_event())
+            with torch.cuda.stream(self._side):
+                self._bucket_work(i)
+        else:
+            self._bucket_work(i)
+        self._launched.add(i)
+
+    def _bucket_work(self, i: int):
+        if self._fc is not None:
+            self._bucket_fused(i)
+            return
+        c, b = self.config, self.buckets[i]
+        lo = self.rank * b["shard"]
+        # reduce-scatter of the flat gradient
+        if self.world == 1:
+            g_shard = b["flat_g"][:b["shard"]]
+        elif dist.get_backend(self.group) == "nccl":
+            dist.reduce_scatter_tensor(b["g_shard"], b["flat_g"], group=self.group)
+            g_shard = b["g_shard"]
+        else:
+            tmp = b["flat_g"].float()
+            dist.all_reduce(tmp, group=self.group)
+            b["g_shard"].copy_(tmp[lo:lo + b["shard"]].to(b["g_shard"].dtype))
+            g_shard = b["g_shard"]
+        p_lp = b["flat_p"][lo:lo + b["shard"]]
+        kw = dict(lr=c.lr, beta1=c.betas[0], beta2=c.betas[1], eps=c.eps, weight_decay=c.weight_decay,
+                  step=self.step_count, grad_scale=1.0 / self.world)
+        lp_out = p_lp if p_lp.dtype != torch.float32 else None
+        if self.capturable:
+            from ..ops.optim_kernels import adam_flat
+
+            adam_flat(b["master"], b["m"], b["v"], g_shard, lp_out, step_dev=self._step_dev, **kw)
+        else:
+            raw.adamw_flat(b["master"], b["m"], b["v"], g_shard, lp_out, **kw)
+        if lp_out is None:
+            p_lp.copy_(b["master"])
+        if self.world > 1:
+            if dist.get_backend(self.group) == "nccl":
+                dist.all_gather_into_tensor(b["flat_p"], p_lp, group=self.group)   # in place: p_lp is slice `rank`
+            else:
+                dist.all_gather_into_tensor(b["flat_p"], p_lp.clone(), group=self.group)
 
     def _padded(self, n: int) -> int:
         return (n + self.world * 8 - 1) // (self.world * 8) * (self.world * 8)
@@ -444,62 +549,71 @@ class ZeRoOptimizer:
         that parameter views stay usable; a rank must not read foreign slices until the next gather)."""
 
     # ---- step
-    def _step_fused(self):
-        """Per bucket: tell the peers that my gradients are complete; one kernel = wait for everybody's gradients,
-        sum my slice over peer memory, AdamW on my shard; pull every rank's new bf16 shard into the parameter
-        buffer; wait until the peers have read my gradients, so that the next backward may overwrite them."""
+    def _bucket_fused(self, i: int):
+        """Tell the peers that my gradients of bucket ``i`` are complete; one kernel = wait for everybody's
+        gradients, sum my slice over peer memory, AdamW on my shard; pull every rank's new bf16 shard into the
+        parameter buffer."""
         from ..ops import _lib
 
-        c, fc = self.config, self._fc
-        self.step_count += 1
-        t, W, R = self.step_count, self.world, self.rank
+        c, fc, b = self.config, self._fc, self.buckets[i]
+        W, R = self.world, self.rank
+        # flag values: the step number; in capturable mode the launch carries 0 and the device counter adds it
+        ep = self._step_dev.data_ptr() if self.capturable else None
+        t = 0 if self.capturable else self.step_count
         status, stream = _lib.status_word(fc.device).data_ptr(), _lib.stream_ptr()
         # waits give up after about 2 s; the first step gets about 13 s, since ranks reach it with start-up skew
-        limit = (1 << 27) if t == 1 else 0
+        limit = (1 << 27) if self.step_count == 1 else 0
+        with torch.cuda.device(fc.device):
+            _lib.check_rc(fc.lib.gf_signal_peers_ep(fc.pad_ptrs, W, R, self._PAD_READY + 8 * i, t, ep, stream),
+                          "gf_signal_peers")
+            rc = fc.lib.gf_rs_adamw_fused_ep(
+                fc.peer_ptrs(b["flat_g"]), fc.mc_ptr(b["flat_g"]), fc.pad_ptrs, W, R, R * b["shard"], b["shard"],
+                b["master"].data_ptr(), b["m"].data_ptr(), b["v"].data_ptr(), b["shard_lp"].data_ptr(),
+                float(c.lr), float(c.betas[0]), float(c.betas[1]), float(c.eps), float(c.weight_decay),
+                self.step_count, 1.0 / W, self._PAD_READY + 8 * i, t, self._PAD_CONSUMED + 8 * i, t,
+                self._PAD_VERSION + 8 * i, t, fc.rs_counter.data_ptr(), 0, limit, status, ep, stream)
+            _lib.check_rc(rc, "gf_rs_adamw_fused")
+            fc.ag_epoch += 1
+            rc = fc.lib.gf_allgather_pull_ep(
+                fc.peer_ptrs(b["shard_lp"]), b["flat_p"].data_ptr(), b["shard"], W, R, fc.pad.data_ptr(),
+                self._PAD_VERSION + 8 * i, t, fc.ag_ready.data_ptr(), fc.ag_epoch, fc.ag_counters.data_ptr(),
+                max(8, 256 // W), limit, status, ep, stream)
+            _lib.check_rc(rc, "gf_allgather_pull")
+
+    def _finish_fused(self):
+        """Wait until the peers have read my gradients, so that the next backward pass may overwrite them."""
+        from ..ops import _lib
+
+        fc = self._fc
+        ep = self._step_dev.data_ptr() if self.capturable else None
+        t = 0 if self.capturable else self.step_count
+        limit = (1 << 27) if self.step_count == 1 else 0
+        status, stream = _lib.status_word(fc.device).data_ptr(), _lib.stream_ptr()
         with torch.cuda.device(fc.device):
             for i in range(len(self.buckets)):
-                _lib.check_rc(fc.lib.gf_signal_peers(fc.pad_ptrs, W, R, self._PAD_READY + 8 * i, t, stream),
-                              "gf_signal_peers")
-            for i, b in enumerate(self.buckets):
-                rc = fc.lib.gf_rs_adamw_fused(
-                    fc.peer_ptrs(b["flat_g"]), fc.mc_ptr(b["flat_g"]), fc.pad_ptrs, W, R, R * b["shard"], b["shard"],
-                    b["master"].data_ptr(), b["m"].data_ptr(), b["v"].data_ptr(), b["shard_lp"].data_ptr(),
-                    float(c.lr), float(c.betas[0]), float(c.betas[1]), float(c.eps), float(c.weight_decay), t,
-                    1.0 / W, self._PAD_READY + 8 * i, t, self._PAD_CONSUMED + 8 * i, t, self._PAD_VERSION + 8 * i, t,
-                    fc.rs_counter.data_ptr(), 0, limit, status, stream)
-                _lib.check_rc(rc, "gf_rs_adamw_fused")
-            for i, b in enumerate(self.buckets):
-                fc.ag_epoch += 1
-                rc = fc.lib.gf_allgather_pull(
-                    fc.peer_ptrs(b["shard_lp"]), b["flat_p"].data_ptr(), b["shard"], W, R, fc.pad.data_ptr(),
-                    self._PAD_VERSION + 8 * i, t, fc.ag_ready.data_ptr(), fc.ag_epoch, fc.ag_counters.data_ptr(),
-                    max(8, 256 // W), limit, status, stream)
-                _lib.check_rc(rc, "gf_allgather_pull")
-            for i in range(len(self.buckets)):
-                _lib.check_rc(fc.lib.gf_wait_flags(fc.pad.data_ptr(), self._PAD_CONSUMED + 8 * i, W, t, limit, status,
-                                                   stream), "gf_wait_flags")
+                _lib.check_rc(fc.lib.gf_wait_flags_ep(fc.pad.data_ptr(), self._PAD_CONSUMED + 8 * i, self.world, t,
+                                                      limit, status, ep, stream), "gf_wait_flags")
 
     def step(self):
+        """Launches what the gradient hooks have not launched yet (every bucket, without overlap), in bucket
+        order, and makes the current stream wait for the side stream."""
         if self._offloaded:
             self.load_from_cpu()
-        if self._fc is not None:
-            self._step_fused()
-            if self.config.cpu_offload:
-                self.offload_to_cpu()
-            return
-        c = self.config
-        self.step_count += 1
-        self.reduce_scatter_gradients()
-        for b in self.buckets:
-            lo = self.rank * b["shard"]
-            p_lp = b["flat_p"][lo:lo + b["shard"]]
-            raw.adamw_flat(b["master"], b["m"], b["v"], b["g_shard"], p_lp if p_lp.dtype != torch.float32 else None,
-                           lr=c.lr, beta1=c.betas[0], beta2=c.betas[1], eps=c.eps, weight_decay=c.weight_decay,
-                           step=self.step_count, grad_scale=1.0 / self.world)
-            if p_lp.dtype == torch.float32:
-                p_lp.copy_(b["master"])
-        self.all_gather_parameters()
-        if c.cpu_offload:
+        self._begin_step()
+        for i in range(len(self.buckets)):
+            if i not in self._launched:
+                self._launch_bucket(i)
+        if self._side is not None:
+            if self._fc is not None:
+                with torch.cuda.stream(self._side):
+                    self._finish_fused()
+            torch.cuda.current_stream().wait_event(self._side.record_event())
+        elif self._fc is not None:
+            self._finish_fused()
+        self._launched = set()
+        self._pending = [len(b["params"]) for b in self.buckets]
+        self._open = False
+        if self.config.cpu_offload:
             self.offload_to_cpu()
 
     def zero_grad(self):

@@ -93,8 +93,14 @@ class FusedComm(Comm):
                                           I, I, I, I, I, I, P, I, L, P, P]
         lib.gf_allgather_pull.argtypes = [P, P, L, I, I, P, I, I, P, I, P, I, L, P, P]
         lib.gf_rs_reduce_only.argtypes = [P, ctypes.c_ulonglong, P, I, I, L, L, P, P, F, I, I, I, I, P, I, L, P, P]
+        lib.gf_signal_peers_ep.argtypes = [P, I, I, I, I, P, P]
+        lib.gf_wait_flags_ep.argtypes = [P, I, I, I, L, P, P, P]
+        lib.gf_rs_adamw_fused_ep.argtypes = [P, ctypes.c_ulonglong, P, I, I, L, L, P, P, P, P, F, F, F, F, F, I, F,
+                                             I, I, I, I, I, I, P, I, L, P, P, P]
+        lib.gf_allgather_pull_ep.argtypes = [P, P, L, I, I, P, I, I, P, I, P, I, L, P, P, P]
         for fn in (lib.gf_signal_peers, lib.gf_wait_flags, lib.gf_rs_adamw_fused, lib.gf_allgather_pull,
-                   lib.gf_rs_reduce_only):
+                   lib.gf_rs_reduce_only, lib.gf_signal_peers_ep, lib.gf_wait_flags_ep, lib.gf_rs_adamw_fused_ep,
+                   lib.gf_allgather_pull_ep):
             fn.restype = I
 
     # ------------------------------------------------------------------ arena

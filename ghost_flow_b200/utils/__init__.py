@@ -25,6 +25,8 @@ from dataclasses import dataclass, field
 
 import torch
 
+from .graphs import GraphedStep  # noqa: F401
+
 
 # =========================================================================== profiler
 @dataclass

@@ -141,7 +141,8 @@ def test_zero2_reduce_scatter_fused_with_adamw_matches_nccl(tmp_path):
     _need(2)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")   # the NCCL arm needs no in-switch reduction
     res = {}
-    for kind, port in (("fused", 29761), ("nccl", 29763)):
+    for kind, port in (("fused", 29761), ("nccl", 29763), ("fused_late", 29779), ("fused_graph", 29781),
+                       ("nccl_graph", 29783)):
         out = str(tmp_path / f"z2_{kind}.pt")
         r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                             "--master-addr", "127.0.0.1", "--master-port", str(port),
@@ -150,8 +151,13 @@ def test_zero2_reduce_scatter_fused_with_adamw_matches_nccl(tmp_path):
         assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
         res[kind] = torch.load(out)
     assert res["fused"]["fused"] and not res["nccl"]["fused"] and res["fused"]["buckets"] >= 2
-    for a, b in zip(res["fused"]["losses"], res["nccl"]["losses"]):
-        assert abs(a - b) < 3e-2, (res["fused"]["losses"], res["nccl"]["losses"])
+    # default: launched from gradient hooks under the backward pass; _late: after it; _graph: the whole step (hooks,
+    # side stream, flag values and Adam step number from a device counter) replayed from one CUDA graph
+    assert res["fused"]["overlap"] and not res["fused_late"]["overlap"] and res["fused_graph"]["graph"]
+    for other in ("nccl", "fused_late", "fused_graph", "nccl_graph"):
+        for a, b in zip(res["fused"]["losses"], res[other]["losses"]):
+            assert abs(a - b) < 3e-2, (other, res["fused"]["losses"], res[other]["losses"])
+        assert (res["fused"]["w"] - res[other]["w"]).norm() / res["fused"]["w"].norm() < 2e-2, other
     assert res["fused"]["losses"][-1] < res["fused"]["losses"][0]
     assert (res["fused"]["w"] - res["nccl"]["w"]).norm() / res["nccl"]["w"].norm() < 2e-2
 
