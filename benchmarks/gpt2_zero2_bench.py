@@ -117,6 +117,8 @@ def main():
                           "loss": round(float(loss), 4), "dtype": "bf16" if cuda else "fp32",
                           "memory_savings_ratio": round(opt.memory_savings_ratio(), 2),
                           "data": "synthetic uniform token ids, random-init weights"}))
+    if a.graph:
+        train.release()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -321,6 +321,142 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+
+// ------------------------------------------------------------------ LayerNorm for short rows (D <= 1024)
+// With D = 768 a 256-thread CTA per row leaves 160 threads idle and pays two block-wide reductions per row. Here
+// one WARP owns a row (VPL 16-byte vectors per lane), the sums are warp shuffles, and a CTA has eight rows in
+// flight. In the backward pass every lane keeps its slice of the weight / bias gradient in registers over all its
+// rows; the eight warps of a CTA then add their slices in shared memory and the CTA writes one partial row.
+template <int VPL>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                          const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                          float* __restrict__ mean_out, float* __restrict__ rstd_out, int T, int D, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nv = D >> 3;
+  constexpr int WPC = NORM_THREADS / 32;
+  float wv[VPL][8], bv[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bv[i][j] = 0.f;
+    if (v < nv) {
+      load8(w + v * 8, wv[i]);
+      if (b) load8(b + v * 8, bv[i]);
+    }
+  }
+  for (int row = blockIdx.x * WPC + warp; row < T; row += gridDim.x * WPC) {
+    float xv[VPL][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + i * 32;
+      if (v < nv) {
+        load8(x + (long long)row * D + v * 8, xv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += xv[i][j];
+      }
+    }
+    const float mean = warp_sum(s) / (float)D;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      if (lane + i * 32 < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = xv[i][j] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / (float)D + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + i * 32;
+      if (v < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (xv[i][j] - mean) * rstd * wv[i][j] + bv[i][j];
+        store8(y + (long long)row * D + v * 8, o);
+      }
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                          const __nv_bfloat16* __restrict__ dy, const float* __restrict__ mean_in,
+                          const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                          float* __restrict__ dw_partial, float* __restrict__ db_partial, int T, int D) {
+  __shared__ float acc[2][1024];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nv = D >> 3;
+  constexpr int WPC = NORM_THREADS / 32;
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) acc[0][i] = acc[1][i] = 0.f;
+  float dwacc[VPL][8], dbacc[VPL][8], wv[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = dbacc[i][j] = 0.f;
+    if (lane + i * 32 < nv) load8(w + (lane + i * 32) * 8, wv[i]);
+  }
+  for (int row = blockIdx.x * WPC + warp; row < T; row += gridDim.x * WPC) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[VPL][8], gv[VPL][8];
+    float sg = 0.f, sgx = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + i * 32;
+      if (v < nv) {
+        load8(x + (long long)row * D + v * 8, xh[i]);
+        load8(dy + (long long)row * D + v * 8, gv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          dwacc[i][j] += gv[i][j] * xh[i][j];
+          dbacc[i][j] += gv[i][j];
+          gv[i][j] *= wv[i][j];
+          sg += gv[i][j];
+          sgx += gv[i][j] * xh[i][j];
+        }
+      }
+    }
+    sg = warp_sum(sg) / (float)D;
+    sgx = warp_sum(sgx) / (float)D;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + i * 32;
+      if (v < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gv[i][j] - sg - xh[i][j] * sgx);
+        store8(dx + (long long)row * D + v * 8, o);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * 32;
+    if (v < nv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&acc[0][v * 8 + j], dwacc[i][j]);
+        atomicAdd(&acc[1][v * 8 + j], dbacc[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) {
+    dw_partial[(long long)blockIdx.x * D + i] = acc[0][i];
+    db_partial[(long long)blockIdx.x * D + i] = acc[1][i];
+  }
+}
+
 static inline int norm_grid(int T) {
   int g = sm_count() * 4;
   return T < g ? T : g;
@@ -363,6 +499,16 @@ GF_API int gf_layernorm_fwd(const void* x, const void* w, const void* b, void* y
                             int D, float eps, void* stream) {
   gf::enter();
   if (D % 8 || D > NORM_THREADS * NORM_MAXV * 8 || T <= 0) return GFH_BAD_ARG;
+  if (D <= 1024) {   // one warp per row
+    const int vpl = (D / 8 + 31) / 32;
+    auto kern = vpl == 1 ? layernorm_fwd_warp_kernel<1> : vpl == 2 ? layernorm_fwd_warp_kernel<2>
+                : vpl == 3 ? layernorm_fwd_warp_kernel<3> : layernorm_fwd_warp_kernel<4>;
+    const int want = (T + 7) / 8, cap = sm_count() * 8;
+    kern<<<want < cap ? want : cap, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, mean, rstd, T,
+        D, eps);
+    return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+  }
   layernorm_fwd_kernel<<<T, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, mean, rstd, T,
       D, eps);
@@ -377,6 +523,14 @@ GF_API int gf_layernorm_bwd(const void* x, const void* w, const void* dy, const 
   if (D % 8 || D > NORM_THREADS * NORM_MAXV * 8 || T <= 0) return GFH_BAD_ARG;
   const int g = norm_grid(T);
   float* s2 = scratch + (long long)g * D;
+  if (D <= 1024) {   // one warp per row; the CTA still writes one partial row per gradient
+    const int vpl = (D / 8 + 31) / 32;
+    auto kern = vpl == 1 ? layernorm_bwd_warp_kernel<1> : vpl == 2 ? layernorm_bwd_warp_kernel<2>
+                : vpl == 3 ? layernorm_bwd_warp_kernel<3> : layernorm_bwd_warp_kernel<4>;
+    kern<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, mean, rstd, (__nv_bfloat16*)dx,
+        scratch, s2, T, D);
+  } else
   layernorm_bwd_kernel<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, mean, rstd, (__nv_bfloat16*)dx,
       scratch, s2, T, D);

@@ -439,6 +439,29 @@ static inline int ew_grid(long long n, int threads) {
   return (int)(g < cap ? (g > 0 ? g : 1) : cap);
 }
 
+// x *= *scalar unless *scalar == 1 (the usual case for the gradient of a loss that is the root of the backward
+// pass): the decision is taken on the device, so the host never has to read the scalar.
+__global__ void scale_by_dev_scalar_kernel(__nv_bfloat16* __restrict__ x, long long n, const float* __restrict__ scalar) {
+  const float s = *scalar;
+  if (s == 1.f) return;
+  const long long nvec = n >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    uint4 u = reinterpret_cast<uint4*>(x)[i];
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w[j]);
+      float2 f = __bfloat1622float2(v);
+      v = __floats2bfloat162_rn(f.x * s, f.y * s);
+      w[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    reinterpret_cast<uint4*>(x)[i] = u;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = nvec << 3; i < n; ++i) x[i] = __float2bfloat16(__bfloat162float(x[i]) * s);
+}
+
 }  // namespace gf
 
 using namespace gf;
@@ -452,6 +475,13 @@ GF_API int gf_rope(void* x, const float* cos_t, const float* sin_t, int T, int H
   rope_kernel<<<ew_grid(total, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, cos_t, sin_t, T, H, D,
                                                                     row_stride, head_stride, S, pos_offset, mode,
                                                                     backward ? -1.f : 1.f);
+  GF_RET();
+}
+// x: bf16 [n], 16-byte aligned; scalar: one fp32 on the device.
+GF_API int gf_scale_by_dev_scalar(void* x, long long n, const float* scalar, void* stream) {
+  gf::enter();
+  if (!x || !scalar || n <= 0 || (reinterpret_cast<uintptr_t>(x) & 15)) return GFH_BAD_ARG;
+  scale_by_dev_scalar_kernel<<<ew_grid(n / 8 + 1, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, n, scalar);
   GF_RET();
 }
 GF_API int gf_swiglu_fwd(const void* gu, void* y, long long T, int F, void* stream) {

@@ -23,13 +23,22 @@ xent_fused_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __r
   extern __shared__ __align__(16) uint8_t xs_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(xs_raw);
   __shared__ float red[32];
-  const int nv = V >> 3;  // host guarantees V % 8 == 0 and ld % 8 == 0
+  // Rows move as 16-byte vectors. The host guarantees ld % 8 == 0 and ld >= round_up(V, 8), so the last vector of a
+  // row whose V is not a multiple of 8 lies inside the row's pitch: its columns >= V are read as -inf (they add
+  // nothing to the sum) and get gradient 0.
+  const int nv = (V + 7) >> 3;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const __nv_bfloat16* xr = logits + (long long)row * ld;
     const long long tgt = targets[row];
     float m = -INFINITY;
     for (int v = threadIdx.x; v < nv; v += XENT_THREADS) {
       uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
+      if (v * 8 + 8 > V) {
+        unsigned short* h = reinterpret_cast<unsigned short*>(&u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v * 8 + j >= V) h[j] = 0xFF80;   // bf16 -inf
+      }
       *reinterpret_cast<uint4*>(xs + v * 8) = u;
       const uint32_t* p = reinterpret_cast<const uint32_t*>(&u);
 #pragma unroll
@@ -228,8 +237,10 @@ using namespace gf;
 GF_API int gf_xent_fused(const void* logits, const long long* targets, float* loss_rows, void* dlogits, int T, int V,
                          long long ld, float grad_scale, long long ignore_index, void* stream) {
   gf::enter();
-  if (V % 8 || ld % 8 || T <= 0) return GFH_BAD_ARG;
-  const size_t smem = (size_t)V * 2;
+  const long long v8 = ((long long)V + 7) / 8 * 8;
+  if (V <= 0 || ld % 8 || ld < v8 || T <= 0) return GFH_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) || (reinterpret_cast<uintptr_t>(dlogits) & 15)) return GFH_BAD_ARG;
+  const size_t smem = (size_t)v8 * 2;
   if (smem > 200 * 1024) return GFH_TOO_LARGE;
   static size_t configured = 0;
   if (smem > configured) {

@@ -35,6 +35,7 @@ _SIGS = {
     "gf_layernorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, P],
     "gf_rope": [P, P, P, I, I, I, L, L, I, I, I, I, P],
     "gf_swiglu_fwd": [P, P, L, I, P],
+    "gf_scale_by_dev_scalar": [P, L, P, P],
     "gf_swiglu_bwd": [P, P, P, L, I, P],
     "gf_unary_fwd": [P, P, L, I, I, P],
     "gf_unary_bwd_bf16": [P, P, P, L, I, P],

@@ -332,13 +332,22 @@ def op_chain(x, names):
 
 
 # ------------------------------------------------------------------------------------------ cross-entropy
+def _padded_rows(rows: int, cols: int, device, dtype, pitch: int | None = None) -> torch.Tensor:
+    """``[rows, cols]`` view of a buffer whose row pitch is a multiple of 64 elements: every row starts on a 16-byte
+    boundary whatever ``cols`` is (a 50257-column logits matrix would not otherwise), which is what TMA tensor maps
+    and the vectorised row kernels need. The padding columns are not initialised."""
+    pitch = pitch or (cols + 63) // 64 * 64
+    return torch.empty(rows, pitch, device=device, dtype=dtype)[:, :cols]
+
+
 class _XentFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, targets, ignore_index, inplace_grad):
         V = logits.shape[-1]
         l2 = logits.reshape(-1, V)
-        if l2.stride(-1) != 1:
-            l2 = l2.contiguous()
+        if l2.stride(-1) != 1 or l2.stride(0) % 8 or l2.stride(0) < (V + 7) // 8 * 8 or l2.data_ptr() % 16:
+            # rows must start on 16-byte boundaries and leave room for the last vector: copy into a padded buffer
+            l2 = _padded_rows(l2.shape[0], V, l2.device, l2.dtype).copy_(l2)
         T = l2.shape[0]
         tg = targets.reshape(-1).to(torch.int64).contiguous()
         n_valid = None
@@ -348,7 +357,7 @@ class _XentFn(torch.autograd.Function):
         need_grad = logits.requires_grad
         dl = None
         if need_grad:
-            dl = l2 if inplace_grad else torch.empty_like(l2)
+            dl = l2 if inplace_grad else _padded_rows(T, V, l2.device, l2.dtype, pitch=l2.stride(0))
         # the 1/N of the mean is folded in here; backward only multiplies by the incoming scalar
         scale = 1.0 / T if n_valid is None else None
         if scale is None:
@@ -368,9 +377,17 @@ class _XentFn(torch.autograd.Function):
         if dl.numel() == 0:
             return None, None, None, None
         g = dl.view(ctx.shape)
-        # dloss is 1.0 for a plain loss.backward(); scale only when it is something else
-        g = g * dloss.to(g.dtype) if dloss.numel() == 1 and float(dloss) != 1.0 else g
-        return g, None, None, None
+        # dloss is 1.0 for a plain loss.backward(): scale only when it is something else. On the GPU the kernel
+        # reads the scalar and returns at once when it is 1, so the host never waits for the value (a host read
+        # here would stall every backward pass and cannot be recorded in a CUDA graph).
+        if dloss.numel() != 1:
+            return g * dloss.to(g.dtype), None, None, None
+        if g.is_cuda and g.dtype == torch.bfloat16 and g.is_contiguous() and g.data_ptr() % 16 == 0:
+            _lib.check_rc(_lib.cuda_lib().gf_scale_by_dev_scalar(g.data_ptr(), g.numel(),
+                                                                 dloss.float().data_ptr(), _lib.stream_ptr()),
+                          "gf_scale_by_dev_scalar")
+            return g, None, None, None
+        return (g * dloss.to(g.dtype) if float(dloss) != 1.0 else g), None, None, None
 
 
 def cross_entropy(logits, targets, ignore_index: int | None = None, inplace_grad: bool = False):
@@ -378,7 +395,7 @@ def cross_entropy(logits, targets, ignore_index: int | None = None, inplace_grad
     gradient in the same pass (``inplace_grad=True`` overwrites ``logits`` with it).
     ``ignore_index=None`` promises that every target is a class id, which avoids a host sync."""
     V = logits.shape[-1]
-    if _cuda_bf16(logits) and V % 8 == 0 and V * 2 <= 200 * 1024:
+    if _cuda_bf16(logits) and (V + 7) // 8 * 16 <= 200 * 1024:
         return _XentFn.apply(logits, targets, ignore_index, inplace_grad)
     return F.cross_entropy(logits.reshape(-1, V).float(), targets.reshape(-1).long(),
                            ignore_index=-100 if ignore_index is None else ignore_index)

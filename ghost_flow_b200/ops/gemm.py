@@ -29,7 +29,12 @@ def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bf
     assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert _is_dense_2d(a) and _is_dense_2d(b), "operands must be 2-D with unit inner stride"
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        if N % 8:
+            # rows of an [M, N] tensor with such an N do not start on 16-byte boundaries; give the result a padded
+            # pitch (the caller gets an [M, N] view) so that it can feed the next kernel as it is
+            out = torch.empty((M, (N + 63) // 64 * 64), dtype=out_dtype, device=a.device)[:, :N]
+        else:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert _is_dense_2d(out)
     lib = _lib.cuda_lib()
     rc = lib.gf_gemm_bf16(

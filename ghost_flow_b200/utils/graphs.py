@@ -39,7 +39,8 @@ class GraphedStep:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        # thread_local: other threads (the NCCL watchdog polls events) may keep calling the runtime during the recording
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             self.static_output = fn(*self.static_inputs)
         self.replays = 0
 
@@ -49,3 +50,10 @@ class GraphedStep:
         self.graph.replay()
         self.replays += 1
         return self.static_output
+
+    def release(self):
+        """Drops the recording (and the memory pool it holds). Call it before tearing a process group down: a live
+        graph that contains collectives keeps the communicator's watchdog from finishing."""
+        torch.cuda.synchronize()
+        self.graph.reset()
+        self.static_output = None

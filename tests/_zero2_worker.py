@@ -63,6 +63,8 @@ def main():
     if rank == 0:
         torch.save({"losses": losses, "w": w, "buckets": len(opt.buckets), "fused": opt._fc is not None,
                     "overlap": opt.overlap, "graph": graph}, out)
+    if graph:
+        gs.release()
     dist.barrier()
     dist.destroy_process_group()
 

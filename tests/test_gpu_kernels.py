@@ -174,8 +174,10 @@ def test_rmsnorm_fused_residual(kernel_status):
     assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(r.grad, rr.grad) < 1e-2
 
 
-@pytest.mark.parametrize("T,D", [(64, 768), (33, 128)])
+@pytest.mark.parametrize("T,D", [(64, 768), (33, 128), (8192, 768), (1000, 1024), (77, 200), (130, 1032), (50, 4096)])
 def test_layernorm_fwd_bwd(T, D, kernel_status):
+    """Rows up to 1024 long go through the warp-per-row kernels (one to four vectors per lane, rows shared by the
+    eight warps of a CTA); longer ones through the CTA-per-row kernels."""
     ops = _ops()
     x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
@@ -243,7 +245,7 @@ def test_swiglu_and_unary(kernel_status):
 
 
 # ----------------------------------------------------------------------------------------- loss / optimizer
-@pytest.mark.parametrize("T,V", [(64, 1000), (37, 32000), (8, 50264)])
+@pytest.mark.parametrize("T,V", [(64, 1000), (37, 32000), (8, 50264), (24, 50257), (16, 1003)])
 def test_xent_fused(T, V, kernel_status):
     ops = _ops()
     logits = (2 * torch.randn(T, V, device=DEV)).to(torch.bfloat16).requires_grad_()
@@ -255,6 +257,25 @@ def test_xent_fused(T, V, kernel_status):
     ref.backward()
     assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
     assert _rel_err(logits.grad, lr.grad) < 2e-2
+
+
+def test_linear_head_with_odd_vocabulary_stays_on_the_kernels(kernel_status):
+    """GPT-2's 50257-entry vocabulary: rows of a [T, 50257] bf16 matrix do not start on 16-byte boundaries, so the
+    head's output, the loss gradient and both backward products use a padded row pitch instead of falling back."""
+    ops = _ops()
+    T, d, V = 192, 256, 50257
+    x = (0.5 * torch.randn(T, d, device=DEV)).to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(V, d, device=DEV)).to(torch.bfloat16).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    logits = ops.linear(x, w)
+    assert logits.shape == (T, V) and logits.stride(0) % 64 == 0
+    loss = ops.cross_entropy(logits, tgt)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(xr @ wr.t(), tgt)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * abs(ref.item())
+    assert _rel_err(x.grad, xr.grad) < 2e-2 and _rel_err(w.grad, wr.grad) < 2e-2
 
 
 def test_adamw_flat_matches_reference_formula(kernel_status):
