@@ -944,25 +944,32 @@ static void no_gather(gf::GemmParams& p) {
 GF_API int gf_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, long long lda,
                         int b_mn_major, long long ldb, long long ldc, int out_fp32, int accumulate,
                         const void* bias, const void* residual, long long ldr, float alpha, int* status,
-                        int bn_hint, int max_ctas, const int* reserved_ptr, int activation, int reserved_int,
+                        int bn_hint, int max_ctas, const int* splitk_ws, int activation, int splitk_ws_floats,
                         void* stream_v) {
   gf::enter();
   gf::GemmParams p;
   no_gather(p);
   p.act = activation == 1 ? 1 : 0;   // epilogue activation after bias and residual: 0 none, 1 ReLU
-  (void)reserved_ptr; (void)reserved_int;   // kept so that the exported signature stays what callers bound
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
-  // Skinny problem (decode-sized M): too few output tiles to fill the machine, so the weight matrix would be
-  // streamed by a handful of SMs. Split K until there is about one work item per SM.
-  if (M <= 256 && !out_fp32 && !accumulate && K >= 2048 && bn_hint == 0 && max_ctas == 0 && p.act == 0) {
-    const int bn = N <= 128 ? 128 : 256;
-    const long long tiles = (long long)((M + gf::BM - 1) / gf::BM) * ((N + bn - 1) / bn);
+  // Few output tiles and a long K (decode-sized M; weight gradients of narrow layers, [768, 2304] over 8192 tokens):
+  // too few tiles to fill the machine. Split K until there is about one work item per SM; the slices add into an
+  // fp32 workspace that a second kernel converts. The workspace is the caller's (splitk_ws, splitk_ws_floats >= M * N:
+  // a buffer that belongs to the calling stream, e.g. from a stream-ordered allocator) or, without one, a buffer
+  // this library keeps per device, which only one stream at a time may use.
+  const int bn_sk = N <= 128 ? 128 : 256;
+  const long long tiles_sk = (long long)((M + gf::BM - 1) / gf::BM) * ((N + bn_sk - 1) / bn_sk);
+  if (tiles_sk * 2 <= gf::sm_count() && !out_fp32 && !accumulate && K >= 2048 && bn_hint == 0 && max_ctas == 0 &&
+      p.act == 0) {
+    const int bn = bn_sk;
+    const long long tiles = tiles_sk;
     const int sms = gf::sm_count();
     int split = (int)(sms / (tiles > 0 ? tiles : 1));
     if (split > K / 512) split = K / 512;
     if (split > 16) split = 16;
     if (split >= 2) {
-      float* ws = gf::splitk_workspace((size_t)M * N);
+      float* ws = (splitk_ws && (long long)splitk_ws_floats >= (long long)M * N)
+                      ? reinterpret_cast<float*>(const_cast<int*>(splitk_ws))
+                      : gf::splitk_workspace((size_t)M * N);
       if (ws) {
         if (cudaMemsetAsync(ws, 0, sizeof(float) * (size_t)M * N, st) != cudaSuccess) return gf::GFH_CUDA;
         p.split_k = split;

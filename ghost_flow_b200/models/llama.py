@@ -31,7 +31,7 @@ class LLaMAAttention(Module):
         B, S, _ = x.shape
         H, Hk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         qkv = self.wqkv(x).view(B, S, H + 2 * Hk, D)
-        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hk], qkv[:, :, H + Hk:]
+        q, k, v = ops.split_qkv(qkv, H, Hk)
         q = ops.rope(q, cos, sin, c.rope_interleaved, start_pos)
         k = ops.rope(k, cos, sin, c.rope_interleaved, start_pos)
         if cache is not None:

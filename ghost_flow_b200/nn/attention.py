@@ -56,8 +56,7 @@ class MultiHeadAttention(Module):
     def _split(self, x):
         B, S, _ = x.shape
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.qkv(x).view(B, S, H + 2 * Hk, D)
-        return qkv[:, :, :H], qkv[:, :, H:H + Hk], qkv[:, :, H + Hk:]
+        return ops.split_qkv(self.qkv(x).view(B, S, H + 2 * Hk, D), H, Hk)
 
     def forward(self, x, mask=None, causal: bool | None = None, rope=None, residual=None):
         """x: ``[B, S, E]``. ``rope`` = (cos, sin, interleaved) applies rotary embedding to q and k."""

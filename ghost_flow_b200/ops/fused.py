@@ -466,6 +466,46 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _SplitQKVFn(torch.autograd.Function):
+    """``qkv [B, S, H + 2 Hk, D] -> q, k, v`` as views. Plain slicing gives the same forward, but its backward pads
+    each of the three gradients to the full shape with zeros and adds them (six passes over the packed tensor); the
+    attention backward already writes its three gradients into one packed buffer, which this function recognises
+    and hands on as it is."""
+
+    @staticmethod
+    def forward(ctx, qkv, H, Hk):
+        ctx.H, ctx.Hk = H, Hk
+        return qkv[:, :, :H], qkv[:, :, H:H + Hk], qkv[:, :, H + Hk:]
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        H, Hk = ctx.H, ctx.Hk
+        if dq is None or dk is None or dv is None:
+            ref = next(t for t in (dq, dk, dv) if t is not None)
+            B, S, _, D = ref.shape
+            dq = dq if dq is not None else ref.new_zeros(B, S, H, D)
+            dk = dk if dk is not None else ref.new_zeros(B, S, Hk, D)
+            dv = dv if dv is not None else ref.new_zeros(B, S, Hk, D)
+        B, S, _, D = dq.shape
+        G = H + 2 * Hk
+        packed = (S * G * D, G * D, D, 1)
+        same = (dq.untyped_storage().data_ptr() == dk.untyped_storage().data_ptr() == dv.untyped_storage().data_ptr()
+                and dq.stride() == packed and dk.stride() == packed and dv.stride() == packed
+                and dk.storage_offset() == dq.storage_offset() + H * D
+                and dv.storage_offset() == dq.storage_offset() + (H + Hk) * D)
+        if same:
+            return dq.as_strided((B, S, G, D), packed, dq.storage_offset()), None, None
+        return torch.cat((dq, dk, dv), 2), None, None
+
+
+def split_qkv(qkv: torch.Tensor, num_heads: int, num_kv_heads: int):
+    """Views ``q [B,S,H,D]``, ``k``, ``v [B,S,Hk,D]`` of a packed projection output ``[B,S,H+2Hk,D]``."""
+    if torch.is_grad_enabled() and qkv.requires_grad:
+        return _SplitQKVFn.apply(qkv, num_heads, num_kv_heads)
+    H, Hk = num_heads, num_kv_heads
+    return qkv[:, :, :H], qkv[:, :, H:H + Hk], qkv[:, :, H + Hk:]
+
+
 def flash_attention(q, k, v, causal: bool = True, scale: float | None = None):
     """Attention over ``q [B,S,Hq,D]``, ``k/v [B,S,Hkv,D]`` (views into a packed QKV tensor are fine).
     head_dim 64 or 128 on the tcgen05 kernels; anything else uses the fp32 reference math."""

@@ -14,6 +14,16 @@ import torch
 from . import _lib
 
 
+_SMS: dict = {}
+
+
+def _sm_count(device) -> int:
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _SMS:
+        _SMS[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _SMS[i]
+
+
 def _is_dense_2d(t: torch.Tensor) -> bool:
     return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.size(1)
 
@@ -37,6 +47,13 @@ def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bf
             out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert _is_dense_2d(out)
     lib = _lib.cuda_lib()
+    # few output tiles and a long K: the kernel splits K and needs an fp32 [M, N] workspace. It comes from torch's
+    # allocator, so it belongs to the current stream (and to the graph's pool while a CUDA graph is recorded).
+    ws = None
+    if (K >= 2048 and out.dtype == torch.bfloat16 and not accumulate and not relu and bn_hint == 0 and max_ctas == 0
+            and M * N < (1 << 31)
+            and 2 * ((M + 127) // 128) * ((N + (127 if N <= 128 else 255)) // (128 if N <= 128 else 256)) <= _sm_count(a.device)):
+        ws = torch.empty(M * N, dtype=torch.float32, device=a.device)
     rc = lib.gf_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
         1 if a_mn_major else 0, a.stride(0), 1 if b_mn_major else 0, b.stride(0), out.stride(0),
@@ -45,7 +62,7 @@ def gemm_raw(a, a_mn_major, b, b_mn_major, M, N, K, out=None, out_dtype=torch.bf
         residual.data_ptr() if residual is not None else None,
         residual.stride(0) if residual is not None else 0,
         float(alpha), _lib.status_word(a.device).data_ptr(), bn_hint, max_ctas,
-        None, 1 if relu else 0, 0,
+        ws.data_ptr() if ws is not None else None, 1 if relu else 0, ws.numel() if ws is not None else 0,
         _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "gf_gemm_bf16")

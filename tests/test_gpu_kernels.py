@@ -55,6 +55,40 @@ def test_gemm_layouts(M, N, K, layout, kernel_status):
     _assert_gemm_elementwise(out, ref, K, f"{layout} {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("M,N,K,layout", [(768, 2304, 8192, "tn"), (768, 768, 4096, "tn"), (3072, 768, 8192, "tn"),
+                                          (200, 760, 2056, "nt"), (64, 4096, 4096, "nt")])
+def test_gemm_split_k_when_tiles_are_few(M, N, K, layout, kernel_status):
+    """Weight-gradient shapes of narrow layers (few output tiles, K = tokens): K is split over the idle SMs and the
+    slices meet in an fp32 workspace that the caller's allocator provides."""
+    ops = _ops()
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float()
+    out = ops.matmul_tn(a.t().contiguous(), b) if layout == "tn" else ops.matmul_nt(a, b.t().contiguous())
+    torch.cuda.synchronize()
+    assert _rel_err(out, ref) < 1e-2
+    _assert_gemm_elementwise(out, ref, K, f"split-k {layout} {M}x{N}x{K}")
+
+
+def test_split_qkv_backward_hands_on_the_packed_gradient(kernel_status):
+    ops = _ops()
+    B, S, H, Hk, D = 2, 256, 4, 2, 64
+    qkv = torch.randn(B, S, H + 2 * Hk, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = ops.split_qkv(qkv, H, Hk)
+    o = ops.flash_attention(q, k, v, causal=True)
+    g = torch.randn_like(o)
+    o.backward(g)
+    ref = qkv.detach().clone().requires_grad_()
+    o2 = ops.flash_attention(ref[:, :, :H], ref[:, :, H:H + Hk], ref[:, :, H + Hk:], causal=True)
+    o2.backward(g)
+    assert _rel_err(qkv.grad, ref.grad) < 1e-3
+    # gradients that are not slices of one buffer are concatenated
+    qkv2 = qkv.detach().clone().requires_grad_()
+    q, k, v = ops.split_qkv(qkv2, H, Hk)
+    (q.float().sum() + 2 * k.float().sum() + 3 * v.float().sum()).backward()
+    assert float(qkv2.grad[:, :, :H].float().mean()) == 1.0 and float(qkv2.grad[:, :, H + Hk:].float().mean()) == 3.0
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_tile_widths_and_epilogue(bn, kernel_status):
     ops = _ops()
