@@ -388,7 +388,7 @@ layernorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 }
 
 template <int VPL>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, 2)
 layernorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                           const __nv_bfloat16* __restrict__ dy, const float* __restrict__ mean_in,
                           const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
@@ -397,12 +397,13 @@ layernorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nv = D >> 3;
   constexpr int WPC = NORM_THREADS / 32;
   for (int i = threadIdx.x; i < D; i += NORM_THREADS) acc[0][i] = acc[1][i] = 0.f;
-  float dwacc[VPL][8], dbacc[VPL][8], wv[VPL][8];
+  // the weight is re-read for every row (1.5 KB, served by L1): keeping it in registers next to the two
+  // accumulators would push the kernel to one CTA per SM
+  float dwacc[VPL][8], dbacc[VPL][8];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = dbacc[i][j] = 0.f;
-    if (lane + i * 32 < nv) load8(w + (lane + i * 32) * 8, wv[i]);
   }
   for (int row = blockIdx.x * WPC + warp; row < T; row += gridDim.x * WPC) {
     const float mean = mean_in[row], rstd = rstd_in[row];
@@ -412,14 +413,16 @@ layernorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
     for (int i = 0; i < VPL; ++i) {
       const int v = lane + i * 32;
       if (v < nv) {
+        float wv[8];
         load8(x + (long long)row * D + v * 8, xh[i]);
         load8(dy + (long long)row * D + v * 8, gv[i]);
+        load8(w + v * 8, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xh[i][j] - mean) * rstd;
           dwacc[i][j] += gv[i][j] * xh[i][j];
           dbacc[i][j] += gv[i][j];
-          gv[i][j] *= wv[i][j];
+          gv[i][j] *= wv[j];
           sg += gv[i][j];
           sgx += gv[i][j] * xh[i][j];
         }
@@ -457,6 +460,41 @@ layernorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
   }
 }
 
+// ------------------------------------------------------------------ column sums (bias gradients)
+// out[d] = sum over rows of x[row, d]: every CTA of a persistent grid adds its rows in registers (fp32) and writes
+// one partial row; fold_partials_kernel adds the partial rows. x is read once, 16 bytes per thread and step.
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restrict__ partial, int T, int D) {
+  const int nv = D >> 3;
+  float acc[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nv) {
+        float f[8];
+        load8(x + (long long)row * ld + v * 8, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nv) {
+      float* dst = partial + (long long)blockIdx.x * D + v * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] = acc[i][j];
+    }
+  }
+}
+
 static inline int norm_grid(int T) {
   int g = sm_count() * 4;
   return T < g ? T : g;
@@ -490,6 +528,21 @@ GF_API int gf_rmsnorm_bwd(const void* x, const void* w, const void* dy, const fl
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres,
       (__nv_bfloat16*)dx, scratch, T, D);
   fold_partials_kernel<<<(D + 31) / 32, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)dw, g, D,
+                                                                          accumulate);
+  gf::note_extra_launches(1);
+  return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
+}
+
+// x: bf16 [T, D] with row pitch ld (elements, multiple of 8); out: bf16 [D]; scratch: fp32 [gf_norm_bwd_grid(T), D].
+GF_API int gf_colsum_bf16(const void* x, long long ld, void* out, float* scratch, int T, int D, int accumulate,
+                          void* stream) {
+  gf::enter();
+  if (D % 8 || ld % 8 || ld < D || D > NORM_THREADS * NORM_MAXV * 8 || T <= 0 || !scratch) return GFH_BAD_ARG;
+  const int g = norm_grid(T);
+  auto kern = D <= NORM_THREADS * 8 ? colsum_partial_kernel<1>
+              : D <= NORM_THREADS * 16 ? colsum_partial_kernel<2> : colsum_partial_kernel<NORM_MAXV>;
+  kern<<<g, NORM_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ld, scratch, T, D);
+  fold_partials_kernel<<<(D + 31) / 32, 256, 0, (cudaStream_t)stream>>>(scratch, (__nv_bfloat16*)out, g, D,
                                                                           accumulate);
   gf::note_extra_launches(1);
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;

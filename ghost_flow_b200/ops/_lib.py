@@ -47,6 +47,7 @@ _SIGS = {
     "gf_adam_flat": [P, P, P, P, P, L, F, F, F, F, F, I, F, I, I, P, P],
     "gf_adam_flat_dev": [P, P, P, P, P, L, F, F, F, F, F, I, F, I, I, P, P, P],
     "gf_counter_add": [P, I, P],
+    "gf_colsum_bf16": [P, L, P, P, I, I, I, P],
     "gf_sgd_flat": [P, P, P, P, L, F, F, F, F, I, I, F, I, P],
     "gf_grad_sumsq": [P, L, P, I, P],
     "gf_flash_attn_fwd": [P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, P, P],

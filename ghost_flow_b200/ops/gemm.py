@@ -129,6 +129,19 @@ def _as_2d(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
+def _colsum(x2: torch.Tensor) -> torch.Tensor:
+    """Sum over the rows of a 2-D tensor, fp32 accumulation, result in the input's dtype (the bias gradient)."""
+    T, D = x2.shape
+    if _kernel_ok(x2) and D % 8 == 0 and D <= 8192 and T > 0:
+        lib = _lib.cuda_lib()
+        out = torch.empty(D, dtype=x2.dtype, device=x2.device)
+        scratch = torch.empty(lib.gf_norm_bwd_grid(T) * D, dtype=torch.float32, device=x2.device)
+        _lib.check_rc(lib.gf_colsum_bf16(x2.data_ptr(), x2.stride(0), out.data_ptr(), scratch.data_ptr(), T, D, 0,
+                                         _lib.stream_ptr()), "gf_colsum_bf16")
+        return out
+    return torch.sum(x2, 0, dtype=torch.float32).to(x2.dtype)   # fp32 accumulation without an fp32 copy of x
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, residual):
@@ -151,7 +164,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = matmul_tn(dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = torch.sum(dy2, 0, dtype=torch.float32).to(dy2.dtype)   # fp32 accumulation without an fp32 copy of dy
+            db = _colsum(dy2)
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres

@@ -70,6 +70,17 @@ def test_gemm_split_k_when_tiles_are_few(M, N, K, layout, kernel_status):
     _assert_gemm_elementwise(out, ref, K, f"split-k {layout} {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("T,D", [(8192, 768), (1000, 3072), (37, 8192), (5, 64)])
+def test_linear_bias_gradient_column_sum(T, D, kernel_status):
+    ops = _ops()
+    x = torch.randn(T, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(D, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.zeros(D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, D, device=DEV, dtype=torch.bfloat16)
+    ops.linear(x, w, b).backward(g)
+    assert _rel_err(b.grad, g.float().sum(0)) < 1e-2
+
+
 def test_split_qkv_backward_hands_on_the_packed_gradient(kernel_status):
     ops = _ops()
     B, S, H, Hk, D = 2, 256, 4, 2, 64
