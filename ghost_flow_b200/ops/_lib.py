@@ -169,13 +169,19 @@ class KernelStatusError(RuntimeError):
 
 
 def check_status(device=None, reset: bool = True) -> None:
-    """Synchronises and raises if any kernel since the last check recorded an error code."""
+    """Synchronises and raises if any kernel since the last check recorded an error code, or if a guard block behind
+    a carve-out of an arena / workspace was overwritten (``parallel.canary``)."""
     w = status_word(device)
     code = int(w.item())
     if code != 0:
         if reset:
             w.zero_()
         raise KernelStatusError(f"ghost_flow_b200 kernel status {code}: {_ERR_NAMES.get(code, 'unknown')}")
+    import sys
+
+    canary = sys.modules.get("ghost_flow_b200.parallel.canary")     # only if something planted guard blocks
+    if canary is not None:
+        canary.check_all()
 
 
 def check_rc(rc: int, what: str) -> None:

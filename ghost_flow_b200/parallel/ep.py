@@ -167,13 +167,18 @@ class ExpertParallelMoE:
             self.ws = SymmetricWorkspace(total, self.device, self.group or dist.group.WORLD)
             alloc, peers = self.ws.alloc, self.ws.peer_ptrs
         else:
-            buf = torch.zeros(total, dtype=torch.uint8, device=self.device)
-            self._buf, off = buf, [0]
+            from .canary import SLACK_BYTES, CanaryLedger
+
+            buf = torch.zeros(total + SLACK_BYTES, dtype=torch.uint8, device=self.device)
+            self._buf = buf
+            self.canaries = CanaryLedger(buf, "expert-parallel workspace")
+            off = [self.canaries.plant(0, "start of the workspace")]
 
             def alloc(numel, dtype):
                 esz = torch.empty((), dtype=dtype).element_size()
                 t = buf[off[0]:off[0] + numel * esz].view(dtype)
-                off[0] += (numel * esz + 255) // 256 * 256
+                off[0] = self.canaries.plant(off[0] + (numel * esz + 255) // 256 * 256,
+                                             f"carve-out {len(self.canaries.blocks)}")
                 return t
 
             def peers(t):

@@ -106,24 +106,29 @@ class FusedComm(Comm):
     # ------------------------------------------------------------------ arena
     def reserve(self, nbytes: int) -> None:
         """Allocates the symmetric arena (collective call: every rank passes the same size)."""
-        nbytes = (nbytes + 4095) // 4096 * 4096
+        from .canary import SLACK_BYTES, CanaryLedger
+
+        nbytes = (nbytes + SLACK_BYTES + 4095) // 4096 * 4096
         self.arena = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.arena_hdl = self._symm.rendezvous(self.arena, self.group_name)
         self.arena_ptrs = [int(p) for p in self.arena_hdl.buffer_ptrs]
         mc = getattr(self.arena_hdl, "multicast_ptr", 0) or 0
         self.arena_mc = int(mc) if self.use_multimem else 0
-        self.offset = 0
+        # guard blocks in front of the first carve-out and behind every carve-out (each rank guards its own copy)
+        self.canaries = CanaryLedger(self.arena, f"symmetric arena of rank {self.rank}")
+        self.offset = self.canaries.plant(0, "start of the arena")
 
     def alloc(self, numel: int, dtype, device=None) -> torch.Tensor:
         """Carves a zero-filled tensor out of the arena (same offset on every rank)."""
         esz = torch.empty((), dtype=dtype).element_size()
         nbytes = (numel * esz + 255) // 256 * 256
-        if self.arena is None or self.offset + nbytes > self.arena.numel():
+        if self.arena is None or self.offset + nbytes + 256 > self.arena.numel():
             raise RuntimeError("symmetric arena exhausted; reserve() more")
         t = self.arena[self.offset:self.offset + numel * esz].view(dtype)
         t._gf_arena_offset = self.offset
-        self.offset += nbytes
         t.zero_()
+        self.offset = self.canaries.plant(self.offset + nbytes, f"carve-out {len(self.canaries.blocks)} "
+                                                                f"({numel} x {str(dtype).replace('torch.', '')})")
         return t
 
     def peer_ptrs(self, t: torch.Tensor):

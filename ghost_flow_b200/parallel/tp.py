@@ -53,22 +53,28 @@ class SymmetricWorkspace:
 
         self.group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        nbytes = (nbytes + 4095) // 4096 * 4096
+        from .canary import SLACK_BYTES, CanaryLedger
+
+        nbytes = (nbytes + SLACK_BYTES + 4095) // 4096 * 4096
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, self.group.group_name)
         self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
-        self.offset = 0
+        # guard blocks: one in front of the first carve-out, one behind every carve-out (each rank guards its own copy)
+        self.canaries = CanaryLedger(self.buf, f"symmetric workspace of rank {self.rank}")
+        self.offset = self.canaries.plant(0, "start of the workspace")
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
 
     def alloc(self, numel: int, dtype) -> torch.Tensor:
         esz = torch.empty((), dtype=dtype).element_size()
         nbytes = (numel * esz + 255) // 256 * 256
-        if self.offset + nbytes > self.buf.numel():
+        if self.offset + nbytes + 256 > self.buf.numel():
             raise RuntimeError("symmetric workspace exhausted")
         t = self.buf[self.offset:self.offset + numel * esz].view(dtype)
-        self.offset += nbytes
+        # the guard block starts at the next 256-byte boundary behind the tensor (same offsets on every rank)
+        self.offset = self.canaries.plant(self.offset + nbytes, f"carve-out {len(self.canaries.blocks)} "
+                                                                f"({numel} x {str(dtype).replace('torch.', '')})")
         return t
 
     def peer_ptrs(self, t: torch.Tensor):
