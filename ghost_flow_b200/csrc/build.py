@@ -81,13 +81,20 @@ def _compile_one(cmd: list[str], src: Path, obj: Path, stamp: Path, digest: str,
     return f"compiled    {src.name}"
 
 
-def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
-    """Compiles what is out of date and links both libraries. Returns their paths."""
+# Sources that contain checked accesses (GF_CHECK_IDX): only these are compiled a second time for the checked library;
+# the other objects are shared between the two libraries.
+CHECKED_SOURCES = ["gf_host.cu", "gemm_bf16.cu", "moe_kernels.cu"]
+
+
+def build(force: bool = False, verbose: bool = False, checked: bool = True) -> dict[str, Path]:
+    """Compiles what is out of date and links the libraries. Returns their paths. ``checked`` also links
+    ``libgfb200_checked.so`` (``-DGF_CHECKED``: data-dependent indices are range-checked on the device and the first
+    offender is reported through the status buffer), which ``GF_CHECKED=1`` makes the package load."""
     LIB_DIR.mkdir(exist_ok=True)
     OBJ_DIR.mkdir(exist_ok=True)
     nvcc = _nvcc()
     jobs = []
-    cuda_objs, host_objs = [], []
+    cuda_objs, host_objs, checked_objs = [], [], []
     for name in CUDA_SOURCES:
         src = HERE / name
         if not src.exists():
@@ -96,6 +103,13 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
         cmd = [nvcc, *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)]
         jobs.append((cmd, src, obj))
         cuda_objs.append(obj)
+        if checked and name in CHECKED_SOURCES:
+            cobj = OBJ_DIR / (name + ".checked.o")
+            jobs.append(([nvcc, *NVCC_FLAGS, "-DGF_CHECKED", "-I", str(HERE), "-c", str(src), "-o", str(cobj)], src,
+                         cobj))
+            checked_objs.append(cobj)
+        elif checked:
+            checked_objs.append(obj)
     for name in HOST_SOURCES:
         src = HERE / name
         if not src.exists():
@@ -127,6 +141,15 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
             if r.returncode != 0:
                 raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
         out["cuda"] = lib
+        if checked:
+            lib = LIB_DIR / "libgfb200_checked.so"
+            newest = max(o.stat().st_mtime for o in checked_objs)
+            if force or not lib.exists() or lib.stat().st_mtime < newest:
+                r = subprocess.run([nvcc, "-shared", "-o", str(lib), *map(str, checked_objs)], capture_output=True,
+                                   text=True)
+                if r.returncode != 0:
+                    raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+            out["cuda_checked"] = lib
     if host_objs:
         lib = LIB_DIR / "libghostflow.so"
         newest = max(o.stat().st_mtime for o in host_objs)

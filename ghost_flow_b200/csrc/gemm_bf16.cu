@@ -639,6 +639,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (p.sc_ret) {
               const int2 rt = __ldg(p.sc_ret + row);
               if (rt.y < 0) continue;
+              if (!GF_CHECK_IDX(p.status, rt.x, p.sc_world, GF_SITE_SCATTER_RANK)) continue;
               cp = p.sc_dst[rt.x] + (long long)rt.y * p.sc_ld + col0;
             }
             if (full && ((p.ldc & 7) == 0)) {

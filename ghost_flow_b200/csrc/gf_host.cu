@@ -114,6 +114,15 @@ int attention_head_group(int heads) {
   return g;
 }
 
+static int* g_check_buffers[32] = {};
+int* check_buffer() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 32) return nullptr;
+  return g_check_buffers[dev];
+}
+void set_check_buffer(int device, int* p) {
+  if (device >= 0 && device < 32) g_check_buffers[device] = p;
+}
 }  // namespace gf
 
 // ------------------------------------------------------------------ C surface
@@ -123,6 +132,19 @@ GF_API void gf_set_device(int dev) { gf::g_device.store(dev); }
 GF_API long long gf_launch_count() { return gf::g_launches.load(); }
 
 GF_API int gf_sm_count() { return gf::sm_count(); }
+// 1 when the library was compiled with -DGF_CHECKED (data-dependent indices are range-checked on the device).
+GF_API int gf_checked_build() {
+#ifdef GF_CHECKED
+  return 1;
+#else
+  return 0;
+#endif
+}
+// status: int32[8] on `device` (word 0 = error code, words 1..7 = the report of a checked build).
+GF_API int gf_set_check_buffer(int device, int* status) {
+  gf::set_check_buffer(device, status);
+  return 0;
+}
 
 GF_API int gf_device_count() {
   int n = 0;

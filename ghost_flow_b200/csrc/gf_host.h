@@ -38,6 +38,10 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
                  CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);
 
 int sm_count();
+// Checked build: the 8-int status buffer of the current device (registered with gf_set_check_buffer), for kernels
+// whose exported signature has no status pointer. Null when none was registered.
+int* check_buffer();
+void set_check_buffer(int device, int* p);
 
 // Heads per dispatch group of the attention kernels: GF_ATT_GROUP when set (tuning), else 8, clamped to [1, heads].
 int attention_head_group(int heads);

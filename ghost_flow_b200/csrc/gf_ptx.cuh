@@ -21,7 +21,38 @@ enum : int {
   GF_ERR_WAIT_SOFTMAX = 6,
   GF_ERR_BAD_ARG = 7,
   GF_ERR_CAPACITY = 8,       // more rows were routed to this rank than its buffers hold
+  GF_ERR_BAD_INDEX = 9,      // checked build: a data-dependent index was out of range (the access was skipped)
 };
+
+// Checked build (-DGF_CHECKED, libgfb200_checked.so): every access whose index comes out of device memory (an expert
+// id, a row handed out by an atomic counter, a return address) is compared with its limit first. The first
+// offender writes {GF_ERR_BAD_INDEX, site, block, thread, index, limit} into the 8-int status buffer and the
+// access is skipped, so a corrupted table shows up as a readable report instead of a stray store into a
+// neighbour's memory. In the normal build the macro is the constant true and costs nothing.
+enum : int {
+  GF_SITE_DISPATCH_EXPERT = 1,   // moe_dispatch_kernel: routed expert id
+  GF_SITE_DISPATCH_ROW = 2,      // moe_dispatch_kernel: destination row in the owner's buffer
+  GF_SITE_SCATTER_RANK = 3,      // grouped GEMM scatter epilogue: rank of a row's return address
+  GF_SITE_COMBINE_SLOT = 4,      // moe_combine_kernel: slot row of a token
+};
+#ifdef GF_CHECKED
+__device__ __forceinline__ bool check_index(int* st, long long idx, long long limit, int site) {
+  if (idx >= 0 && idx < limit) return true;
+  if (st && atomicCAS(st, 0, GF_ERR_BAD_INDEX) == 0) {
+    st[1] = site;
+    st[2] = (int)blockIdx.x;
+    st[3] = (int)threadIdx.x;
+    st[4] = (int)(idx & 0xffffffffll);
+    st[5] = (int)(idx >> 32);
+    st[6] = (int)(limit & 0xffffffffll);
+    st[7] = (int)(limit >> 32);
+  }
+  return false;
+}
+#define GF_CHECK_IDX(st, idx, limit, site) gf::check_index((st), (long long)(idx), (long long)(limit), (site))
+#else
+#define GF_CHECK_IDX(st, idx, limit, site) (true)
+#endif
 
 #ifndef GF_WAIT_LIMIT
 #define GF_WAIT_LIMIT (1u << 22)   // polls; each poll may suspend up to ~1 us inside try_wait

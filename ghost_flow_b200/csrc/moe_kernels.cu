@@ -163,13 +163,15 @@ __global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long lo
                                     const float* __restrict__ scale, int T, int k, int K, int E, int world, int rank,
                                     int rows_cap, const int* __restrict__ send_base, int* __restrict__ cursor,
                                     int* __restrict__ dest_row, int reuse_rows, Peers bufs, Peers rets, Peers flags,
-                                    int flag_row, int epoch, int* done_counter) {
+                                    int flag_row, int epoch, int* done_counter, int* chk) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int el = E / world;
+  (void)chk;
   for (int pair = blockIdx.x * wpb + (threadIdx.x >> 5); pair < T * k; pair += gridDim.x * wpb) {
     const int t = pair / k;
     const int e = idx[pair];
+    if (!GF_CHECK_IDX(chk, e, E, GF_SITE_DISPATCH_EXPERT)) continue;
     int row;
     if (reuse_rows) {
       row = dest_row[pair];
@@ -181,6 +183,7 @@ __global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long lo
       if (lane == 0) dest_row[pair] = row;
     }
     if (row >= rows_cap) continue;            // capacity overflow is reported by the owner's plan kernel
+    if (!GF_CHECK_IDX(chk, row, rows_cap, GF_SITE_DISPATCH_ROW)) continue;   // a negative row: corrupted table
     const int owner = e / el;
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(bufs.p[owner]) + (long long)row * K;
     const __nv_bfloat16* src = x + (long long)t * ldx;
@@ -351,7 +354,8 @@ GF_API int gf_moe_dispatch(const void* x, long long ldx, const int* idx, const f
   if (grid > cap) grid = cap;
   moe_dispatch_kernel<<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, ldx, idx, scale, T, k, K, E, world, rank, rows_cap, send_base, cursor, dest_row,
-      reuse_rows, to_peers(bufs, world), to_peers(rets, world), to_peers(flags, world), flag_row, epoch, done_counter);
+      reuse_rows, to_peers(bufs, world), to_peers(rets, world), to_peers(flags, world), flag_row, epoch, done_counter,
+      gf::check_buffer());
   return cudaGetLastError() == cudaSuccess ? GFH_OK : GFH_CUDA;
 }
 

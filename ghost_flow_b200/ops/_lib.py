@@ -74,8 +74,12 @@ def _bind(lib, sigs):
     return lib
 
 
+CHECKED = os.environ.get("GF_CHECKED", "0") == "1"
+
+
 def lib_path() -> Path:
-    return _PKG / "lib" / "libgfb200.so"
+    """The kernel library; ``GF_CHECKED=1`` selects the build whose data-dependent indices are range-checked."""
+    return _PKG / "lib" / ("libgfb200_checked.so" if CHECKED else "libgfb200.so")
 
 
 def host_lib_path() -> Path:
@@ -148,8 +152,13 @@ def status_word(device=None) -> torch.Tensor:
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     t = _STATUS.get(key)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        # word 0: error code; words 1..7: {site, block, thread, index lo/hi, limit lo/hi} of a checked build's report
+        t = torch.zeros(8, dtype=torch.int32, device=dev)
         _STATUS[key] = t
+        lib = cuda_lib()
+        if hasattr(lib, "gf_set_check_buffer"):
+            lib.gf_set_check_buffer.argtypes = [c_int, c_void_p]
+            lib.gf_set_check_buffer(key, t.data_ptr())
     return t
 
 
@@ -161,7 +170,11 @@ _ERR_NAMES = {
     5: "timed out waiting for a peer flag",
     6: "timed out in the softmax hand-off",
     7: "bad argument seen on the device",
+    8: "more rows were routed to a rank than its buffers hold",
+    9: "index out of range (checked build)",
 }
+_SITES = {1: "moe_dispatch_kernel: expert id", 2: "moe_dispatch_kernel: destination row",
+          3: "grouped GEMM scatter epilogue: rank of a return address", 4: "moe_combine_kernel: slot row"}
 
 
 class KernelStatusError(RuntimeError):
@@ -172,11 +185,18 @@ def check_status(device=None, reset: bool = True) -> None:
     """Synchronises and raises if any kernel since the last check recorded an error code, or if a guard block behind
     a carve-out of an arena / workspace was overwritten (``parallel.canary``)."""
     w = status_word(device)
-    code = int(w.item())
+    rec = w.tolist()
+    code = rec[0]
     if code != 0:
         if reset:
             w.zero_()
-        raise KernelStatusError(f"ghost_flow_b200 kernel status {code}: {_ERR_NAMES.get(code, 'unknown')}")
+        detail = ""
+        if code == 9:
+            index = (rec[5] << 32) | (rec[4] & 0xFFFFFFFF)
+            limit = (rec[7] << 32) | (rec[6] & 0xFFFFFFFF)
+            detail = (f" at {_SITES.get(rec[1], f'site {rec[1]}')}, block {rec[2]}, thread {rec[3]}: index {index} "
+                      f"outside [0, {limit}); the access was skipped")
+        raise KernelStatusError(f"ghost_flow_b200 kernel status {code}: {_ERR_NAMES.get(code, 'unknown')}{detail}")
     import sys
 
     canary = sys.modules.get("ghost_flow_b200.parallel.canary")     # only if something planted guard blocks

@@ -161,7 +161,7 @@ def bounded_device_wait(pad: torch.Tensor, index: int, world: int, value: int, l
     _lib.check_rc(lib.gf_wait_flags(pad.data_ptr(), index, world, value, limit, status.data_ptr(), _lib.stream_ptr()),
                   "gf_wait_flags")
     torch.cuda.synchronize(pad.device)
-    code = int(status.item())
+    code = int(status[0].item())
     status.zero_()
     return code
 

@@ -510,7 +510,7 @@ class Zero3LlamaEngine:
         from ..ops import _lib
 
         if self._status_host is None:
-            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_host = torch.zeros(8, dtype=torch.int32).pin_memory()
             self._status_event = torch.cuda.Event()
         self._status_host.copy_(_lib.status_word(self.device), non_blocking=True)
         self._status_event.record()
