@@ -133,3 +133,75 @@ class Fp8Linear(torch.nn.Module):
         xq, xs = quantize_rows(x2, self.mode)
         y = gemm_fp8(xq, xs, self.qweight, self.scale, self.mode, self.bias)
         return y.view(*shape[:-1], self.out_features)
+
+
+# ------------------------------------------------------------------------------------------ training linear
+class _Fp8LinearFn(torch.autograd.Function):
+    """``y = x @ w^T (+ bias)`` with all three products of the layer (forward, input gradient, weight gradient) on
+    the e4m3 tensor-core kernel. Every operand of every product is quantised along its own contraction axis with one
+    scale per row (``quantize_rows`` of the operand, transposed where the contraction runs over its rows):
+
+    * forward   ``y[T,N]  = q(x)[T,K]   . q(w)[N,K]^T``    scales per token and per output feature
+    * dgrad     ``dx[T,K] = q(dy)[T,N]  . q(w^T)[K,N]^T``  scales per token and per input feature
+    * wgrad     ``dw[N,K] = q(dy^T)[N,T]. q(x^T)[K,T]^T``  scales per output feature and per input feature
+
+    Accumulation is fp32 in tensor memory; results are bf16. The bf16 master weight stays the parameter: nothing is
+    kept in fp8 between steps (the reference's fp8 mode is likewise a cast around fp32 state,
+    ghostflow-nn/src/mixed_precision.rs:29-60, 264-285)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16)
+        wq, ws = quantize_rows(w.to(torch.bfloat16), 0)
+        xq, xs = quantize_rows(x2, 0)
+        y = gemm_fp8(xq, xs, wq, ws, 0, bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
+        return y.view(*x.shape[:-1], w.shape[0]).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = quantize_rows(dy2.contiguous(), 0)
+            wtq, wts = quantize_rows(w.to(torch.bfloat16).t().contiguous(), 0)
+            dx = gemm_fp8(gq, gs, wtq, wts, 0).view(ctx.x_shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            gtq, gts = quantize_rows(dy2.t().contiguous(), 0)
+            xtq, xts = quantize_rows(x2.t().contiguous(), 0)
+            dw = gemm_fp8(gtq, gts, xtq, xts, 0).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def fp8_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Differentiable linear layer whose three GEMMs run in e4m3 (see :class:`_Fp8LinearFn`). The contraction
+    lengths (in-features, out-features, tokens) must be multiples of 16 on the GPU kernel."""
+    return _Fp8LinearFn.apply(x, w, bias)
+
+
+class Fp8TrainLinear(torch.nn.Linear):
+    """Drop-in ``nn.Linear`` whose forward and backward products are e4m3 GEMMs; parameters stay bf16 / fp32."""
+
+    def forward(self, x):
+        return fp8_linear(x, self.weight, self.bias)
+
+
+def convert_linears_to_fp8(module: torch.nn.Module, skip=("lm_head",)) -> int:
+    """Replaces every ``torch.nn.Linear`` (and subclass using ``weight`` / ``bias``) below ``module`` whose name is
+    not in ``skip`` by :class:`Fp8TrainLinear` sharing the same parameters. Returns the number of layers converted."""
+    n = 0
+    for name, child in list(module.named_children()):
+        if isinstance(child, torch.nn.Linear) and not isinstance(child, Fp8TrainLinear) and name not in skip:
+            new = Fp8TrainLinear(child.in_features, child.out_features, child.bias is not None,
+                                 device=child.weight.device, dtype=child.weight.dtype)
+            new.weight, new.bias = child.weight, child.bias
+            setattr(module, name, new)
+            n += 1
+        else:
+            n += convert_linears_to_fp8(child, skip)
+    return n

@@ -382,8 +382,12 @@ class _XentFn(torch.autograd.Function):
         # here would stall every backward pass and cannot be recorded in a CUDA graph).
         if dloss.numel() != 1:
             return g * dloss.to(g.dtype), None, None, None
-        if g.is_cuda and g.dtype == torch.bfloat16 and g.is_contiguous() and g.data_ptr() % 16 == 0:
-            _lib.check_rc(_lib.cuda_lib().gf_scale_by_dev_scalar(g.data_ptr(), g.numel(),
+        g2 = g.reshape(-1, g.shape[-1])
+        if g.is_cuda and g.dtype == torch.bfloat16 and g2.stride(1) == 1 and g2.data_ptr() == g.data_ptr() \
+                and g.data_ptr() % 16 == 0:
+            # rows may have a padded pitch: the span from the first to the last element is scaled, padding included
+            span = (g2.shape[0] - 1) * g2.stride(0) + g2.shape[1]
+            _lib.check_rc(_lib.cuda_lib().gf_scale_by_dev_scalar(g.data_ptr(), span,
                                                                  dloss.float().data_ptr(), _lib.stream_ptr()),
                           "gf_scale_by_dev_scalar")
             return g, None, None, None
