@@ -56,7 +56,7 @@ def main():
     comm = FusedComm(dev) if world > 1 else Comm()
     T = a.micro_batch * a.seq
     eng = MixtralEngine(cfg, dev, tokens_per_rank=T, optim=OptimConfig(lr=1e-4, weight_decay=0.1), comm=comm, seed=0,
-                        capacity_factor=a.capacity_factor)
+                        capacity_factor=a.capacity_factor, expert_init="device")
     g = torch.Generator().manual_seed(1 + rank)
 
     def batch():

@@ -109,7 +109,8 @@ class ExpertParallelMoE:
     arrive than fit the owner's kernel records status 8 and :func:`ghost_flow_b200.ops._lib.check_status` raises.
     """
 
-    def __init__(self, d_model, d_ff, num_experts, k, tokens, device, group=None, capacity_factor=None, seed=0):
+    def __init__(self, d_model, d_ff, num_experts, k, tokens, device, group=None, capacity_factor=None, seed=0,
+                 init_weights: bool = True):
         self.group = group
         distributed = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if distributed else 1
@@ -130,15 +131,20 @@ class ExpertParallelMoE:
         # tile-sized extents; ``gate`` and its gradient are views of the first ``num_experts`` rows
         ep_rows = (num_experts + 127) // 128 * 128
         self.gate_pad = torch.zeros(ep_rows, d_model, dtype=bf, device=self.device)
-        self.gate_pad[:num_experts] = init(num_experts, d_model, std=0.02)
         self.gate = self.gate_pad[:num_experts]
-        all13 = init(num_experts, 2 * d_ff, d_model, std=0.02)
-        all2 = init(num_experts, d_model, d_ff, std=0.02)
-        lo, hi = self.rank * self.el, (self.rank + 1) * self.el
-        self.w13, self.w2 = all13[lo:hi].contiguous(), all2[lo:hi].contiguous()
         self.gate_grad_pad = torch.zeros_like(self.gate_pad)
-        self.grads = {"gate": self.gate_grad_pad[:num_experts], "w13": torch.zeros_like(self.w13),
-                      "w2": torch.zeros_like(self.w2)}
+        if init_weights:
+            self.gate_pad[:num_experts] = init(num_experts, d_model, std=0.02)
+            all13 = init(num_experts, 2 * d_ff, d_model, std=0.02)
+            all2 = init(num_experts, d_model, d_ff, std=0.02)
+            lo, hi = self.rank * self.el, (self.rank + 1) * self.el
+            self.w13, self.w2 = all13[lo:hi].contiguous(), all2[lo:hi].contiguous()
+            self.grads = {"gate": self.gate_grad_pad[:num_experts], "w13": torch.zeros_like(self.w13),
+                          "w2": torch.zeros_like(self.w2)}
+        else:
+            # a workspace without parameters of its own: the owner points it at a layer with set_weights
+            self.w13 = self.w2 = None
+            self.grads = {}
         self.epoch = 0
         self.last_counts = None
         # One instance can serve every MoE layer of a model (its buffers are workspaces; the weights are swapped

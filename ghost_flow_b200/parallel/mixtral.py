@@ -29,18 +29,26 @@ class _ExpertState:
     """One layer's local experts and router: bf16 weights, fp32 master copies, Adam moments. The gradient buffers
     are the engine's: a layer's experts are updated as soon as its backward pass is over, so one set serves all."""
 
-    def __init__(self, moe: ExpertParallelMoE, seed: int, std: float):
+    def __init__(self, moe: ExpertParallelMoE, seed: int, std: float, init_device: str = "cpu"):
         dev = moe.device
-        g = torch.Generator(device="cpu").manual_seed(seed)
         E, el, d, f = moe.E, moe.el, moe.d, moe.f
         lo = moe.rank * el
-        # every rank draws the same full tensors and keeps its slice, so the model does not depend on the world size
-        gate = torch.randn(E, d, generator=g) * std
-        w13 = (torch.randn(E, 2 * f, d, generator=g) * std)[lo:lo + el]
-        w2 = (torch.randn(E, d, f, generator=g) * std)[lo:lo + el]
+        # One generator per expert, seeded by (layer seed, expert): a rank draws its own experts only, and an expert's
+        # weights do not depend on the world size. Drawn on the host by default (the same numbers on every device
+        # type, which the tests against the CPU engine rely on); ``init_device="device"`` draws on the GPU, which a
+        # 47 B-parameter model needs to start in seconds rather than minutes.
+        gdev = dev if (init_device == "device" and dev.type == "cuda") else torch.device("cpu")
+
+        def draw(sub_seed, *shape):
+            g = torch.Generator(device=gdev).manual_seed(seed * 4099 + sub_seed)
+            return (torch.randn(*shape, generator=g, device=gdev) * std).to(dev)
+
+        gate = draw(0, E, d)
+        w13 = torch.stack([draw(1 + 2 * e, 2 * f, d) for e in range(lo, lo + el)])
+        w2 = torch.stack([draw(2 + 2 * e, d, f) for e in range(lo, lo + el)])
         lp = torch.bfloat16 if dev.type == "cuda" else torch.float32
         self.gate_pad = torch.zeros_like(moe.gate_pad, dtype=lp)
-        self.master = {"gate": gate.to(dev), "w13": w13.contiguous().to(dev), "w2": w2.contiguous().to(dev)}
+        self.master = {"gate": gate, "w13": w13, "w2": w2}
         self.gate_pad[:E] = self.master["gate"].to(self.gate_pad.dtype)
         self.w13 = self.master["w13"].to(lp) if lp != torch.float32 else self.master["w13"].clone()
         self.w2 = self.master["w2"].to(lp) if lp != torch.float32 else self.master["w2"].clone()
@@ -61,7 +69,7 @@ class MixtralEngine(Zero3LlamaEngine):
 
     def __init__(self, cfg: MixtralConfig, device, tokens_per_rank: int, optim: OptimConfig | None = None, group=None,
                  seed: int = 0, dtype=torch.bfloat16, comm: Comm | None = None, capacity_factor: float | None = None,
-                 persist_gathered: bool | None = None):
+                 persist_gathered: bool | None = None, expert_init: str = "cpu"):
         super().__init__(cfg, device, optim=optim, group=group, seed=seed, dtype=dtype, comm=comm,
                          persist_gathered=persist_gathered)
         if self.opt.max_grad_norm is not None:
@@ -70,12 +78,12 @@ class MixtralEngine(Zero3LlamaEngine):
         cf = capacity_factor if capacity_factor is not None else (cfg.capacity_factor or 2.0)
         self.moe = ExpertParallelMoE(cfg.hidden_size, cfg.intermediate_size, E, k, tokens_per_rank, self.device,
                                      group=self.comm.group, capacity_factor=min(float(cf), float(self.world)) if self.world > 1 else 1.0,
-                                     seed=seed)
+                                     seed=seed, init_weights=False)
         self.moe.keep_slot_outputs = True
         # the loss is a mean over the ranks, and so is its auxiliary part: every rank adds coef / world of its own
         self.moe.aux_coef = float(cfg.router_aux_loss_coef) / self.world
         self.tokens_per_rank = tokens_per_rank
-        self.experts = [_ExpertState(self.moe, seed * 7919 + 31 * i + 1, cfg.initializer_range)
+        self.experts = [_ExpertState(self.moe, seed * 7919 + 31 * i + 1, cfg.initializer_range, expert_init)
                         for i in range(cfg.num_hidden_layers)]
         e0 = self.experts[0]
         self.gate_grad_pad = torch.zeros_like(e0.gate_pad)
