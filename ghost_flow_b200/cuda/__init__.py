@@ -344,7 +344,7 @@ class LaunchConfig:
 KERNELS = {
     "add": "gf_binary", "mul": "gf_binary", "relu": "gf_unary", "gelu": "gf_unary", "sigmoid": "gf_unary",
     "matmul": "gf_gemm_bf16", "matmul_tiled": "gf_gemm_bf16", "matmul_tensor_core": "gf_gemm_bf16",
-    "flash_attention_forward": "gf_flash_attn_fwd2", "flash_attention_backward": "gf_flash_attn_bwd",
+    "flash_attention_forward": "gf_flash_attn_fwd3", "flash_attention_backward": "gf_flash_attn_bwd2",
     "sum_reduce": "gf_reduce", "max_reduce": "gf_reduce", "softmax": "gf_softmax_rows",
     "cross_entropy": "gf_xent_fused", "layer_norm": "gf_layernorm_fwd", "rms_norm": "gf_rmsnorm_fwd",
     "batch_norm": "gf_batchnorm_train",
