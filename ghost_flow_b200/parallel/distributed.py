@@ -310,9 +310,18 @@ class ZeRoStats:
     grad_bytes_per_rank: int
     optimizer_bytes_per_rank: int
     offloaded_bytes: int = 0
+    # what this implementation keeps allocated on the rank (see ZeRoOptimizer: the flat parameter and gradient
+    # buckets stay whole at every stage; only the optimizer state is sharded)
+    resident_param_bytes: int = 0
+    resident_grad_bytes: int = 0
+
+    def resident_bytes(self) -> int:
+        return self.resident_param_bytes + self.resident_grad_bytes + self.optimizer_bytes_per_rank
 
     def memory_savings_ratio(self) -> float:
-        """Bytes of the unsharded mixed-precision state (2 + 2 + 12 per parameter) over this rank's share."""
+        """Bytes of the unsharded mixed-precision state (2 + 2 + 12 per parameter) over this rank's share as the
+        STAGE defines it (the reference's formula, ghostflow-nn/src/zero_optimizer.rs:344-368). What this
+        implementation really holds is :meth:`resident_bytes`."""
         base = self.total_params * 16
         mine = self.param_bytes_per_rank + self.grad_bytes_per_rank + self.optimizer_bytes_per_rank
         return base / max(1, mine)
@@ -325,9 +334,14 @@ class ZeRoOptimizer:
     All trainable parameters are laid into flat buckets of at most ``bucket_size`` elements, padded to a multiple
     of the world size; rank r owns the r-th slice of every bucket: its fp32 master copy and both moments live
     only there. ``step()``: reduce-scatter of each gradient bucket (mean), fused AdamW on the owned slice (one
-    kernel: fp32 update + low-precision copy), all-gather of the updated slices. Stage 2 frees the gradient
-    buckets between steps except for the owned slice; stage 3 additionally keeps only the owned parameter slice
-    between steps (``gather_parameters`` / ``release_parameters`` bracket forward+backward).
+    kernel: fp32 update + low-precision copy), all-gather of the updated slices.
+
+    The stages differ in what they are ALLOWED to drop, not in what this class drops: the flat parameter and
+    gradient buckets stay allocated whole at every stage (parameters and ``.grad`` are views of them, which is what
+    lets the collectives and the fused kernels run on single flat tensors), so the memory this class saves is the
+    optimizer state (12 of 16 bytes per parameter), i.e. stage 1. ``get_stats()`` reports both the stage's nominal
+    share (the reference's formula) and the bytes really resident. The engine that shards parameters and gradients
+    for real is :class:`~ghost_flow_b200.parallel.zero3.Zero3LlamaEngine`.
     """
 
     # signal-pad layout of the fused path (int32 indices, 8 per bucket, one slot per writer rank)
@@ -364,6 +378,7 @@ class ZeRoOptimizer:
         self.overlap = (cuda and self.world > 1) if overlap is None else (bool(overlap) and cuda)
         self.capturable = bool(capturable) and cuda
         self._sync_hooks = True
+        self._flag_epoch = 0
         self._open = False
         self._launched: set = set()
         self._side = torch.cuda.Stream(self.params[0].device) if self.overlap else None
@@ -431,6 +446,7 @@ class ZeRoOptimizer:
             return
         self._open = True
         self.step_count += 1
+        self._flag_epoch += 1          # flag values of the fused path: launches of this object, never set back
         if self.capturable:
             from ..ops import _lib
 
@@ -559,10 +575,10 @@ class ZeRoOptimizer:
         W, R = self.world, self.rank
         # flag values: the step number; in capturable mode the launch carries 0 and the device counter adds it
         ep = self._step_dev.data_ptr() if self.capturable else None
-        t = 0 if self.capturable else self.step_count
+        t = 0 if self.capturable else self._flag_epoch
         status, stream = _lib.status_word(fc.device).data_ptr(), _lib.stream_ptr()
         # waits give up after about 2 s; the first step gets about 13 s, since ranks reach it with start-up skew
-        limit = (1 << 27) if self.step_count == 1 else 0
+        limit = (1 << 27) if self._flag_epoch == 1 else 0
         with torch.cuda.device(fc.device):
             _lib.check_rc(fc.lib.gf_signal_peers_ep(fc.pad_ptrs, W, R, self._PAD_READY + 8 * i, t, ep, stream),
                           "gf_signal_peers")
@@ -586,8 +602,8 @@ class ZeRoOptimizer:
 
         fc = self._fc
         ep = self._step_dev.data_ptr() if self.capturable else None
-        t = 0 if self.capturable else self.step_count
-        limit = (1 << 27) if self.step_count == 1 else 0
+        t = 0 if self.capturable else self._flag_epoch
+        limit = (1 << 27) if self._flag_epoch == 1 else 0
         status, stream = _lib.status_word(fc.device).data_ptr(), _lib.stream_ptr()
         with torch.cuda.device(fc.device):
             for i in range(len(self.buckets)):
@@ -650,9 +666,11 @@ class ZeRoOptimizer:
         st = self.config.stage
         off = sum(b[k].numel() * 4 for b in self.buckets for k in ("master", "m", "v") if not b[k].is_cuda
                   and self.buckets[0]["flat_p"].is_cuda)
+        padded = sum(b["padded"] for b in self.buckets)
         return ZeRoStats(st, self.world, total, owned,
                          (owned if st >= ZeRoStage.Stage3 else total) * esz,
-                         (owned if st >= ZeRoStage.Stage2 else total) * esz, owned * 12, off)
+                         (owned if st >= ZeRoStage.Stage2 else total) * esz, owned * 12, off,
+                         resident_param_bytes=padded * esz, resident_grad_bytes=padded * esz)
 
     def memory_savings_ratio(self) -> float:
         return self.get_stats().memory_savings_ratio()
@@ -662,6 +680,11 @@ class ZeRoOptimizer:
                 "buckets": [{k: b[k].detach().cpu() for k in ("master", "m", "v")} for b in self.buckets]}
 
     def load_state_dict(self, sd):
+        if self.capturable:
+            # the device counter is both Adam's step number and the flag value of the fused path: it may only grow
+            if self._fc is not None and int(sd["step"]) < self.step_count:
+                raise RuntimeError("a capturable fused optimizer cannot go back to an earlier step; load into a new one")
+            self._step_dev.fill_(int(sd["step"]))
         self.step_count = sd["step"]
         for b, s in zip(self.buckets, sd["buckets"]):
             for k in ("master", "m", "v"):
