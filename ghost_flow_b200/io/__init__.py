@@ -149,6 +149,48 @@ class Checkpoint:
     extra: dict = field(default_factory=dict)
 
 
+@dataclass
+class ModelMetadata:
+    """Metadata block of a checkpoint (ghostflow-nn/src/serialization.rs:27-50)."""
+    name: str = "model"
+    version: str = "1.0.0"
+    framework_version: str = "0.4.0"
+    epoch: int = 0
+    loss: float = 0.0
+    extra: dict = field(default_factory=dict)
+
+
+@dataclass
+class ModelCheckpoint:
+    """The reference's checkpoint object (ghostflow-nn/src/serialization.rs:12-25): parameters, metadata and an
+    optional optimizer state, with ``save`` / ``load`` on the GFCP format. :class:`Checkpoint` is the flat record the
+    rest of this package passes around; the two convert into each other."""
+    parameters: dict
+    metadata: ModelMetadata = field(default_factory=ModelMetadata)
+    optimizer_state: dict | None = None
+
+    def with_optimizer_state(self, state: dict) -> "ModelCheckpoint":
+        self.optimizer_state = dict(state)
+        return self
+
+    def to_checkpoint(self) -> "Checkpoint":
+        m = self.metadata
+        return Checkpoint(self.parameters, self.optimizer_state, m.epoch, m.loss, m.name, m.version,
+                          m.framework_version, dict(m.extra))
+
+    @classmethod
+    def from_checkpoint(cls, ck: "Checkpoint") -> "ModelCheckpoint":
+        return cls(ck.parameters, ModelMetadata(ck.model_name, ck.version, ck.framework_version, ck.epoch, ck.loss,
+                                                dict(ck.extra)), ck.optimizer_state)
+
+    def save(self, path) -> None:
+        save_checkpoint(self.to_checkpoint(), path)
+
+    @classmethod
+    def load(cls, path) -> "ModelCheckpoint":
+        return cls.from_checkpoint(load_checkpoint(path))
+
+
 def save_checkpoint(ckpt: Checkpoint, path) -> None:
     lib = _lib_io()
     n, names, ndims, dims, data, keep = _pack(ckpt.parameters)

@@ -14,7 +14,7 @@ from .multimodal import (  # noqa: F401
 from .geometry import (  # noqa: F401
     ActorCriticAgent, DQNAgent, FarthestPointSampler, GATLayer, GCNLayer, Graph, GraphSAGELayer, KNNGrouper, Mesh,
     MeshConv, MeshEncoder, MeshPool, MeshUtils, MPNNLayer, PointNet, PointNetBackbone, PointNetConfig, PolicyNetwork,
-    PPOAgent, QNetwork, REINFORCEAgent, ReplayBuffer, SAGEAggregator, STN3d, ValueNetwork,
+    Experience, PPOAgent, QNetwork, REINFORCEAgent, ReplayBuffer, SAGEAggregator, STN3d, ValueNetwork,
 )
 from .vision import (  # noqa: F401
     VGG, BasicBlock, Bottleneck, ChannelsLastEngine, InvertedResidual, MobileNetV2, ResNet, resnet18, resnet34,

@@ -333,11 +333,25 @@ class MPNNLayer(Module):
 
 
 # =========================================================================== reinforcement learning
+@dataclass
+class Experience:
+    """One transition of a replay buffer (ghostflow-nn/src/rl.rs:21-28)."""
+    state: torch.Tensor
+    action: int
+    reward: float
+    next_state: torch.Tensor
+    done: bool
+
+
 class ReplayBuffer:
     def __init__(self, capacity: int):
         self.capacity, self.data, self.pos = capacity, [], 0
 
-    def push(self, state, action, reward, next_state, done):
+    def push(self, state, action=None, reward=None, next_state=None, done=None):
+        """``push(Experience(...))`` or ``push(state, action, reward, next_state, done)``."""
+        if isinstance(state, Experience):
+            state, action, reward, next_state, done = (state.state, state.action, state.reward, state.next_state,
+                                                       state.done)
         item = (torch.as_tensor(state, dtype=torch.float32), int(action), float(reward),
                 torch.as_tensor(next_state, dtype=torch.float32), float(done))
         if len(self.data) < self.capacity:

@@ -32,7 +32,7 @@ from .mixed_precision import (  # noqa: F401
 from .techniques import (  # noqa: F401
     CheckpointConfig, CheckpointedLayer, CheckpointedSequential, CheckpointManager, CheckpointStats,
     CheckpointStrategy, CurriculumConfig, CurriculumLearning, CurriculumStats, CurriculumStrategy,
-    DifficultyScorer, DistillationConfig, DistillationMethod, DistillationStats, DynamicQuantization,
+    DifficultyMetric, DifficultyScorer, DistillationConfig, DistillationMethod, DistillationStats, DynamicQuantization,
     KnowledgeDistillation, LoRAConfig, LoRALinear, PacingFunction, PrefixTuning, PrefixTuningConfig, PromptInit,
     PromptTuning, PromptTuningConfig, PTuningV2, QLoRAConfig, QLoRALinear, QuantizationAwareTraining,
     QuantizationConfig, QuantizationScheme, QuantizedTensor, estimate_memory_savings,

@@ -476,6 +476,14 @@ class CurriculumStrategy(enum.Enum):
     AntiCurriculum = "anti_curriculum"
 
 
+class DifficultyMetric(enum.Enum):
+    """How a sample's difficulty is scored (ghostflow-nn/src/curriculum_learning.rs:27-38)."""
+    Loss = "loss"
+    Confidence = "confidence"      # difficulty = 1 - confidence of the prediction
+    Complexity = "complexity"      # length / feature count handed in by the caller
+    Custom = "custom"              # user function
+
+
 class PacingFunction(enum.Enum):
     Linear = "linear"
     Exponential = "exponential"
@@ -486,7 +494,7 @@ class PacingFunction(enum.Enum):
 @dataclass
 class CurriculumConfig:
     strategy: CurriculumStrategy = CurriculumStrategy.Fixed
-    metric: str = "loss"
+    metric: str = "loss"                      # or a DifficultyMetric (``difficulty_metric`` is the reference's name)
     initial_threshold: float = 0.3
     final_threshold: float = 1.0
     warmup_epochs: int = 10
@@ -503,6 +511,10 @@ class CurriculumConfig:
                                          final_threshold=0.0)
 
 
+CurriculumConfig.difficulty_metric = property(
+    lambda self: DifficultyMetric(self.metric.value if isinstance(self.metric, DifficultyMetric) else self.metric))
+
+
 @dataclass
 class CurriculumStats:
     epoch: int = 0
@@ -514,13 +526,19 @@ class CurriculumStats:
 class DifficultyScorer:
     """Scores samples in [0, 1]: normalised loss, sequence length or a user function."""
 
-    def __init__(self, metric: str = "loss", fn=None):
-        self.metric, self.fn = metric, fn
+    def __init__(self, metric="loss", fn=None):
+        self.metric = metric.value if isinstance(metric, DifficultyMetric) else metric
+        self.fn = fn
+        if self.metric == "custom" and fn is None:
+            raise ValueError("DifficultyMetric.Custom needs a scoring function")
 
     def score(self, values):
-        v = torch.as_tensor(values, dtype=torch.float32)
         if self.fn is not None:
             v = torch.as_tensor([self.fn(x) for x in values], dtype=torch.float32)
+        else:
+            v = torch.as_tensor(values, dtype=torch.float32)
+        if self.metric == "confidence":
+            v = 1.0 - v                                   # a confident prediction is an easy sample
         lo, hi = v.min(), v.max()
         return (v - lo) / (hi - lo).clamp(min=1e-12)
 

@@ -37,6 +37,9 @@ class _Scheduler:
         self._opt.set_lr(self._lr_at(self.current_step) if self.current_step else self.base_lr)
 
 
+LRScheduler = _Scheduler     # the reference's trait name (ghostflow-optim/src/scheduler.rs:6-9): step() and get_lr()
+
+
 class StepLR(_Scheduler):
     def __init__(self, optimizer, step_size: int, gamma: float = 0.1):
         super().__init__(optimizer)

@@ -327,6 +327,20 @@ class ZeRoStats:
         return base / max(1, mine)
 
 
+@dataclass
+class ParameterPartition:
+    """Where one parameter lives in the flat partitioning (ghostflow-nn/src/zero_optimizer.rs:96-108). Buckets are
+    cut by element ranges, so a tensor can straddle two owners: ``owner_rank`` owns its first element, ``owners``
+    lists every rank that owns a part of it."""
+    name: str
+    owner_rank: int
+    start_idx: int          # first element in the flat bucket
+    end_idx: int            # one past the last element
+    shape: tuple
+    bucket: int = 0
+    owners: tuple = ()
+
+
 class ZeRoOptimizer:
     """AdamW with ZeRO partitioning over flat element ranges (not whole tensors as in the reference, whose owner
     map depends on hash-map order).
@@ -533,6 +547,21 @@ class ZeRoOptimizer:
     def partition_parameters(self):
         """[(bucket, first element, last element)] owned by this rank."""
         return [(i, self.rank * b["shard"], (self.rank + 1) * b["shard"]) for i, b in enumerate(self.buckets)]
+
+    def parameter_partitions(self, names=None) -> list:
+        """One :class:`ParameterPartition` per parameter, in bucket order. ``names``: optional list of names in the
+        order the parameters were given (defaults to ``param<i>``)."""
+        out, k = [], 0
+        for bi, b in enumerate(self.buckets):
+            off = 0
+            for p in b["params"]:
+                lo, hi = off, off + p.numel()
+                first, last = lo // b["shard"], (hi - 1) // b["shard"]
+                out.append(ParameterPartition(names[k] if names else f"param{k}", first, lo, hi, tuple(p.shape), bi,
+                                              tuple(range(first, last + 1))))
+                off = hi
+                k += 1
+        return out
 
     def owns(self, bucket: int, element: int) -> bool:
         b = self.buckets[bucket]

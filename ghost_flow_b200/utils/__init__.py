@@ -189,6 +189,25 @@ class MemoryStats:
         return self.reused_allocations / self.total_allocations if self.total_allocations else 0.0
 
 
+@dataclass
+class AllocationStats:
+    """Counters of a tracked allocator (ghostflow-core/src/memory.rs:214-239)."""
+    allocations: int = 0
+    deallocations: int = 0
+    total_allocated: int = 0
+    current_allocated: int = 0
+    peak_allocated: int = 0
+
+    def current_mb(self) -> float:
+        return self.current_allocated / (1024.0 * 1024.0)
+
+    def peak_mb(self) -> float:
+        return self.peak_allocated / (1024.0 * 1024.0)
+
+    def total_mb(self) -> float:
+        return self.total_allocated / (1024.0 * 1024.0)
+
+
 class MemoryPool:
     """Size-bucketed (power of two) reuse of pinned host staging buffers."""
 
@@ -231,15 +250,23 @@ class TrackedAllocator:
 
     def __init__(self):
         self.allocations, self.deallocations, self.bytes_allocated = 0, 0, 0
+        self._current = self._peak = 0
 
     def allocate(self, shape, dtype=torch.float32, device="cpu"):
         t = torch.empty(shape, dtype=dtype, device=device)
         self.allocations += 1
-        self.bytes_allocated += t.numel() * t.element_size()
+        n = t.numel() * t.element_size()
+        self.bytes_allocated += n
+        self._current += n
+        self._peak = max(self._peak, self._current)
         return t
 
     def free(self, t):
         self.deallocations += 1
+        self._current -= t.numel() * t.element_size()
+
+    def allocation_stats(self) -> AllocationStats:
+        return AllocationStats(self.allocations, self.deallocations, self.bytes_allocated, self._current, self._peak)
 
     def stats(self):
         return {"allocations": self.allocations, "deallocations": self.deallocations,

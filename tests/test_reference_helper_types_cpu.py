@@ -1,0 +1,65 @@
+"""Small public types of the reference that other code passes around: checkpoint object and metadata, parameter
+partition records, the scheduler base, allocation statistics, difficulty metrics, replay-buffer experiences."""
+import torch
+
+import ghost_flow_b200 as gf
+from ghost_flow_b200 import io as gio
+from ghost_flow_b200.models import Experience, ReplayBuffer
+from ghost_flow_b200.nn import CurriculumConfig, DifficultyMetric, DifficultyScorer
+from ghost_flow_b200.optim import SGD, LRScheduler, StepLR
+from ghost_flow_b200.parallel.distributed import ParameterPartition, ZeRoConfig, ZeRoOptimizer
+from ghost_flow_b200.utils import AllocationStats, TrackedAllocator
+
+
+def test_model_checkpoint_round_trip(tmp_path):
+    params = {"fc.weight": torch.randn(4, 3), "fc.bias": torch.randn(4)}
+    ck = gio.ModelCheckpoint(params, gio.ModelMetadata(name="mlp", epoch=7, loss=0.25, extra={"lr": "0.01"}))
+    ck.with_optimizer_state({"fc.weight.exp_avg": torch.ones(12)})
+    path = tmp_path / "m.gfcp"
+    ck.save(path)
+    back = gio.ModelCheckpoint.load(path)
+    assert back.metadata.name == "mlp" and back.metadata.epoch == 7 and abs(back.metadata.loss - 0.25) < 1e-7
+    assert back.metadata.extra["lr"] == "0.01"
+    assert torch.equal(back.parameters["fc.weight"], params["fc.weight"])
+    assert torch.equal(back.optimizer_state["fc.weight.exp_avg"], torch.ones(12))
+
+
+def test_parameter_partitions_cover_every_element_once():
+    ps = [torch.nn.Parameter(torch.randn(10, 7)), torch.nn.Parameter(torch.randn(33)),
+          torch.nn.Parameter(torch.randn(5, 5))]
+    opt = ZeRoOptimizer(ps, ZeRoConfig(bucket_size=80))
+    parts = opt.parameter_partitions(["a", "b", "c"])
+    assert [p.name for p in parts] == ["a", "b", "c"] and all(isinstance(p, ParameterPartition) for p in parts)
+    assert parts[0].shape == (10, 7) and parts[0].end_idx - parts[0].start_idx == 70
+    assert parts[1].bucket == 1 and parts[1].start_idx == 0          # 70 + 33 > 80: a new bucket
+    assert all(p.owner_rank == 0 and p.owners == (0,) for p in parts)  # one rank owns everything
+
+
+def test_scheduler_base_and_allocation_stats():
+    w = torch.nn.Parameter(torch.zeros(2))
+    sched = StepLR(SGD([w], lr=0.1), step_size=2, gamma=0.5)
+    assert isinstance(sched, LRScheduler)
+    for _ in range(2):
+        sched.step()
+    assert abs(sched.get_lr() - 0.05) < 1e-9
+    alloc = TrackedAllocator()
+    a = alloc.allocate((256, 1024))
+    b = alloc.allocate((512, 1024))
+    alloc.free(a)
+    st = alloc.allocation_stats()
+    assert isinstance(st, AllocationStats) and st.allocations == 2 and st.deallocations == 1
+    assert st.peak_mb() == 3.0 and st.current_mb() == 2.0 and st.total_mb() == 3.0
+    del b
+
+
+def test_difficulty_metric_and_experience():
+    assert CurriculumConfig(metric="loss").difficulty_metric is DifficultyMetric.Loss
+    conf = DifficultyScorer(DifficultyMetric.Confidence).score([0.9, 0.5, 0.1])
+    assert conf[0] < conf[1] < conf[2]                    # the confident sample is the easy one
+    custom = DifficultyScorer(DifficultyMetric.Custom, fn=len).score(["ab", "abcd", "a"])
+    assert custom.argmax() == 1
+    buf = ReplayBuffer(4)
+    buf.push(Experience(torch.zeros(3), 1, 0.5, torch.ones(3), False))
+    buf.push(torch.ones(3), 2, -1.0, torch.zeros(3), True)
+    s, a, r, s2, d = buf.sample(2)
+    assert s.shape == (2, 3) and sorted(a.tolist()) == [1, 2] and gf is not None
