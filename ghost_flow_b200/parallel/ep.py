@@ -152,6 +152,9 @@ class ExpertParallelMoE:
         # workspace into the layer's context.
         self.keep_slot_outputs = False
         self.aux_coef = 0.0
+        # backward adds into ``grads`` (several micro-batches per step) unless this is False: then it overwrites them,
+        # which saves zeroing and re-reading 1.4 GB of expert gradients per Mixtral-sized layer
+        self.accumulate_grads = True
         if self.device.type == "cuda":
             self._alloc()
 
@@ -289,10 +292,11 @@ class ExpertParallelMoE:
         wait = (src_start, self.flags[FLAG_DISPATCH * 8:], W, ep)
         da = torch.empty(R, f, dtype=torch.bfloat16, device=dev)
         grouped_gemm(self.dys, self.w2, da, 1, seg, self.el, rows_cap=R, N=f, K=d, b_mn=True, wait=wait)
-        grouped_gemm(self.dys, ctx.a, self.grads["w2"], 2, seg, self.el, rows_cap=R, M=d, N=f, K=R, accumulate=True)
+        acc = self.accumulate_grads
+        grouped_gemm(self.dys, ctx.a, self.grads["w2"], 2, seg, self.el, rows_cap=R, M=d, N=f, K=R, accumulate=acc)
         dh = raw.swiglu_bwd(ctx.h, da)
         # padding rows of h are zero, so dh is zero there as well and the weight gradient ignores them
-        grouped_gemm(dh, xs, self.grads["w13"], 2, seg, self.el, rows_cap=R, M=2 * f, N=d, K=R, accumulate=True)
+        grouped_gemm(dh, xs, self.grads["w13"], 2, seg, self.el, rows_cap=R, M=2 * f, N=d, K=R, accumulate=acc)
         grouped_gemm(dh, self.w13, self.dcomb, 1, seg, self.el, rows_cap=R, N=d, K=2 * f, b_mn=True,
                      scatter=(ret, self.p["dcomb"], self._flag_ptrs(FLAG_COMBINE), d, self.rank, W, ep,
                               self.done[1:]))
@@ -305,7 +309,7 @@ class ExpertParallelMoE:
         dl = torch.zeros(T, self.gate_pad.shape[0], dtype=torch.bfloat16, device=dev)
         dl[:, :E] = dlogits
         raw.gemm(dl, False, self.gate_pad, False, out=dx, accumulate=True)
-        raw.gemm(dl, True, ctx.x, False, out=self.gate_grad_pad, accumulate=True)
+        raw.gemm(dl, True, ctx.x, False, out=self.gate_grad_pad, accumulate=acc)
         return dx
 
     @staticmethod
@@ -385,9 +389,11 @@ class ExpertParallelMoE:
         xr, y, aux, leaves = ctx
         total = (y * dy.float()).sum() + self.aux_coef * aux
         gx, gg, g13, g2 = torch.autograd.grad(total, [xr, *leaves])
-        self.grads["gate"] += gg.to(self.grads["gate"].dtype)
-        self.grads["w13"] += g13.to(self.grads["w13"].dtype)
-        self.grads["w2"] += g2.to(self.grads["w2"].dtype)
+        for name, g in (("gate", gg), ("w13", g13), ("w2", g2)):
+            if self.accumulate_grads:
+                self.grads[name] += g.to(self.grads[name].dtype)
+            else:
+                self.grads[name].copy_(g.to(self.grads[name].dtype))
         return gx.to(dy.dtype)
 
     # ------------------------------------------------------------------ autograd wrapper

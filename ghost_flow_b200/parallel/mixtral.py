@@ -80,6 +80,7 @@ class MixtralEngine(Zero3LlamaEngine):
                                      group=self.comm.group, capacity_factor=min(float(cf), float(self.world)) if self.world > 1 else 1.0,
                                      seed=seed, init_weights=False)
         self.moe.keep_slot_outputs = True
+        self.moe.accumulate_grads = False      # one backward pass per step: gradients are written, not added
         # the loss is a mean over the ranks, and so is its auxiliary part: every rank adds coef / world of its own
         self.moe.aux_coef = float(cfg.router_aux_loss_coef) / self.world
         self.tokens_per_rank = tokens_per_rank
@@ -114,9 +115,6 @@ class MixtralEngine(Zero3LlamaEngine):
     def _layer_bwd(self, w, g, saved, dout, B, S, layer_index: int = 0):
         sa, x2, rstd2, ctx = saved
         self._use(layer_index)
-        self.gate_grad_pad.zero_()
-        self.g13.zero_()
-        self.g2.zero_()
         dh2 = self.moe.backward(ctx, dout.contiguous())
         dx2, _ = K.rmsnorm_bwd(x2, w["ffn_norm"], dh2.to(x2.dtype), rstd2, dres=dout, dw_out=g["ffn_norm"])
         self._update_experts(layer_index)
