@@ -12,7 +12,7 @@ from .multimodal import (  # noqa: F401
     PositionalEncoder, RaySampler, ResidualBlock, UNet, VolumeRenderer,
 )
 from .geometry import (  # noqa: F401
-    ActorCriticAgent, DQNAgent, FarthestPointSampler, GATLayer, GCNLayer, Graph, GraphSAGELayer, KNNGrouper, Mesh,
+    ActorCriticAgent, AggregatorType, DQNAgent, FarthestPointSampler, GATLayer, GCNLayer, Graph, GraphSAGELayer, KNNGrouper, Mesh,
     MeshConv, MeshEncoder, MeshPool, MeshUtils, MPNNLayer, PointNet, PointNetBackbone, PointNetConfig, PolicyNetwork,
     Experience, PPOAgent, QNetwork, REINFORCEAgent, ReplayBuffer, SAGEAggregator, STN3d, ValueNetwork,
 )

@@ -284,7 +284,11 @@ class GATLayer(Module):
 class SAGEAggregator(enum.Enum):
     Mean = "mean"
     Max = "max"
+    Pool = "max"          # the reference's name for the max-pooling aggregator (ghostflow-nn/src/gnn.rs:224-228)
     LSTM = "lstm"
+
+
+AggregatorType = SAGEAggregator
 
 
 class GraphSAGELayer(Module):

@@ -33,8 +33,8 @@ from .techniques import (  # noqa: F401
     CheckpointConfig, CheckpointedLayer, CheckpointedSequential, CheckpointManager, CheckpointStats,
     CheckpointStrategy, CurriculumConfig, CurriculumLearning, CurriculumStats, CurriculumStrategy,
     DifficultyMetric, DifficultyScorer, DistillationConfig, DistillationMethod, DistillationStats, DynamicQuantization,
-    KnowledgeDistillation, LoRAConfig, LoRALinear, PacingFunction, PrefixTuning, PrefixTuningConfig, PromptInit,
-    PromptTuning, PromptTuningConfig, PTuningV2, QLoRAConfig, QLoRALinear, QuantizationAwareTraining,
+    KnowledgeDistillation, LoRAConfig, LoRALinear, PacingFunction, LayerPrefix, PrefixTuning, PrefixTuningConfig, PromptInit, PromptInitStrategy,
+    PromptTuning, PromptTuningConfig, PTuningV2, QLoRAConfig, QLoRALinear, QuantType, QuantizationAwareTraining, ScoredSample,
     QuantizationConfig, QuantizationScheme, QuantizedTensor, estimate_memory_savings,
 )
 from .moe import Expert, MixtureOfExperts, MoEConfig, MoEStats, Router, RoutingStrategy  # noqa: F401
@@ -45,6 +45,6 @@ from .privacy import (  # noqa: F401
     RandomizedSmoothing, SecureAggregation,
 )
 from .inference import (  # noqa: F401
-    BatchInference, CudaGraphRunner, InferenceConfig, InferenceOptimizer, InferenceSession, ONNXAttribute, ONNXGraph, ONNXModel,
-    ONNXNode, ONNXTensor, onnx_to_tensor, tensor_to_onnx, warmup_model,
+    BatchInference, CudaGraphRunner, FusedOp, InferenceConfig, InferenceOptimizer, InferenceSession, ONNXAttribute, ONNXGraph, ONNXModel,
+    ONNXDataType, ONNXNode, ONNXTensor, onnx_to_tensor, tensor_to_onnx, warmup_model,
 )

@@ -11,6 +11,7 @@ through ``torch.onnx``.
 """
 from __future__ import annotations
 
+import enum
 import struct
 import time
 from dataclasses import dataclass, field
@@ -31,10 +32,22 @@ class InferenceConfig:
     use_cuda_graph: bool = False     # replay CUDA inputs from a captured graph (see CudaGraphRunner)
 
 
+@dataclass
+class FusedOp:
+    """A fusion the optimizer performed: its name and the operators it replaced
+    (ghostflow-nn/src/inference.rs:45-50; there the list is a fixed announcement, here it records what was done)."""
+    name: str
+    ops: list
+
+
 class InferenceOptimizer:
     def __init__(self, config: InferenceConfig | None = None):
         self.config = config or InferenceConfig()
         self.applied: list[str] = []
+        self.fused_ops: list = []
+
+    def get_fused_ops(self) -> list:
+        return list(self.fused_ops)
 
     @torch.no_grad()
     def optimize(self, model: torch.nn.Module) -> torch.nn.Module:
@@ -64,6 +77,8 @@ class InferenceOptimizer:
                 a.bias = torch.nn.Parameter(new_bias)
                 self._replace(module, n2, torch.nn.Identity())
                 self.applied.append(f"fold_bn:{n1}+{n2}")
+                self.fused_ops.append(FusedOp("ConvBN" if a.weight.dim() == 4 else "LinearBN",
+                                              [type(a).__name__, type(b).__name__]))
         for _, child in module.named_children():
             self._fold_bn(child)
 
@@ -228,14 +243,31 @@ def warmup_model(fn, input_shape, iterations: int = 10, device=None) -> float:
 
 
 # ------------------------------------------------------------------------------------------- legacy "ONNX" container
+class ONNXDataType(enum.Enum):
+    """Element types of the container (ghostflow-nn/src/onnx.rs:11-19)."""
+    Float32 = "float32"
+    Float64 = "float64"
+    Int32 = "int32"
+    Int64 = "int64"
+    Uint8 = "uint8"
+
+    def torch_dtype(self):
+        return getattr(torch, self.value)
+
+
 @dataclass
 class ONNXTensor:
     name: str
     dims: list
     data: list
+    dtype: "ONNXDataType" = None
+
+    def __post_init__(self):
+        if self.dtype is None:
+            self.dtype = ONNXDataType.Float32
 
     def to_tensor(self):
-        return torch.tensor(self.data, dtype=torch.float32).reshape(self.dims)
+        return torch.tensor(self.data, dtype=self.dtype.torch_dtype()).reshape(self.dims)
 
 
 @dataclass

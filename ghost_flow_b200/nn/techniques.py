@@ -169,6 +169,27 @@ _NF4 = torch.tensor([-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748
                      0.7229568362236023, 1.0])
 
 
+# the sixteen e2m1 values (sign, 2 exponent bits, 1 mantissa bit) scaled to [-1, 1]
+_FP4 = torch.tensor(sorted({s * v / 6.0 for s in (-1.0, 1.0) for v in (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)})
+                    + [1.0])[:16]
+
+
+class QuantType(enum.Enum):
+    """Storage format of a frozen QLoRA base weight (ghostflow-nn/src/lora.rs:187-196): a code book of values in
+    [-1, 1] indexed by the stored code, times the per-block absmax. NF4 = the sixteen normal-float quantiles,
+    FP4 = the e2m1 values, INT8 = 255 evenly spaced levels (symmetric int8)."""
+    NF4 = "nf4"
+    FP4 = "fp4"
+    INT8 = "int8"
+
+    def code_book(self) -> torch.Tensor:
+        if self is QuantType.NF4:
+            return _NF4
+        if self is QuantType.FP4:
+            return _FP4
+        return torch.arange(-127, 128, dtype=torch.float32) / 127.0
+
+
 @dataclass
 class QLoRAConfig(LoRAConfig):
     bits: int = 4
@@ -201,7 +222,12 @@ class QLoRALinear(Module):
         flat = F.pad(flat, (0, pad))
         blocks = flat.view(-1, bs)
         absmax = blocks.abs().amax(1).clamp(min=1e-12)
-        codes = (blocks / absmax[:, None]).unsqueeze(-1).sub(_NF4).abs().argmin(-1).to(torch.uint8)
+        qt = self.config.quant_type
+        self.quant_type = qt if isinstance(qt, QuantType) else QuantType(str(qt).lower())
+        book = self.quant_type.code_book()
+        norm = blocks / absmax[:, None]
+        # nearest code-book entry, in chunks (an int8 book has 255 entries)
+        codes = torch.cat([c.unsqueeze(-1).sub(book).abs().argmin(-1) for c in norm.split(4096)]).to(torch.uint8)
         self.register_buffer("codes", codes)
         if self.config.double_quant:
             s = absmax.max() / 255.0
@@ -213,7 +239,7 @@ class QLoRALinear(Module):
 
     def dequantize(self):
         absmax = self.absmax_q.float() * self.absmax_scale if self.config.double_quant else self.absmax
-        w = _NF4.to(self.codes.device)[self.codes.long()] * absmax[:, None]
+        w = self.quant_type.code_book().to(self.codes.device)[self.codes.long()] * absmax[:, None]
         w = w.reshape(-1)
         if self._pad:
             w = w[:-self._pad]
@@ -371,6 +397,9 @@ class PromptInit(enum.Enum):
     Text = "text"
 
 
+PromptInitStrategy = PromptInit     # the reference's name (ghostflow-nn/src/prompt_tuning.rs:27-36)
+
+
 @dataclass
 class PromptTuningConfig:
     num_virtual_tokens: int = 20
@@ -430,11 +459,22 @@ class PrefixTuningConfig:
     def large(cls): return cls(20)
 
 
+@dataclass
+class LayerPrefix:
+    """Key and value prefix of one layer (ghostflow-nn/src/prompt_tuning.rs:252-259)."""
+    prefix_key: torch.Tensor
+    prefix_value: torch.Tensor
+
+
 class PrefixTuning(Module):
     def __init__(self, config: PrefixTuningConfig | None = None):
         super().__init__()
         self.config = c = config or PrefixTuningConfig()
         self.prefix = Parameter(torch.randn(c.num_layers, 2, c.num_prefix_tokens, c.d_model) * 0.02)
+
+    def layer_prefix(self, layer: int) -> "LayerPrefix":
+        """The pair of :meth:`get_layer_prefix` as the reference's record type."""
+        return LayerPrefix(*self.get_layer_prefix(layer))
 
     def get_layer_prefix(self, layer: int):
         """(key_prefix, value_prefix), each ``[P, H, D/H]``."""
@@ -543,6 +583,15 @@ class DifficultyScorer:
         return (v - lo) / (hi - lo).clamp(min=1e-12)
 
 
+@dataclass
+class ScoredSample:
+    """A sample with its difficulty (ghostflow-nn/src/curriculum_learning.rs:116-127)."""
+    index: int
+    difficulty: float                 # 0 = easy, 1 = hard
+    loss: float | None = None
+    metadata: dict = field(default_factory=dict)
+
+
 class CurriculumLearning:
     def __init__(self, config: CurriculumConfig | None = None):
         self.config = config or CurriculumConfig()
@@ -589,6 +638,13 @@ class CurriculumLearning:
                                     CurriculumStrategy.TeacherStudent):
             l = torch.as_tensor(losses, dtype=torch.float32)
             self.difficulties[torch.as_tensor(indices)] = (l / l.max().clamp(min=1e-12)).clamp(0, 1)
+
+    def scored_samples(self, losses=None) -> list:
+        """Every sample as a :class:`ScoredSample`, easiest first (``losses``: optional per-sample losses)."""
+        assert self.difficulties is not None, "call initialize_samples first"
+        order = torch.argsort(self.difficulties)
+        return [ScoredSample(int(i), float(self.difficulties[i]), None if losses is None else float(losses[int(i)]))
+                for i in order]
 
     def next_epoch(self):
         self.epoch += 1

@@ -64,12 +64,28 @@ class ProfileScope:
         return False
 
 
+@dataclass
+class ProfileRecord:
+    """One timed scope (ghostflow-core/src/profiler.rs:141-146)."""
+    name: str
+    duration_ms: float
+
+
+@dataclass
+class ProfileSummary:
+    """Totals per operation name (ghostflow-core/src/profiler.rs:170-175)."""
+    total_operations: int
+    op_stats: dict
+
+
 class Profiler:
-    def __init__(self, use_cuda_events: bool = True):
+    def __init__(self, use_cuda_events: bool = True, keep_records: int = 100_000):
         self.enabled = True
         self.use_cuda_events = use_cuda_events
         self.stats: dict[str, OpStats] = {}
         self._pending = []
+        self.records: list = []            # the last ``keep_records`` scopes in completion order
+        self._keep = keep_records
 
     def start(self, name: str) -> ProfileScope:
         return ProfileScope(self, name)
@@ -77,6 +93,8 @@ class Profiler:
     scope = start
 
     def _record(self, name, ms):
+        if len(self.records) < self._keep:
+            self.records.append(ProfileRecord(name, ms))
         s = self.stats.setdefault(name, OpStats())
         s.count += 1
         s.total_ms += ms
@@ -94,6 +112,10 @@ class Profiler:
         return {k: {"count": v.count, "total_ms": v.total_ms, "avg_ms": v.avg_ms, "min_ms": v.min_ms, "max_ms": v.max_ms}
                 for k, v in self.stats.items()}
 
+    def get_summary(self) -> ProfileSummary:
+        self._flush()
+        return ProfileSummary(sum(v.count for v in self.stats.values()), dict(self.stats))
+
     def print_summary(self):
         rows = sorted(self.summary().items(), key=lambda kv: -kv[1]["total_ms"])
         print(f"{'op':<32}{'count':>8}{'total ms':>12}{'avg ms':>10}{'min ms':>10}{'max ms':>10}")
@@ -101,7 +123,7 @@ class Profiler:
             print(f"{k:<32}{v['count']:>8}{v['total_ms']:>12.3f}{v['avg_ms']:>10.3f}{v['min_ms']:>10.3f}{v['max_ms']:>10.3f}")
 
     def reset(self):
-        self.stats, self._pending = {}, []
+        self.stats, self._pending, self.records = {}, [], []
 
     def hook_modules(self, enable: bool = True):
         """Times every ``ghost_flow_b200.nn.Module`` call under its class name."""

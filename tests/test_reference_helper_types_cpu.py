@@ -63,3 +63,43 @@ def test_difficulty_metric_and_experience():
     buf.push(torch.ones(3), 2, -1.0, torch.zeros(3), True)
     s, a, r, s2, d = buf.sample(2)
     assert s.shape == (2, 3) and sorted(a.tolist()) == [1, 2] and gf is not None
+
+
+def test_small_nn_types():
+    from ghost_flow_b200 import nn
+    from ghost_flow_b200.models import AggregatorType, GraphSAGELayer
+    from ghost_flow_b200.utils import Profiler, ProfileRecord, ProfileSummary
+
+    # QLoRA base weights in the three storage formats: the finer the code book, the smaller the error
+    torch.manual_seed(0)
+    errs = {}
+    for qt in (nn.QuantType.FP4, nn.QuantType.NF4, nn.QuantType.INT8):
+        lin = nn.QLoRALinear(64, 32, nn.QLoRAConfig(quant_type=qt, double_quant=False))
+        torch.manual_seed(1)
+        w = torch.randn(32, 64) * 0.1
+        lin._quantize(w)
+        errs[qt] = ((lin.dequantize() - w).norm() / w.norm()).item()
+    assert errs[nn.QuantType.INT8] < 0.01 < errs[nn.QuantType.NF4] < errs[nn.QuantType.FP4] < 0.2, errs
+    assert nn.PromptInitStrategy.Vocab is nn.PromptInit.Vocab
+    pt = nn.PrefixTuning(nn.PrefixTuningConfig(num_prefix_tokens=4, num_layers=2, d_model=32, num_heads=4))
+    lp = pt.layer_prefix(1)
+    assert isinstance(lp, nn.LayerPrefix) and lp.prefix_key.shape == lp.prefix_value.shape
+    cl = nn.CurriculumLearning()
+    cl.initialize_samples([0.9, 0.1, 0.5])
+    ss = cl.scored_samples(losses=[3.0, 1.0, 2.0])
+    assert [s.index for s in ss] == [1, 2, 0] and isinstance(ss[0], nn.ScoredSample) and ss[0].loss == 1.0
+    t = nn.ONNXTensor("ids", [2, 2], [1, 2, 3, 4], nn.ONNXDataType.Int64).to_tensor()
+    assert t.dtype == torch.int64 and t.shape == (2, 2)
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.BatchNorm1d(4), torch.nn.ReLU())
+    opt = nn.InferenceOptimizer()
+    opt.optimize(net)
+    assert [f.name for f in opt.get_fused_ops()] == ["LinearBN"] and isinstance(opt.get_fused_ops()[0], nn.FusedOp)
+    assert AggregatorType.Pool is AggregatorType.Max and GraphSAGELayer is not None
+    prof = Profiler(use_cuda_events=False)
+    with prof.start("a"):
+        pass
+    with prof.start("a"):
+        pass
+    s = prof.get_summary()
+    assert isinstance(s, ProfileSummary) and s.total_operations == 2 and s.op_stats["a"].count == 2
+    assert len(prof.records) == 2 and isinstance(prof.records[0], ProfileRecord)
