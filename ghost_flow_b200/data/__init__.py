@@ -210,6 +210,28 @@ def collate_batch(samples):
     return torch.stack([torch.as_tensor(x) for x in xs]), torch.stack(ys)
 
 
+class DataLoaderIter:
+    """Iterator over the batches of one epoch (ghostflow-data/src/dataloader.rs:72-110): ``next()`` yields
+    ``(inputs, targets)``; ``current_batch`` counts what has been handed out, ``len()`` what is left."""
+
+    def __init__(self, loader: "DataLoader"):
+        self.loader = loader
+        self.current_batch = 0
+        self._total = len(loader)
+        self._gen = loader._batches()
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        item = next(self._gen)
+        self.current_batch += 1
+        return item
+
+    def __len__(self):
+        return max(0, self._total - self.current_batch)
+
+
 class DataLoader:
     def __init__(self, dataset, batch_size: int = 1, shuffle: bool = False, drop_last: bool = False,
                  num_workers: int = 0, sampler=None, seed: int = 0, pin_memory: bool = False, collate_fn=None):
@@ -241,6 +263,9 @@ class DataLoader:
         return n // self.batch_size if self._drop_last else (n + self.batch_size - 1) // self.batch_size
 
     def __iter__(self):
+        return DataLoaderIter(self)
+
+    def _batches(self):
         if self.sampler is not None:
             sampler = self.sampler
             if hasattr(sampler, "set_epoch"):

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
+from typing import NamedTuple
 
 import torch
 import torch.nn.functional as F
@@ -267,7 +268,13 @@ class T5Model(Module):
 
     def forward(self, input_ids, decoder_input_ids):
         mem = self.encoder(self.shared(input_ids))
-        return self.decoder(self.shared(decoder_input_ids), mem), mem
+        return T5Output(self.decoder(self.shared(decoder_input_ids), mem), mem)
+
+
+class T5Output(NamedTuple):
+    """Result of the encoder-decoder stack (ghostflow-nn/src/t5.rs:321-328); unpacks as ``(decoder, encoder)``."""
+    last_hidden_state: torch.Tensor
+    encoder_last_hidden_state: torch.Tensor
 
 
 class T5ForConditionalGeneration(Module):

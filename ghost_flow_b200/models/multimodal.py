@@ -28,6 +28,27 @@ from ..nn.transformer import TransformerEncoderLayer
 
 # =========================================================================== CLIP
 @dataclass
+class CLIPVisionConfig:
+    """Vision tower parameters (ghostflow-nn/src/clip.rs:28-44)."""
+    image_size: int = 224
+    patch_size: int = 16
+    hidden_size: int = 768
+    num_layers: int = 12
+    num_heads: int = 12
+    mlp_ratio: int = 4
+
+
+@dataclass
+class CLIPTextConfig:
+    """Text tower parameters (ghostflow-nn/src/clip.rs:45-62)."""
+    vocab_size: int = 49408
+    hidden_size: int = 512
+    num_layers: int = 12
+    num_heads: int = 8
+    max_position_embeddings: int = 77
+
+
+@dataclass
 class CLIPConfig:
     embed_dim: int = 512
     logit_scale_init: float = 2.6592
@@ -41,6 +62,23 @@ class CLIPConfig:
     text_layers: int = 12
     text_heads: int = 8
     max_text_len: int = 77
+
+    @classmethod
+    def from_towers(cls, vision: "CLIPVisionConfig", text: "CLIPTextConfig", embed_dim: int = 512):
+        """The flat configuration of this package from the reference's two tower records."""
+        return cls(embed_dim=embed_dim, image_size=vision.image_size, patch_size=vision.patch_size,
+                   vision_width=vision.hidden_size, vision_layers=vision.num_layers, vision_heads=vision.num_heads,
+                   vocab_size=text.vocab_size, text_width=text.hidden_size, text_layers=text.num_layers,
+                   text_heads=text.num_heads, max_text_len=text.max_position_embeddings)
+
+    @property
+    def vision_config(self) -> "CLIPVisionConfig":
+        return CLIPVisionConfig(self.image_size, self.patch_size, self.vision_width, self.vision_layers,
+                                self.vision_heads, 4)
+
+    @property
+    def text_config(self) -> "CLIPTextConfig":
+        return CLIPTextConfig(self.vocab_size, self.text_width, self.text_layers, self.text_heads, self.max_text_len)
 
     @classmethod
     def vit_b_32(cls): return cls(patch_size=32)

@@ -25,6 +25,7 @@ import re
 import threading
 import time
 import uuid
+from dataclasses import dataclass
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 import torch
@@ -182,6 +183,41 @@ def _build_llama(state: dict, device, extra: dict | None = None):
     return model, desc
 
 
+@dataclass
+class ModelInfo:
+    """What the registry reports about a loaded model (ghostflow-serve/src/models.rs:8-17)."""
+    id: str
+    name: str
+    version: str
+    input_shape: list
+    output_shape: list
+    loaded_at: str
+
+
+@dataclass
+class PredictionRequest:
+    """Body of ``POST /models/{id}/predict`` (ghostflow-serve/src/models.rs:19-24)."""
+    inputs: list
+    shape: list | None = None
+
+    @classmethod
+    def from_json(cls, body: dict) -> "PredictionRequest":
+        if "inputs" not in body:
+            raise ValueError("missing 'inputs'")
+        return cls(body["inputs"], body.get("shape"))
+
+
+@dataclass
+class PredictionResponse:
+    """Answer of the predict route (ghostflow-serve/src/models.rs:26-32)."""
+    outputs: list
+    shape: list
+    inference_time_ms: float
+
+    def to_json(self) -> dict:
+        return {"outputs": self.outputs, "shape": self.shape, "inference_time_ms": self.inference_time_ms}
+
+
 class LoadedLlama:
     """A LLaMA checkpoint behind the generation batcher. ``predict`` takes token ids (one prompt per row) and
     ``max_new_tokens`` and returns the greedy continuation."""
@@ -291,6 +327,17 @@ class ModelRegistry:
             return self.models[mid]
         except KeyError:
             raise ModelNotFound(mid) from None
+
+    def info(self, mid) -> ModelInfo:
+        m = self.get(mid)
+        return ModelInfo(m.id, m.name, str(m.desc.get("version", "1.0.0")), list(m.desc.get("input_shape", [])),
+                         list(m.desc.get("output_shape", [])),
+                         time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime(m.loaded_at)))
+
+    def handle(self, mid, request: PredictionRequest) -> PredictionResponse:
+        """Typed form of :meth:`predict`."""
+        r = self.predict(mid, request.inputs, request.shape)
+        return PredictionResponse(r["outputs"], r["shape"], r["inference_time_ms"])
 
     def predict(self, mid, inputs, shape=None):
         """Runs model ``mid`` on ``inputs`` (the reference's ``ModelRegistry::predict``, ghostflow-serve/src/models.rs:81-105,

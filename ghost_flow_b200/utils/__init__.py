@@ -323,9 +323,71 @@ _PATTERNS = [
 ]
 
 
+@dataclass
+class GraphNode:
+    """One operation of a :class:`ComputeGraph` (ghostflow-core/src/fusion.rs:22-30)."""
+    id: int
+    op: str
+    inputs: list = field(default_factory=list)
+
+
+@dataclass
+class FusionOpportunity:
+    """A run of nodes that one kernel of this library can execute (ghostflow-core/src/fusion.rs:243-249)."""
+    pattern_name: str
+    nodes: list
+    estimated_speedup: float
+    kernel: str = ""
+
+
+class ComputeGraph:
+    """A small op graph for fusion analysis (ghostflow-core/src/fusion.rs:32-80): nodes are added in topological
+    order with the ids of their inputs."""
+
+    def __init__(self):
+        self.nodes: list = []
+
+    def add_node(self, op: str, inputs=()) -> int:
+        self.nodes.append(GraphNode(len(self.nodes), op, list(inputs)))
+        return len(self.nodes) - 1
+
+    def consumers(self, node_id: int) -> list:
+        return [n.id for n in self.nodes if node_id in n.inputs]
+
+    def chains(self) -> list:
+        """Maximal runs of nodes in which every node is the only consumer of its predecessor (only such runs can be
+        fused without keeping an intermediate alive)."""
+        out, seen = [], set()
+        for n in self.nodes:
+            if n.id in seen:
+                continue
+            run, cur = [n.id], n
+            seen.add(n.id)
+            while True:
+                cons = self.consumers(cur.id)
+                if len(cons) != 1 or self.nodes[cons[0]].inputs[0] != cur.id or cons[0] in seen:
+                    break
+                cur = self.nodes[cons[0]]
+                run.append(cur.id)
+                seen.add(cur.id)
+            out.append(run)
+        return out
+
+
 class FusionEngine:
     def __init__(self):
         self.fused: list = []
+
+    def find_opportunities(self, graph: "ComputeGraph") -> list:
+        """:class:`FusionOpportunity` records for every pattern match inside a single-consumer chain of ``graph``."""
+        out = []
+        for run in graph.chains():
+            names = [graph.nodes[i].op for i in run]
+            for start, pat in self.analyze(names):
+                n = next(len(p[0]) for p in _PATTERNS if p[1] == pat)
+                out.append(FusionOpportunity(pat.value, run[start:start + n], self.estimate_speedup(pat),
+                                             self.kernel_for(pat)))
+        return out
 
     def analyze(self, ops: list[str]) -> list:
         """Finds fusable runs in a list of op names; returns ``[(start_index, pattern)]`` (longest match first)."""
@@ -384,11 +446,63 @@ class DeviceInfo:
         return cls("cpu", (0, 0), 100.0, 1, 0, False)
 
 
+@dataclass
+class OperationType:
+    """What a layout is chosen for (ghostflow-core/src/layout/mod.rs:56-66): a kind plus its parameters. Build with
+    the class methods, e.g. ``OperationType.Conv2d((3, 3), (1, 1))`` or ``OperationType.MatMul(4096, 4096, 4096)``."""
+    kind: str
+    params: dict = field(default_factory=dict)
+
+    @classmethod
+    def Conv2d(cls, kernel=(3, 3), stride=(1, 1)): return cls("Conv2d", {"kernel": tuple(kernel), "stride": tuple(stride)})
+    @classmethod
+    def MatMul(cls, m, n, k): return cls("MatMul", {"m": m, "n": n, "k": k})
+    @classmethod
+    def BatchNorm(cls): return cls("BatchNorm")
+    @classmethod
+    def LayerNorm(cls): return cls("LayerNorm")
+    @classmethod
+    def Attention(cls, heads, seq_len): return cls("Attention", {"heads": heads, "seq_len": seq_len})
+    @classmethod
+    def ElementWise(cls): return cls("ElementWise")
+    @classmethod
+    def Pooling(cls): return cls("Pooling")
+
+
+@dataclass
+class OptimizedLayout:
+    """Padded allocation plan of a tensor (ghostflow-core/src/memory.rs:156-163)."""
+    original_size: int
+    aligned_size: int
+    padding: int
+    stride: list
+
+
+def optimize_layout(shape, element_size: int = 4, alignment: int = 256, pad_rows: bool = False) -> OptimizedLayout:
+    """Row-major strides of ``shape`` (in elements) with the total size rounded up to ``alignment`` bytes; with
+    ``pad_rows`` the innermost row is padded to the alignment too (what TMA tensor maps and 16-byte vector kernels
+    want: every row starts on an aligned address)."""
+    shape = list(shape)
+    inner = shape[-1] if shape else 1
+    if pad_rows and shape:
+        per = max(1, alignment // element_size)
+        inner = (inner + per - 1) // per * per
+    stride, acc = [], 1
+    for i, d in enumerate(reversed(shape)):
+        stride.append(acc)
+        acc *= inner if i == 0 else d
+    stride.reverse()
+    original = element_size * (math.prod(shape) if shape else 1)
+    aligned = (acc * element_size + alignment - 1) // alignment * alignment
+    return OptimizedLayout(original, aligned, aligned - original, stride)
+
+
 class LayoutOptimizer:
     def __init__(self, device: DeviceInfo | None = None):
         self.device = device or DeviceInfo()
 
-    def choose_layout(self, op: str, shape) -> MemoryLayout:
+    def choose_layout(self, op, shape) -> MemoryLayout:
+        op = op.kind if isinstance(op, OperationType) else op
         if op.lower().startswith("conv") and self.device.has_tensor_cores:
             return MemoryLayout.NHWC
         if len(shape) == 3:
@@ -448,6 +562,15 @@ def list_devices() -> list:
     return devs
 
 
+class ElementwiseOp(enum.Enum):
+    """Element-wise operations of the hardware façade (ghostflow-core/src/hardware.rs:239-247)."""
+    Add = "add"
+    Mul = "mul"
+    ReLU = "relu"
+    Sigmoid = "sigmoid"
+    Tanh = "tanh"
+
+
 class HardwareOps:
     """``matmul_hw / conv2d_hw / elementwise_hw`` on a chosen device; non-B200 backends raise NotImplementedError."""
 
@@ -467,10 +590,17 @@ class HardwareOps:
     def conv2d_hw(self, x, w, bias=None, stride=1, padding=0):
         return torch.nn.functional.conv2d(self._to(x), self._to(w), None if bias is None else self._to(bias), stride, padding)
 
-    def elementwise_hw(self, x, op: str):
+    def elementwise_hw(self, x, op, other=None):
+        """``op``: an :class:`ElementwiseOp` or its name; Add / Mul take ``other``."""
         from .. import ops
 
-        return ops.unary(self._to(x), op)
+        name = op.value if isinstance(op, ElementwiseOp) else str(op)
+        if name in ("add", "mul"):
+            if other is None:
+                raise ValueError(f"{name} needs a second operand")
+            x, other = self._to(x), self._to(other)
+            return x + other if name == "add" else x * other
+        return ops.unary(self._to(x), name)
 
 
 # =========================================================================== sparse

@@ -103,3 +103,54 @@ def test_small_nn_types():
     s = prof.get_summary()
     assert isinstance(s, ProfileSummary) and s.total_operations == 2 and s.op_stats["a"].count == 2
     assert len(prof.records) == 2 and isinstance(prof.records[0], ProfileRecord)
+
+
+def test_graph_layout_hardware_serve_and_model_records():
+    from ghost_flow_b200 import models as M
+    from ghost_flow_b200 import serve
+    from ghost_flow_b200.data import DataLoader, DataLoaderIter, TensorDataset
+    from ghost_flow_b200.utils import (ComputeGraph, ElementwiseOp, FusionEngine, FusionOpportunity, HardwareOps,
+                                       LayoutOptimizer, MemoryLayout, OperationType, OptimizedLayout, list_devices,
+                                       optimize_layout)
+
+    g = ComputeGraph()
+    x = g.add_node("Input")
+    c = g.add_node("Conv2d", [x])
+    b = g.add_node("BatchNorm2d", [c])
+    r = g.add_node("ReLU", [b])
+    lin = g.add_node("Linear", [r])
+    g.add_node("ReLU", [lin])
+    g.add_node("Sigmoid", [lin])                       # a second consumer: Linear + ReLU may not fuse
+    ops = FusionEngine().find_opportunities(g)
+    assert [o.pattern_name for o in ops] == ["ConvBNReLU"] and ops[0].nodes == [c, b, r]
+    assert isinstance(ops[0], FusionOpportunity) and ops[0].estimated_speedup > 1 and ops[0].kernel
+    lay = optimize_layout((37, 50257), element_size=2, alignment=128, pad_rows=True)
+    assert isinstance(lay, OptimizedLayout) and lay.stride == [50304, 1] and lay.aligned_size % 128 == 0
+    assert lay.padding == lay.aligned_size - 37 * 50257 * 2
+    lo = LayoutOptimizer()
+    assert lo.choose_layout(OperationType.Conv2d((3, 3), (1, 1)), (8, 64, 56, 56)) is MemoryLayout.NHWC
+    assert OperationType.MatMul(4, 5, 6).params == {"m": 4, "n": 5, "k": 6}
+    hw = HardwareOps(list_devices()[0])
+    a = torch.tensor([-1.0, 2.0])
+    assert torch.equal(hw.elementwise_hw(a, ElementwiseOp.ReLU), torch.tensor([0.0, 2.0]))
+    assert torch.equal(hw.elementwise_hw(a, ElementwiseOp.Mul, a), torch.tensor([1.0, 4.0]))
+    reg = serve.ModelRegistry("cpu")
+    mid = reg.register("double", lambda t: 2 * t, [3], [3])
+    info = reg.info(mid)
+    assert isinstance(info, serve.ModelInfo) and info.name == "double" and info.input_shape == [3]
+    resp = reg.handle(mid, serve.PredictionRequest.from_json({"inputs": [1.0, 2.0, 3.0]}))
+    assert isinstance(resp, serve.PredictionResponse) and resp.outputs == [[2.0, 4.0, 6.0]]
+    assert resp.to_json()["shape"] == [1, 3]
+    cfg = M.CLIPConfig.from_towers(M.CLIPVisionConfig(image_size=32, patch_size=8, hidden_size=64, num_layers=1, num_heads=2),
+                                   M.CLIPTextConfig(vocab_size=100, hidden_size=32, num_layers=1, num_heads=2,
+                                                    max_position_embeddings=16), embed_dim=24)
+    assert cfg.vision_config.hidden_size == 64 and cfg.text_config.max_position_embeddings == 16
+    t5 = M.T5Model(M.T5Config.t5_tiny())
+    ids = torch.randint(0, 100, (2, 6))
+    out = t5(ids, ids[:, :3])
+    assert isinstance(out, M.T5Output) and out.last_hidden_state.shape[:2] == (2, 3)
+    assert out.encoder_last_hidden_state.shape[:2] == (2, 6)
+    it = iter(DataLoader(TensorDataset(torch.arange(10.0)[:, None], torch.arange(10)), batch_size=4))
+    assert isinstance(it, DataLoaderIter) and len(it) == 3
+    xb, yb = next(it)
+    assert xb.shape == (4, 1) and it.current_batch == 1 and len(it) == 2 and len(list(it)) == 2
