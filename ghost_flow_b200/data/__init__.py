@@ -107,7 +107,21 @@ class SyntheticTokenDataset(Dataset):
 
 
 # ------------------------------------------------------------------------------------------- samplers
-class SequentialSampler:
+class Sampler:
+    """Base of the index samplers (the trait of ghostflow-data/src/sampler.rs:6-12): an iterable of dataset indices
+    with a length."""
+
+    def __iter__(self):
+        raise NotImplementedError
+
+    def __len__(self):
+        raise NotImplementedError
+
+    def is_empty(self) -> bool:
+        return len(self) == 0
+
+
+class SequentialSampler(Sampler):
     def __init__(self, n: int):
         self.n = n
 
@@ -118,7 +132,7 @@ class SequentialSampler:
         return self.n
 
 
-class RandomSampler:
+class RandomSampler(Sampler):
     def __init__(self, n: int, seed: int = 0, replacement: bool = False, num_samples: int | None = None):
         self.n, self.seed, self.replacement, self.num_samples = n, seed, replacement, num_samples or n
         self.epoch = 0
@@ -136,7 +150,7 @@ class RandomSampler:
         return self.num_samples
 
 
-class WeightedRandomSampler:
+class WeightedRandomSampler(Sampler):
     def __init__(self, weights, num_samples: int, replacement: bool = True, seed: int = 0):
         self.weights = torch.as_tensor(weights, dtype=torch.float64)
         self.num_samples, self.replacement, self.seed = num_samples, replacement, seed
@@ -168,7 +182,7 @@ class BatchSampler:
         return n // self.batch_size if self.drop_last else (n + self.batch_size - 1) // self.batch_size
 
 
-class DistributedSampler:
+class DistributedSampler(Sampler):
     """Rank ``r`` of ``world`` gets the contiguous slice ``[r * n // world ...)``; the last rank takes the
     remainder (the reference's rule). ``even=True`` instead pads so that every rank gets the same count."""
 
@@ -300,7 +314,18 @@ class DistributedDataLoader(DataLoader):
 
 
 # ------------------------------------------------------------------------------------------- transforms
-class Compose:
+class Transform:
+    """Base of the transforms (the trait of ghostflow-data/src/transforms.rs:6-9): ``apply(tensor) -> tensor``;
+    calling the object does the same."""
+
+    def apply(self, x):
+        return self(x)
+
+    def __call__(self, x):
+        raise NotImplementedError
+
+
+class Compose(Transform):
     def __init__(self, transforms):
         self.transforms = list(transforms)
 
@@ -310,7 +335,7 @@ class Compose:
         return x
 
 
-class ToTensor:
+class ToTensor(Transform):
     """uint8 ``[H, W, C]`` (or ``[H, W]``) image -> float ``[C, H, W]`` in [0, 1]."""
 
     def __call__(self, x):
@@ -324,7 +349,7 @@ class ToTensor:
         return t.float()
 
 
-class Normalize:
+class Normalize(Transform):
     def __init__(self, mean, std):
         self.mean, self.std = torch.as_tensor(mean, dtype=torch.float32), torch.as_tensor(std, dtype=torch.float32)
 
@@ -336,7 +361,7 @@ class Normalize:
         return (x - self.mean.view(-1, 1, 1)) / self.std.view(-1, 1, 1)
 
 
-class _Random:
+class _Random(Transform):
     def __init__(self, seed: int = 0):
         self.gen = torch.Generator().manual_seed(seed)
 
