@@ -373,23 +373,69 @@ class ExpertParallelMoE:
         return y
 
     def _forward_ref(self, x, residual):
-        assert self.world == 1, "the CPU path holds all experts in one process"
+        """CPU path. One rank: the dense oracle under autograd. Several ranks (gloo): tokens are all-gathered, every
+        rank runs ITS experts over the tokens of all ranks that were routed to them, and the partial outputs are
+        summed back to the tokens' owners: the same mathematics as the dispatch / combine kernels, written with
+        collectives."""
         xr = x.detach().clone().requires_grad_(True)
         # leaves that share storage with the current weights; the context keeps them, so the backward pass still
         # differentiates this call's weights after set_weights pointed the layer somewhere else
         gate, w13, w2 = (t.detach().requires_grad_(True) for t in (self.gate, self.w13, self.w2))
-        y = self.dense_reference(xr, w13, w2, residual=residual, gate=gate)
-        probs = torch.softmax(xr.float() @ gate.float().t(), -1)
+        if self.world == 1:
+            y = self.dense_reference(xr, w13, w2, residual=residual, gate=gate)
+            x_all, lo = xr, 0
+        else:
+            T = x.shape[0]
+            gathered = torch.empty(self.world * T, x.shape[1], dtype=x.dtype)
+            dist.all_gather_into_tensor(gathered, x.detach().contiguous(), group=self.group)
+            x_all = gathered.requires_grad_(True)
+            lo = self.rank * T
+            y = self._local_experts(x_all, gate, w13, w2)            # [W * T, d]: this rank's experts only
+        probs = torch.softmax(x_all[lo:lo + x.shape[0]].float() @ gate.float().t(), -1)
         idx = probs.topk(self.k, -1).indices
         frac = torch.bincount(idx.flatten(), minlength=self.E).float() / idx.numel()
         aux = self.E * (frac * probs.mean(0)).sum()
-        return y.to(x.dtype).detach(), (xr, y, aux, (gate, w13, w2))
+        if self.world == 1:
+            out = y
+        else:
+            part = y.detach().clone()
+            dist.all_reduce(part, group=self.group)
+            out = part[lo:lo + x.shape[0]]
+            if residual is not None:
+                out = out + residual.float()
+        return out.to(x.dtype).detach(), (x_all, y, aux, (gate, w13, w2), lo, x.shape[0])
+
+    def _local_experts(self, x_all, gate, w13, w2):
+        """Sum over this rank's experts of (routing weight x expert output) for every token of ``x_all``."""
+        xf = x_all.float()
+        probs = torch.softmax(xf @ gate.float().t(), -1)
+        top, idx = probs.topk(self.k, -1)
+        wts = top / top.sum(-1, keepdim=True)
+        y = torch.zeros_like(xf)
+        for j in range(self.el):
+            e = self.rank * self.el + j
+            tok, slot = (idx == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            g, u = (xf[tok] @ w13[j].float().t()).chunk(2, -1)
+            y = y.index_add(0, tok, ((torch.nn.functional.silu(g) * u) @ w2[j].float().t()) * wts[tok, slot, None])
+        return y
 
     def _backward_ref(self, ctx, dy):
-        xr, y, aux, leaves = ctx
-        total = (y * dy.float()).sum() + self.aux_coef * aux
-        gx, gg, g13, g2 = torch.autograd.grad(total, [xr, *leaves])
+        x_all, y, aux, leaves, lo, T = ctx
+        if self.world == 1:
+            dy_all = dy.float()
+        else:
+            dy_all = torch.empty(self.world * T, dy.shape[1], dtype=torch.float32)
+            dist.all_gather_into_tensor(dy_all, dy.float().contiguous(), group=self.group)
+        total = (y * dy_all).sum() + self.aux_coef * aux
+        gx, gg, g13, g2 = torch.autograd.grad(total, [x_all, *leaves], allow_unused=True)
+        if self.world > 1:
+            gx = gx.contiguous()
+            dist.all_reduce(gx, group=self.group)          # every rank's experts contributed to my tokens' gradient
+            gx = gx[lo:lo + T]
         for name, g in (("gate", gg), ("w13", g13), ("w2", g2)):
+            g = torch.zeros_like(self.grads[name]) if g is None else g
             if self.accumulate_grads:
                 self.grads[name] += g.to(self.grads[name].dtype)
             else:

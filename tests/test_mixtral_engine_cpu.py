@@ -128,3 +128,34 @@ def test_mixtral_engine_state_round_trip():
     sd = a.state_dict()
     assert sd["layers.1.moe.w13"].shape == (4, 256, 64) and sd["layers.0.moe.gate"].shape == (4, 64)
     assert torch.equal(sd["layers.1.moe.w2"], b.state_dict()["layers.1.moe.w2"])
+
+
+def test_mixtral_engine_on_two_cpu_ranks_matches_one_rank(tmp_path):
+    """Expert parallelism = 2 over gloo (tokens gathered, each rank runs its two experts, partial outputs summed
+    back; attention units under ZeRO-3) against one rank holding all four experts and the whole batch."""
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, here)
+    import _mixtral_cpu_worker as w
+
+    for aux, tol in ((0.0, 2e-5), (0.05, 2e-3)):
+        out = str(tmp_path / f"mx{aux}.pt")
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                            "--master-addr", "127.0.0.1", "--master-port", "29691" if aux == 0 else "29693",
+                            os.path.join(here, "_mixtral_cpu_worker.py"), out, str(aux)],
+                           env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-3000:]
+        two = torch.load(out)
+        one = w.run(1, 0, aux)
+        assert one["losses"][-1] < one["losses"][0]
+        # with the auxiliary loss every rank balances its own tokens, one rank the whole batch: close, not equal
+        for a, b in zip(two["losses"], one["losses"]):
+            assert abs(a - b) < tol, (aux, two["losses"], one["losses"])
+        if aux == 0:        # (Adam turns the small difference of the balancing gradients into percents of the weights)
+            for k in ("w13", "gate", "wqkv"):
+                rel = ((two[k] - one[k]).norm() / one[k].norm()).item()
+                assert rel < 1e-4, (k, rel)
