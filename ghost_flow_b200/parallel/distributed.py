@@ -389,13 +389,15 @@ class ZeRoOptimizer:
         self.step_count = 0
         self.buckets = []
         cuda = bool(self.params) and self.params[0].is_cuda
-        self.overlap = (cuda and self.world > 1) if overlap is None else (bool(overlap) and cuda)
+        # on CPU ranks (gloo) an explicit overlap=True launches the bucket work straight from the hooks (no side
+        # stream): nothing overlaps there, but the hook bookkeeping is the same and can be tested without a GPU
+        self.overlap = (cuda and self.world > 1) if overlap is None else bool(overlap)
         self.capturable = bool(capturable) and cuda
         self._sync_hooks = True
         self._flag_epoch = 0
         self._open = False
         self._launched: set = set()
-        self._side = torch.cuda.Stream(self.params[0].device) if self.overlap else None
+        self._side = torch.cuda.Stream(self.params[0].device) if (self.overlap and cuda) else None
         self._step_dev = (torch.zeros(1, dtype=torch.int32, device=self.params[0].device) if self.capturable
                           else None)
         groups, cur, n = [], [], 0

@@ -97,6 +97,57 @@ def case_zero(rank, world, out):
     return res
 
 
+def case_zero_hooks(rank, world, out):
+    """The hook-driven schedule of the generic ZeRO optimizer on CPU ranks: buckets launched from gradient hooks as
+    their last gradient arrives, a parameter without a gradient (its bucket is launched by step()), gradient
+    accumulation over two backward passes with no_sync()."""
+    from ghost_flow_b200.parallel.distributed import ZeRoConfig, ZeRoOptimizer, ZeRoStage
+    x, y = data()
+    xs, ys = x.chunk(world), y.chunk(world)
+
+    class WithUnused(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.net = model()
+            self.extra = torch.nn.Linear(3, 3)     # never used in the forward pass: no gradient, hook never fires
+
+        def forward(self, t):
+            return self.net(t)
+
+    build = WithUnused
+
+    ref = build()
+    opt_ref = torch.optim.AdamW([p for p in ref.parameters()], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m = build()
+    m.load_state_dict(ref.state_dict())
+    cfg = ZeRoConfig(stage=ZeRoStage.Stage2, world_size=world, rank=rank, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1,
+                     bucket_size=300)
+    opt = ZeRoOptimizer(m.parameters(), cfg, overlap=True)
+    launched_in_backward = []
+    res = {}
+    for step in range(4):
+        opt_ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        for p in ref.extra.parameters():
+            p.grad = torch.zeros_like(p)           # the flat optimizer decays every parameter of its buckets
+        opt_ref.step()
+        opt.zero_grad()
+        if step % 2 == 0:
+            torch.nn.functional.mse_loss(m(xs[rank]), ys[rank]).backward()
+        else:                                       # the same gradient from two half-weighted backward passes
+            with opt.no_sync():
+                (0.5 * torch.nn.functional.mse_loss(m(xs[rank]), ys[rank])).backward()
+                assert not opt._launched
+            (0.5 * torch.nn.functional.mse_loss(m(xs[rank]), ys[rank])).backward()
+        launched_in_backward.append(len(opt._launched))
+        opt.step()
+        assert not opt._launched and not opt._open
+    res["hooks_param_err"] = max((p - q).abs().max().item() for p, q in zip(m.parameters(), ref.parameters()))
+    res["hooks_buckets"] = len(opt.buckets)
+    res["hooks_launched_in_backward"] = launched_in_backward
+    return res
+
+
 def case_pipeline(rank, world, out):
     from ghost_flow_b200.parallel.distributed import PipelineParallel
     x, y = data(16)

@@ -41,6 +41,15 @@ def test_zero_stages_match_adamw(tmp_path):
         assert d["zero3_savings"] > d["zero2_savings"] > d["zero1_savings"] > 1.0
 
 
+def test_zero_buckets_launched_from_gradient_hooks(tmp_path):
+    r, res = _run("zero_hooks", tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    for d in res:
+        assert d["hooks_param_err"] < 2e-5, d
+        # every bucket but the one holding the unused layer went out during the backward pass
+        assert d["hooks_buckets"] >= 3 and all(n == d["hooks_buckets"] - 1 for n in d["hooks_launched_in_backward"]), d
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_pipeline_1f1b_matches_single_process(tmp_path, world):
     r, res = _run("pipeline", tmp_path, world=world)
