@@ -426,12 +426,12 @@ template <int HD>
 static int launch_fa_bwd(const void* q, const void* k, const void* v, const void* dout, long long ldq, long long ldk,
                          long long ldv, long long lddo, FaBwdParams& p, cudaStream_t stream) {
   using Cfg = FaBwdCfg<HD>;
-  static bool configured = false;
+  static gf::DeviceOnce configured;
   auto kern = fa_bwd_kernel<HD>;
-  if (!configured) {
+  if (configured.todo()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return GFH_CUDA;
-    configured = true;
+    configured.mark();
   }
   const uint64_t T = (uint64_t)p.B * p.S;
   CUtensorMap tq, tk, tv, tdo;

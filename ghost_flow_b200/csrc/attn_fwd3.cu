@@ -370,12 +370,12 @@ template <int HD>
 static int launch_fa3(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                       Fa3Params& p, cudaStream_t stream) {
   using Cfg = Fa3Cfg<HD>;
-  static bool configured = false;
+  static gf::DeviceOnce configured;
   auto kern = fa_fwd3_kernel<HD>;
-  if (!configured) {
+  if (configured.todo()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return GFH_CUDA;
-    configured = true;
+    configured.mark();
   }
   const uint64_t T = (uint64_t)p.B * p.S;
   CUtensorMap tq, tk, tv;

@@ -328,8 +328,8 @@ __global__ void fill_int_kernel(int* p, int n, int v) {
 using namespace gf;
 
 static void configure_comm_kernels() {
-  static bool done = false;
-  if (done) return;
+  static gf::DeviceOnce done;
+  if (!done.todo()) return;
   prefer_max_smem(signal_peers_kernel);
   prefer_max_smem(wait_flags_kernel);
   prefer_max_smem(rs_adamw_kernel<true>);
@@ -339,7 +339,7 @@ static void configure_comm_kernels() {
   prefer_max_smem(allgather_pull_kernel);
   prefer_max_smem(fill_int_kernel);
   prefer_max_smem(counter_add_kernel);
-  done = true;
+  done.mark();
 }
 
 static inline uint32_t limit_or_default(long long wait_limit) {

@@ -393,10 +393,10 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm2Par
   using Cfg = G2Cfg<BNH>;
   constexpr int G2_SMEM_BYTES = Cfg::SMEM_BYTES;
   constexpr int G2_BN = Cfg::BN;
-  static bool configured = false;
+  static gf::DeviceOnce configured;
   static int max_pairs = 0;
   auto kern = gemm2sm_bf16_kernel<BNH, A_MN, B_MN>;
-  if (!configured) {
+  if (configured.todo()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess)
       return GFH_CUDA;
     // how many CTA pairs the device can hold at once (a GPC with an odd number of free SMs strands one)
@@ -414,7 +414,7 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm2Par
       n = sm_count() / 2;
     }
     max_pairs = n;
-    configured = true;
+    configured.mark();
   }
   p.tiles_m = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
   p.tiles_n = (p.N + G2_BN - 1) / G2_BN;

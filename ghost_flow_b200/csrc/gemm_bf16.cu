@@ -775,13 +775,13 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_ctas,
                        cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool configured = false;
+  static gf::DeviceOnce configured;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  if (!configured) {
+  if (configured.todo()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES + RS_STAGE_BYTES);
     if (e != cudaSuccess) return GFH_CUDA;
-    configured = true;
+    configured.mark();
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -791,12 +791,12 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   const int n_copy = p.g_operand >= 0 ? p.g_copy_ctas : 0;
   if (tiles < grid - n_copy) grid = tiles + n_copy;
   p.group_m = 0;
-  static int band_rows = 0;          // rows of a band of the tile walk; GF_GEMM_BAND overrides the default of 16
-  if (band_rows == 0) {
+  // rows of a band of the tile walk; GF_GEMM_BAND overrides the default of 16 (read once, thread-safe)
+  static const int band_rows = [] {
     const char* e = getenv("GF_GEMM_BAND");
-    band_rows = e ? atoi(e) : 16;
-    if (band_rows < 1) band_rows = 16;
-  }
+    const int v = e ? atoi(e) : 16;
+    return v < 1 ? 16 : v;
+  }();
   const int band = p.tiles_m > band_rows ? band_rows : p.tiles_m;
   if (p.rs_world > 0) {
     // row blocks alternate between owners when every owner has whole row blocks; otherwise start after the own rows

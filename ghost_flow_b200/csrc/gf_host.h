@@ -2,6 +2,7 @@
 // driver entry point (no link-time dependency on libcuda), status word access,
 // and the C error codes of the library.
 #pragma once
+#include <atomic>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -38,6 +39,28 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
                  CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);
 
 int sm_count();
+
+// "The attributes of this kernel are set" per device. cudaFuncSetAttribute applies to the current device only, so a
+// process that drives several GPUs has to repeat it on each; a single function-local bool would skip it on the
+// second device. Races are benign (two threads may both set the same attribute to the same value).
+struct DeviceOnce {
+  std::atomic<unsigned char> done[64];
+  DeviceOnce() { for (auto& d : done) d.store(0); }
+  static int device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) d = 0;
+    return d;
+  }
+  bool todo() { return done[device()].load(std::memory_order_acquire) == 0; }
+  void mark() { done[device()].store(1, std::memory_order_release); }
+};
+// The same for attributes that only ever grow (dynamic shared-memory limit raised to the largest request so far).
+struct DeviceMax {
+  std::atomic<size_t> value[64];
+  DeviceMax() { for (auto& v : value) v.store(0); }
+  size_t get() { return value[DeviceOnce::device()].load(std::memory_order_acquire); }
+  void set(size_t v) { value[DeviceOnce::device()].store(v, std::memory_order_release); }
+};
 // Checked build: the 8-int status buffer of the current device (registered with gf_set_check_buffer), for kernels
 // whose exported signature has no status pointer. Null when none was registered.
 int* check_buffer();

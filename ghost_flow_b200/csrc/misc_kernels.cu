@@ -338,11 +338,11 @@ GF_API int gf_conv_bn_relu(const float* x, const float* w, const float* bias, co
   if (OH <= 0 || OW <= 0) return GFH_BAD_ARG;
   const size_t smem = (size_t)Cin * KH * KW * sizeof(float);
   if (smem > 160 * 1024) return GFH_TOO_LARGE;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  static gf::DeviceMax configured;
+  if (smem > 48 * 1024 && smem > configured.get()) {
     if (cudaFuncSetAttribute(conv_bn_relu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return GFH_CUDA;
-    configured = smem;
+    configured.set(smem);
   }
   dim3 grid((OH * OW + 127) / 128, Cout, N);
   conv_bn_relu_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(x, w, bias, gamma, beta, mean, var, y, N, Cin, H, W,

@@ -420,12 +420,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int BN, int MODE>
 static int launch_f8(const CUtensorMap& tmA, const CUtensorMap& tmB, F8Params& p, cudaStream_t stream) {
   using Cfg = F8Cfg<BN>;
-  static bool configured = false;
+  static gf::DeviceOnce configured;
   auto kern = gemm_fp8_kernel<BN, MODE>;
-  if (!configured) {
+  if (configured.todo()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return GFH_CUDA;
-    configured = true;
+    configured.mark();
   }
   p.tiles_m = (p.M + F8_BM - 1) / F8_BM;
   p.tiles_n = (p.N + BN - 1) / BN;

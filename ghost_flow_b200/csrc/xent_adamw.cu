@@ -242,12 +242,12 @@ GF_API int gf_xent_fused(const void* logits, const long long* targets, float* lo
   if ((reinterpret_cast<uintptr_t>(logits) & 15) || (reinterpret_cast<uintptr_t>(dlogits) & 15)) return GFH_BAD_ARG;
   const size_t smem = (size_t)v8 * 2;
   if (smem > 200 * 1024) return GFH_TOO_LARGE;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static gf::DeviceMax configured;
+  if (smem > configured.get()) {
     if (cudaFuncSetAttribute(xent_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return GFH_CUDA;
-    configured = smem;
+    configured.set(smem);
   }
   xent_fused_kernel<<<T, XENT_THREADS, smem, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, targets,
                                                                     loss_rows, (__nv_bfloat16*)dlogits, T, V, ld,
@@ -262,11 +262,11 @@ GF_API int gf_adam_flat_dev(float* p, float* m, float* v, const void* g, void* p
                             int grad_dtype, const int* skip, const int* step_dev, void* stream) {
   gf::enter();
   if (n <= 0) return GFH_OK;
-  static bool configured = false;
-  if (!configured) {
+  static gf::DeviceOnce configured;
+  if (configured.todo()) {
     prefer_max_smem(adam_flat_kernel<__nv_bfloat16>);
     prefer_max_smem(adam_flat_kernel<float>);
-    configured = true;
+    configured.mark();
   }
   AdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.grad_scale = grad_scale;
