@@ -74,6 +74,8 @@ class MixtralEngine(Zero3LlamaEngine):
                          persist_gathered=persist_gathered)
         if self.opt.max_grad_norm is not None:
             raise NotImplementedError("gradient clipping is not wired into the expert optimizer yet")
+        if self.recompute:
+            raise NotImplementedError("activation recompute would dispatch every layer's tokens twice")
         E, k = cfg.num_local_experts, cfg.num_experts_per_tok
         cf = capacity_factor if capacity_factor is not None else (cfg.capacity_factor or 2.0)
         self.moe = ExpertParallelMoE(cfg.hidden_size, cfg.intermediate_size, E, k, tokens_per_rank, self.device,
