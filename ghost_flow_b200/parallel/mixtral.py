@@ -191,5 +191,9 @@ class MixtralEngine(Zero3LlamaEngine):
                 lp[name].copy_(e.master[name].to(lp[name].dtype))
         super().load_shard_state(st)
 
+    def accumulate(self, tokens, targets):
+        raise NotImplementedError("the expert optimizer updates a layer right after its backward pass; gradient "
+                                  "accumulation over micro-batches is not wired into it")
+
     def expert_parameters(self) -> int:
         return sum(v.numel() for e in self.experts for v in e.master.values())

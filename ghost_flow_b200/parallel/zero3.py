@@ -192,6 +192,9 @@ class Zero3LlamaEngine:
         self.last_stats = {}
         self.skipped_steps = 0
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._micro = 0            # micro-batches since the last optimizer update (gradient accumulation)
+        self._applying = True      # False while a micro-batch of accumulate() runs
+        self._gred_tmp = None
         # kernel status word of the previous steps, copied to pinned memory without stalling the stream
         self._status_host = None
         self._status_event = None
@@ -286,22 +289,38 @@ class Zero3LlamaEngine:
         o = self.opt
         kw = dict(lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay,
                   step=self.step_count)
-        deferred = o.max_grad_norm is not None
+        # deferred: with clipping, and for every micro-batch of an accumulated step (the first one overwrites the
+        # accumulator, the later ones add to it; the norm of the sum is then taken in _finish_clipped_step)
+        accumulating = self._micro > 1 or not self._applying
+        deferred = o.max_grad_norm is not None or accumulating
+        first = self._micro == 1
 
         def run():
             if deferred:
                 if unit.gred is None:
                     unit.gred = torch.zeros(unit.shard_numel, dtype=torch.float32, device=self.device)
                 if self.comm.fused:
-                    self.comm.reduce_only(unit, unit.index, g_full, slot, unit.gred, self._sumsq)
+                    if first:
+                        self.comm.reduce_only(unit, unit.index, g_full, slot, unit.gred, self._sumsq)
+                    else:
+                        if self._gred_tmp is None or self._gred_tmp.numel() < unit.shard_numel:
+                            self._gred_tmp = torch.empty(max(u.shard_numel for u in self.units), dtype=torch.float32,
+                                                         device=self.device)
+                        tmp = self._gred_tmp[:unit.shard_numel]
+                        self.comm.reduce_only(unit, unit.index, g_full, slot, tmp, self._sumsq)
+                        unit.gred.add_(tmp)
                     return
                 if self.world == 1:
-                    unit.gred.copy_(g_full[:unit.shard_numel].float())
+                    new = g_full[:unit.shard_numel].float()
                 else:
                     g = self.gshard[:unit.shard_numel]
                     self.comm.reduce_scatter(g_full, g)
-                    unit.gred.copy_(g.float())
-                self._sumsq.add_(unit.gred.square().sum())
+                    new = g.float()
+                if first:
+                    unit.gred.copy_(new)
+                    self._sumsq.add_(unit.gred.square().sum())
+                else:
+                    unit.gred.add_(new)
                 return
             if self.comm.fused:
                 self.comm.reduce_scatter_adamw(unit, unit.index, g_full, slot, **kw)
@@ -334,14 +353,29 @@ class Zero3LlamaEngine:
         if self.streams.cuda:
             torch.cuda.current_stream().wait_stream(self.streams.opt)
             torch.cuda.current_stream().wait_stream(self.streams.comm)
-        total = self._sumsq.clone()
+        n_micro = max(1, self._micro)
+        if n_micro > 1:
+            # the per-unit sums of squares were taken per micro-batch: take the norm of the accumulated mean instead
+            total = torch.stack([u.gred.square().sum() for u in self.units]).sum().reshape(1) / float(n_micro) ** 2
+        else:
+            total = self._sumsq.clone()
+        self._sumsq.zero_()
+        if o.max_grad_norm is None:
+            # accumulation without clipping: no norm, no host read
+            self.last_stats = {"micro_batches": n_micro}
+            for u in self.units:
+                K.adamw_flat(u.master, u.m, u.v, u.gred, u.shard, lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
+                             weight_decay=o.weight_decay, step=self.step_count, grad_scale=1.0 / n_micro)
+                if self.comm.fused:
+                    self.comm.publish_version(u.index)
+            return True
         if self.world > 1:
             self.comm.all_reduce_scalar(total)
         norm = float(total.sqrt())                      # one host read per step: the decision to skip is the host's
         finite = math.isfinite(norm)
-        coef = min(1.0, o.max_grad_norm / (norm + 1e-6)) if finite else 0.0
-        self.last_stats = {"grad_norm": norm, "clip_coef": coef, "skipped": not finite}
-        self._sumsq.zero_()
+        coef = (min(1.0, o.max_grad_norm / (norm + 1e-6)) if finite else 0.0) / n_micro
+        self.last_stats = {"grad_norm": norm, "clip_coef": coef * n_micro, "skipped": not finite,
+                           "micro_batches": n_micro}
         if not finite:
             self.step_count -= 1                        # bias correction continues from the last applied step
             self.skipped_steps += 1
@@ -416,14 +450,24 @@ class Zero3LlamaEngine:
         return self._attn_bwd(w, g, sa, dx2, B, S)
 
     # ------------------------------------------------------------------ one training step
-    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    def accumulate(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Forward and backward of one micro-batch WITHOUT an optimizer step: every unit's gradient is reduced over
+        the ranks as usual and added to this rank's fp32 shard accumulator. The next :meth:`step` adds its own
+        micro-batch and applies AdamW to the mean over all micro-batches since the last update. Returns this
+        micro-batch's global mean loss."""
+        return self.step(tokens, targets, _apply=False)
+
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor, _apply: bool = True) -> torch.Tensor:
         """One optimizer step on this rank's micro-batch ``tokens/targets [B, S]`` (int64, on device).
         Returns the global mean loss as a 0-d fp32 tensor on the device."""
         c = self.cfg
         B, S = tokens.shape
         T = B * S
         self._poll_status(force=(self.step_count % 8 == 7))
-        self.step_count += 1
+        self._micro += 1
+        self._applying = _apply
+        if _apply:
+            self.step_count += 1
         L = len(self.layers)
         tok = tokens.reshape(-1)
         tgt = targets.reshape(-1)
@@ -495,8 +539,10 @@ class Zero3LlamaEngine:
         grad_free[gslot] = self._reduce_and_update(self.embed, gslot)
         for e in grad_free:
             self._wait(e)
-        if self.opt.max_grad_norm is not None:
+        if _apply and (self.opt.max_grad_norm is not None or self._micro > 1):
             self._finish_clipped_step()
+        if _apply:
+            self._micro = 0
         if self.world > 1:
             loss = self.comm.all_reduce_scalar(loss.clone()) / self.world
         self._post_status()
