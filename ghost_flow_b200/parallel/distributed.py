@@ -440,6 +440,10 @@ class ZeRoOptimizer:
         def hook(_param):
             if not self._sync_hooks or self._offloaded:
                 return
+            if bucket_index in self._launched:
+                # the bucket was reduced and its shard updated during an earlier backward pass of this step
+                raise RuntimeError("a second backward pass reached a bucket that was already reduced and updated in "
+                                   "this step: wrap every backward pass but the last in ZeRoOptimizer.no_sync()")
             self._pending[bucket_index] -= 1
             if self._pending[bucket_index] == 0:
                 self._launch_bucket(bucket_index)

@@ -143,6 +143,15 @@ def case_zero_hooks(rank, world, out):
         opt.step()
         assert not opt._launched and not opt._open
     res["hooks_param_err"] = max((p - q).abs().max().item() for p, q in zip(m.parameters(), ref.parameters()))
+    # a second backward pass without no_sync() would add to gradients that were already consumed: refused
+    opt.zero_grad()
+    torch.nn.functional.mse_loss(m(xs[rank]), ys[rank]).backward()
+    try:
+        torch.nn.functional.mse_loss(m(xs[rank]), ys[rank]).backward()
+        res["hooks_second_backward_refused"] = False
+    except RuntimeError as e:
+        res["hooks_second_backward_refused"] = "no_sync" in str(e)
+    opt.step()
     res["hooks_buckets"] = len(opt.buckets)
     res["hooks_launched_in_backward"] = launched_in_backward
     return res

@@ -46,6 +46,7 @@ def test_zero_buckets_launched_from_gradient_hooks(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     for d in res:
         assert d["hooks_param_err"] < 2e-5, d
+        assert d["hooks_second_backward_refused"], d
         # every bucket but the one holding the unused layer went out during the backward pass
         assert d["hooks_buckets"] >= 3 and all(n == d["hooks_buckets"] - 1 for n in d["hooks_launched_in_backward"]), d
 
