@@ -130,3 +130,32 @@ def test_rank_loss_between_steps_restarts_at_smaller_world(tmp_path):
         assert abs(x - y) < 1e-5, (got["losses"], full["losses"])
     for x, y in zip(partial["losses"], full["losses"]):
         assert abs(x - y) < 1e-5
+
+
+def test_elastic_supervisor_restarts_the_job_at_the_surviving_world_size(tmp_path):
+    """The loop around the launcher: the job loses rank 3 between steps, the survivors write the marker and exit, the
+    supervisor starts the job again at the largest world size that still divides the global batch, from the sharded
+    checkpoint; the continued loss curve is the uninterrupted one."""
+    from ghost_flow_b200.parallel import elastic, fault
+
+    ck, mk = tmp_path / "ck", tmp_path / "marker"
+    _launch(2, "--steps", 5, "--out", tmp_path / "full.pt")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    res = elastic.run_elastic(
+        [WORKER, "--steps", 6, "--save", ck, "--save-at", 2, "--die-rank", 3, "--die-step", 3, "--marker-dir", mk,
+         "--out", tmp_path / "broken"],
+        nproc=4, marker_dir=mk, divides=4, master_port=29790, env=env, capture=True, timeout=600,
+        on_restart=lambda marker, world: ["--steps", 3, "--load", marker["checkpoint_dir"], "--die-rank", -1,
+                                          "--save", "", "--out", tmp_path / "resumed.pt"])
+    assert res.returncode == 0 and res.restarts == 1 and res.worlds == [4, 2], res
+    assert res.markers[0]["failed_ranks"] == [3] and res.markers[0]["old_world"] == 4
+    assert elastic.next_world({"new_world": 7}, divides=64) == 4 and elastic.next_world({"new_world": 7}) == 7
+    full, got = torch.load(tmp_path / "full.pt"), torch.load(tmp_path / "resumed.pt")
+    assert got["step"] == 5
+    for x, y in zip(got["losses"], full["losses"][2:]):
+        assert abs(x - y) < 1e-5, (got["losses"], full["losses"])
+    # a job that fails without a marker is not restarted
+    plain = elastic.run_elastic([WORKER, "--no-such-flag"], nproc=1, marker_dir=tmp_path / "none", master_port=29795,
+                                env=env, capture=True, timeout=300)
+    assert plain.returncode != 0 and plain.restarts == 0 and plain.worlds == [1]
+    assert fault.read_restart_marker(tmp_path / "none") is None
