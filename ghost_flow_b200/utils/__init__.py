@@ -19,6 +19,7 @@ import contextlib
 import enum
 import json
 import math
+import os
 import statistics
 import time
 from dataclasses import dataclass, field
@@ -58,9 +59,9 @@ class ProfileScope:
         if self.cuda:
             self.e1.record()
             torch.cuda.nvtx.range_pop()
-            self.profiler._pending.append((self.name, self.e0, self.e1))
+            self.profiler._pending.append((self.name, self.e0, self.e1, self.t0))
         else:
-            self.profiler._record(self.name, (time.perf_counter() - self.t0) * 1e3)
+            self.profiler._record(self.name, (time.perf_counter() - self.t0) * 1e3, self.t0)
         return False
 
 
@@ -69,6 +70,7 @@ class ProfileRecord:
     """One timed scope (ghostflow-core/src/profiler.rs:141-146)."""
     name: str
     duration_ms: float
+    start_ms: float = 0.0        # host time of the scope's entry, relative to the profiler's creation
 
 
 @dataclass
@@ -86,15 +88,16 @@ class Profiler:
         self._pending = []
         self.records: list = []            # the last ``keep_records`` scopes in completion order
         self._keep = keep_records
+        self._t_origin = time.perf_counter()
 
     def start(self, name: str) -> ProfileScope:
         return ProfileScope(self, name)
 
     scope = start
 
-    def _record(self, name, ms):
+    def _record(self, name, ms, t0=None):
         if len(self.records) < self._keep:
-            self.records.append(ProfileRecord(name, ms))
+            self.records.append(ProfileRecord(name, ms, 0.0 if t0 is None else (t0 - self._t_origin) * 1e3))
         s = self.stats.setdefault(name, OpStats())
         s.count += 1
         s.total_ms += ms
@@ -103,8 +106,8 @@ class Profiler:
     def _flush(self):
         if self._pending:
             torch.cuda.synchronize()
-            for name, e0, e1 in self._pending:
-                self._record(name, e0.elapsed_time(e1))
+            for name, e0, e1, t0 in self._pending:
+                self._record(name, e0.elapsed_time(e1), t0)
             self._pending = []
 
     def summary(self) -> dict:
@@ -115,6 +118,17 @@ class Profiler:
     def get_summary(self) -> ProfileSummary:
         self._flush()
         return ProfileSummary(sum(v.count for v in self.stats.values()), dict(self.stats))
+
+    def export_chrome_trace(self, path) -> int:
+        """Writes the recorded scopes as a Chrome / Perfetto trace (``chrome://tracing``, ui.perfetto.dev): one
+        complete event per scope, placed at the host time of its entry with its measured duration (device time for
+        CUDA-event scopes). Returns the number of events."""
+        self._flush()
+        events = [{"name": r.name, "ph": "X", "ts": r.start_ms * 1e3, "dur": r.duration_ms * 1e3, "pid": os.getpid(),
+                   "tid": 0, "cat": "ghost_flow"} for r in self.records]
+        with open(path, "w") as f:
+            json.dump({"traceEvents": events, "displayTimeUnit": "ms"}, f)
+        return len(events)
 
     def print_summary(self):
         rows = sorted(self.summary().items(), key=lambda kv: -kv[1]["total_ms"])

@@ -154,3 +154,22 @@ def test_graph_layout_hardware_serve_and_model_records():
     assert isinstance(it, DataLoaderIter) and len(it) == 3
     xb, yb = next(it)
     assert xb.shape == (4, 1) and it.current_batch == 1 and len(it) == 2 and len(list(it)) == 2
+
+
+def test_profiler_exports_a_chrome_trace(tmp_path):
+    import json
+    import time
+
+    from ghost_flow_b200.utils import Profiler
+
+    prof = Profiler(use_cuda_events=False)
+    with prof.start("outer"):
+        time.sleep(0.01)
+        with prof.start("inner"):
+            time.sleep(0.005)
+    n = prof.export_chrome_trace(tmp_path / "trace.json")
+    ev = json.load(open(tmp_path / "trace.json"))["traceEvents"]
+    assert n == 2 and {e["name"] for e in ev} == {"outer", "inner"} and all(e["ph"] == "X" for e in ev)
+    outer, inner = (next(e for e in ev if e["name"] == k) for k in ("outer", "inner"))
+    assert outer["ts"] <= inner["ts"] and inner["ts"] + inner["dur"] <= outer["ts"] + outer["dur"] + 1e3
+    assert outer["dur"] >= 14e3
