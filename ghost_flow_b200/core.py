@@ -153,6 +153,84 @@ TensorElement = (float, int, bool)
 StateDict = dict
 
 
+class Storage:
+    """Flat typed buffer behind a tensor (ghostflow-core/src/storage.rs:8-120): a 1-D torch tensor plus a
+    readers-writer lock; ``read()`` / ``write()`` are the guards (context managers that yield the buffer)."""
+
+    def __init__(self, dtype=torch.float32, length: int = 0, device="cpu"):
+        import threading
+
+        self.data = torch.zeros(length, dtype=dtype, device=device)
+        self._cond = threading.Condition()
+        self._readers = 0
+        self._writing = False
+
+    @classmethod
+    def from_slice(cls, values, dtype=torch.float32, device="cpu"):
+        s = cls(dtype, 0, device)
+        s.data = torch.as_tensor(values, dtype=dtype, device=device).reshape(-1).clone()
+        return s
+
+    def __len__(self):
+        return self.data.numel()
+
+    def len(self):
+        return self.data.numel()
+
+    def is_empty(self):
+        return self.data.numel() == 0
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    def read(self):
+        return StorageReadGuard(self)
+
+    def write(self):
+        return StorageWriteGuard(self)
+
+
+class StorageReadGuard:
+    """Shared access: any number of readers, no writer."""
+
+    def __init__(self, storage: Storage):
+        self.s = storage
+
+    def __enter__(self):
+        with self.s._cond:
+            while self.s._writing:
+                self.s._cond.wait()
+            self.s._readers += 1
+        return self.s.data
+
+    def __exit__(self, *exc):
+        with self.s._cond:
+            self.s._readers -= 1
+            self.s._cond.notify_all()
+        return False
+
+
+class StorageWriteGuard:
+    """Exclusive access."""
+
+    def __init__(self, storage: Storage):
+        self.s = storage
+
+    def __enter__(self):
+        with self.s._cond:
+            while self.s._writing or self.s._readers:
+                self.s._cond.wait()
+            self.s._writing = True
+        return self.s.data
+
+    def __exit__(self, *exc):
+        with self.s._cond:
+            self.s._writing = False
+            self.s._cond.notify_all()
+        return False
+
+
 class Serializable:
     """Mix-in: anything with ``state_dict()`` / ``load_state_dict()`` gains ``save(path)`` / ``load(path)`` in the
     GHOSTFLW format (or GFCP / safetensors by extension or ``fmt``)."""

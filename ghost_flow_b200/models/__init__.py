@@ -4,11 +4,11 @@ from .gpt import GPTForCausalLM, GPTForSequenceClassification, GPTModel  # noqa:
 from .llama import LLaMAForCausalLM, LLaMAModel  # noqa: F401
 from .encoders import (  # noqa: F401
     BertForMaskedLM, BertForSequenceClassification, BertForTokenClassification, BertModel, BertOutput,
-    MixtralForCausalLM, PatchEmbedding, T5ForConditionalGeneration, T5ForSequenceClassification, T5Model, T5Output,
+    MixtralForCausalLM, PatchEmbedding, T5ForConditionalGeneration, T5Embeddings, T5ForSequenceClassification, T5Model, T5Output,
     VisionTransformer,
 )
 from .multimodal import (  # noqa: F401
-    CLIP, CLIPConfig, CLIPTextConfig, CLIPVisionConfig, DDPM, BetaSchedule, DiffusionConfig, NeRF, NeRFConfig, NeRFMLP, NoiseScheduler,
+    CLIP, CLIPConfig, CLIPTextConfig, CLIPTextLayer, CLIPVisionConfig, DDPM, BetaSchedule, DiffusionConfig, NeRF, NeRFConfig, NeRFMLP, NoiseScheduler,
     PositionalEncoder, RaySampler, ResidualBlock, UNet, VolumeRenderer,
 )
 from .geometry import (  # noqa: F401

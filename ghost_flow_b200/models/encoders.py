@@ -258,11 +258,25 @@ T5Encoder = T5Stack
 T5Decoder = T5Stack
 
 
+class T5Embeddings(Embedding):
+    """The token table shared by encoder, decoder and (scaled) output head (ghostflow-nn/src/t5.rs:127-175; there
+    the three users hold independent copies, here they share this one module)."""
+
+    def __init__(self, cfg: T5Config):
+        super().__init__(cfg.vocab_size, cfg.d_model)
+        self.cfg = cfg
+
+    def forward(self, input_ids):
+        if input_ids.dim() != 2:
+            raise ValueError(f"expected 2-D input_ids, got {input_ids.dim()}-D")
+        return super().forward(input_ids)
+
+
 class T5Model(Module):
     def __init__(self, cfg: T5Config):
         super().__init__()
         self.cfg = cfg
-        self.shared = Embedding(cfg.vocab_size, cfg.d_model)
+        self.shared = T5Embeddings(cfg)
         self.encoder = T5Stack(cfg, False)
         self.decoder = T5Stack(cfg, True)
 

@@ -93,6 +93,24 @@ class CLIPConfig:
                               max_text_len=16)
 
 
+class MLP(Module):
+    """The feed-forward block of a CLIP layer (ghostflow-nn/src/clip.rs:400-430): Linear, QuickGELU-free GELU, Linear."""
+
+    def __init__(self, width: int, hidden: int):
+        super().__init__()
+        self.fc1, self.fc2 = Linear(width, hidden), Linear(hidden, width)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(x)))
+
+
+class CLIPTextLayer(TransformerEncoderLayer):
+    """One pre-norm, causally masked layer of the text tower (ghostflow-nn/src/clip.rs:300-350)."""
+
+    def __init__(self, c: "CLIPConfig"):
+        super().__init__(c.text_width, c.text_heads, 4 * c.text_width, 0.0, True, causal=True)
+
+
 class CLIPVisionEncoder(Module):
     def __init__(self, c: CLIPConfig):
         super().__init__()
@@ -120,8 +138,7 @@ class CLIPTextEncoder(Module):
         super().__init__()
         self.tok = Embedding(c.vocab_size, c.text_width)
         self.pos = Parameter(torch.randn(1, c.max_text_len, c.text_width) * 0.01)
-        self.layers = ModuleList([TransformerEncoderLayer(c.text_width, c.text_heads, 4 * c.text_width, 0.0, True,
-                                                          causal=True) for _ in range(c.text_layers)])
+        self.layers = ModuleList([CLIPTextLayer(c) for _ in range(c.text_layers)])
         self.norm = LayerNorm(c.text_width)
         self.out = Linear(c.text_width, c.embed_dim, bias=False)
 

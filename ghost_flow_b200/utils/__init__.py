@@ -433,6 +433,92 @@ class FusionEngine:
         return self.fuse([type(m).__name__ for m in module.modules() if not list(m.children())])
 
 
+# =========================================================================== "JIT": cached fused element-wise chains
+class OptimizationLevel(enum.Enum):
+    """Kept for the reference's surface (ghostflow-core/src/jit/mod.rs:39-46). There is nothing to tune: a chain is
+    one launch of the op-chain kernel at every level; O0 runs the operations one by one."""
+    O0 = 0
+    O1 = 1
+    O2 = 2
+    O3 = 3
+
+
+@dataclass(frozen=True)
+class GraphSignature:
+    """Cache key of a compiled graph: operation names and input shapes (ghostflow-core/src/jit/mod.rs:26-31)."""
+    ops: tuple
+    shapes: tuple = ()
+
+
+class CompiledKernel:
+    """What :meth:`JitCompiler.compile` returns: call it with the input tensor."""
+
+    def __init__(self, signature: GraphSignature, names: tuple, fused: bool):
+        self.signature, self.names, self.fused = signature, names, fused
+        self.calls = 0
+
+    def __call__(self, x):
+        from .. import ops
+
+        self.calls += 1
+        if self.fused:
+            return ops.op_chain(x, list(self.names))          # one pass over memory (gf_op_chain on the GPU)
+        for n in self.names:
+            x = ops.unary(x, n)
+        return x
+
+    execute = __call__
+
+
+class JitCompiler:
+    """The reference generates CUDA source for a chain of element-wise operations and compiles it with nvcc at run
+    time (ghostflow-core/src/jit/mod.rs:48-150; the generated kernel is never launched there). Here the same job is
+    done without a compiler at run time: the library's op-chain kernel takes up to eight unary operations as launch
+    arguments and applies them in one pass, so "compiling" a graph means checking that it is such a chain and
+    caching the callable under its signature. Graphs with other operations are refused with the reason."""
+
+    _NAMES = {"relu": "relu", "gelu": "gelu", "sigmoid": "sigmoid", "tanh": "tanh", "silu": "silu", "exp": "exp",
+              "neg": "neg", "abs": "abs", "sqrt": "sqrt", "square": "square"}
+
+    def __init__(self, optimization_level: OptimizationLevel = OptimizationLevel.O3):
+        self.optimization_level = optimization_level
+        self.cache: dict = {}
+        self.hits = self.misses = 0
+
+    def compute_signature(self, graph: "ComputeGraph", shapes=()) -> GraphSignature:
+        return GraphSignature(tuple(n.op for n in graph.nodes), tuple(tuple(s) for s in shapes))
+
+    def compile(self, graph: "ComputeGraph", shapes=()) -> CompiledKernel:
+        from ..ops.fused import OPS
+
+        sig = self.compute_signature(graph, shapes)
+        if sig in self.cache:
+            self.hits += 1
+            return self.cache[sig]
+        self.misses += 1
+        body = [n for n in graph.nodes if n.op.lower() not in ("input", "output")]
+        names = []
+        for i, n in enumerate(body):
+            key = self._NAMES.get(n.op.lower())
+            if key is None or key not in OPS:
+                raise ValueError(f"cannot fuse operation {n.op!r}: only chains of unary element-wise operations "
+                                 f"({', '.join(sorted(k for k in self._NAMES if k in OPS))}) compile to one kernel")
+            if i and n.inputs and n.inputs[0] != body[i - 1].id:
+                raise ValueError("the graph is not a single chain")
+            names.append(key)
+        if not names or len(names) > 8:
+            raise ValueError("a chain needs between one and eight operations")
+        kern = CompiledKernel(sig, tuple(names), fused=self.optimization_level != OptimizationLevel.O0)
+        self.cache[sig] = kern
+        return kern
+
+    def clear_cache(self):
+        self.cache.clear()
+
+    def cache_size(self) -> int:
+        return len(self.cache)
+
+
 # =========================================================================== layouts
 class MemoryLayout(enum.Enum):
     NCHW = "NCHW"

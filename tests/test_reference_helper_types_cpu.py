@@ -173,3 +173,68 @@ def test_profiler_exports_a_chrome_trace(tmp_path):
     outer, inner = (next(e for e in ev if e["name"] == k) for k in ("outer", "inner"))
     assert outer["ts"] <= inner["ts"] and inner["ts"] + inner["dur"] <= outer["ts"] + outer["dur"] + 1e3
     assert outer["dur"] >= 14e3
+
+
+def test_jit_facade_compiles_unary_chains_and_caches_them():
+    from ghost_flow_b200.utils import (CompiledKernel, ComputeGraph, GraphSignature, JitCompiler, OptimizationLevel)
+
+    g = ComputeGraph()
+    x = g.add_node("Input")
+    a = g.add_node("ReLU", [x])
+    b = g.add_node("Tanh", [a])
+    g.add_node("Sigmoid", [b])
+    jit = JitCompiler()
+    k = jit.compile(g, shapes=[(4, 8)])
+    assert isinstance(k, CompiledKernel) and k.names == ("relu", "tanh", "sigmoid") and k.fused
+    assert isinstance(k.signature, GraphSignature) and k.signature.shapes == ((4, 8),)
+    t = torch.randn(4, 8)
+    assert torch.allclose(k(t), torch.sigmoid(torch.tanh(torch.relu(t))), atol=1e-6)
+    assert jit.compile(g, shapes=[(4, 8)]) is k and jit.hits == 1 and jit.cache_size() == 1
+    assert jit.compile(g, shapes=[(2, 8)]) is not k and jit.cache_size() == 2          # another shape, another entry
+    slow = JitCompiler(OptimizationLevel.O0).compile(g)
+    assert not slow.fused and torch.allclose(slow(t), k(t))
+    bad = ComputeGraph()
+    i = bad.add_node("Input")
+    bad.add_node("Conv2d", [i])
+    try:
+        jit.compile(bad)
+        raise AssertionError("a convolution is not an element-wise chain")
+    except ValueError as e:
+        assert "Conv2d" in str(e)
+
+
+def test_storage_guards_and_shared_t5_table():
+    import threading
+    import time
+
+    from ghost_flow_b200 import models as M
+    from ghost_flow_b200.core import Storage, StorageReadGuard, StorageWriteGuard
+
+    st = Storage.from_slice([1.0, 2.0, 3.0])
+    assert st.len() == 3 and not st.is_empty() and Storage(torch.float32, 0).is_empty()
+    order = []
+
+    def reader():
+        with st.read():
+            order.append("reader in")
+
+    with st.write() as w:
+        assert isinstance(st.write(), StorageWriteGuard) and isinstance(st.read(), StorageReadGuard)
+        t = threading.Thread(target=reader)
+        t.start()
+        time.sleep(0.05)                                    # the reader is blocked on the write guard by now
+        w[0] = 10.0
+        order.append("writer done")
+    t.join(timeout=5)
+    assert order == ["writer done", "reader in"]            # the reader waited for the writer
+    with st.read() as a, st.read() as b:                    # readers share
+        assert float(a[0]) == 10.0 and a.data_ptr() == b.data_ptr()
+    t5 = M.T5Model(M.T5Config.t5_tiny())
+    assert isinstance(t5.shared, M.T5Embeddings)
+    try:
+        t5.shared(torch.zeros(3, dtype=torch.long))
+        raise AssertionError("1-D ids must be refused")
+    except ValueError:
+        pass
+    c = M.CLIP(M.CLIPConfig.tiny())
+    assert isinstance(c.text.layers[0], M.CLIPTextLayer) if hasattr(c, "text") else True
