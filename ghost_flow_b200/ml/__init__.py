@@ -27,3 +27,6 @@ from .preprocessing import PolynomialFeatures, OneHotEncoder, TargetEncoder  # n
 
 gpu = automl          # ghostflow-ml/src/gpu.rs names live in ``automl`` (GPUContext, GPUTensor, GPUOps, ...)
 distributed = automl  # ghostflow-ml/src/distributed.rs names likewise (DataParallelTrainer, RingAllReduce, ...)
+
+from . import options  # noqa: E402,F401
+from .options import *  # noqa: E402,F401,F403

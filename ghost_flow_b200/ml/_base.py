@@ -45,7 +45,7 @@ class Estimator:
 
     def set(self, **kw):
         for k, v in kw.items():
-            setattr(self, "_" + k, v)
+            setattr(self, "_" + k, _plain(v))
         return self
 
     def get_params(self) -> dict:
@@ -65,9 +65,16 @@ class Estimator:
         return copy.deepcopy(self)
 
 
+def _plain(value):
+    """Option enums (``ml.options``) are stored as the strings the algorithms compare against."""
+    import enum
+
+    return value.value if isinstance(value, enum.Enum) else value
+
+
 def _make_setter(name):
     def setter(self, value):
-        setattr(self, "_" + name, value)
+        setattr(self, "_" + name, _plain(value))
         return self
     setter.__name__ = name
     return setter

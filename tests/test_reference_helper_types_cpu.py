@@ -238,3 +238,18 @@ def test_storage_guards_and_shared_t5_table():
         pass
     c = M.CLIP(M.CLIPConfig.tiny())
     assert isinstance(c.text.layers[0], M.CLIPTextLayer) if hasattr(c, "text") else True
+
+
+def test_ml_option_enums_are_accepted_where_strings_are():
+    import numpy as np
+
+    from ghost_flow_b200 import ml
+
+    X = np.random.RandomState(0).randn(200, 3)
+    a = ml.KBinsDiscretizer(4).strategy(ml.BinStrategy.Quantile).encode(ml.BinEncode.Ordinal).fit(X)
+    b = ml.KBinsDiscretizer(4).strategy("quantile").fit(X)
+    assert np.allclose(a.bin_edges_[0], b.bin_edges_[0]) and a._strategy == "quantile"
+    n1 = ml.Normalizer(ml.Norm.L1).fit(X).transform(X)
+    assert np.allclose(np.abs(np.asarray(n1.data)).sum(1), 1.0, atol=1e-5)
+    assert ml.options.option_value(ml.Scoring.F1) == "f1" and str(ml.SeasonalType.Additive) == "additive"
+    assert ml.OPTICSMetric is ml.TSNEMetric
