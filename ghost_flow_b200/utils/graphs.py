@@ -30,6 +30,15 @@ class GraphedStep:
         self.fn = fn
         self.static_inputs = [t.clone() for t in example_inputs]
         self.warmup_outputs = []
+        self.replays = 0
+        self.graph = None
+        if not (torch.cuda.is_available() and all(t.is_cuda for t in self.static_inputs)):
+            # no GPU: the same object runs the step eagerly, so a script written for graphs runs anywhere
+            for _ in range(warmup):
+                out = fn(*self.static_inputs)
+                self.warmup_outputs.append(out.detach().clone() if torch.is_tensor(out) else out)
+            self.static_output = None
+            return
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -45,6 +54,10 @@ class GraphedStep:
         self.replays = 0
 
     def __call__(self, *inputs):
+        if self.graph is None:
+            self.replays += 1
+            self.static_output = self.fn(*inputs)
+            return self.static_output
         for dst, src in zip(self.static_inputs, inputs):
             dst.copy_(src, non_blocking=True)
         self.graph.replay()
@@ -54,6 +67,7 @@ class GraphedStep:
     def release(self):
         """Drops the recording (and the memory pool it holds). Call it before tearing a process group down: a live
         graph that contains collectives keeps the communicator's watchdog from finishing."""
-        torch.cuda.synchronize()
-        self.graph.reset()
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph.reset()
         self.static_output = None

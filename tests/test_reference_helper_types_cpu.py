@@ -253,3 +253,24 @@ def test_ml_option_enums_are_accepted_where_strings_are():
     assert np.allclose(np.abs(np.asarray(n1.data)).sum(1), 1.0, atol=1e-5)
     assert ml.options.option_value(ml.Scoring.F1) == "f1" and str(ml.SeasonalType.Additive) == "additive"
     assert ml.OPTICSMetric is ml.TSNEMetric
+
+
+def test_graphed_step_runs_eagerly_without_a_gpu():
+    from ghost_flow_b200.utils import GraphedStep
+
+    net = torch.nn.Linear(4, 1)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+
+    def train(x, y):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(net(x), y)
+        loss.backward()
+        opt.step()
+        return loss.detach()
+
+    x, y = torch.randn(16, 4), torch.randn(16, 1)
+    gs = GraphedStep(train, (x, y), warmup=2)
+    assert gs.graph is None and len(gs.warmup_outputs) == 2
+    losses = [float(gs(x, y)) for _ in range(5)]
+    assert gs.replays == 5 and losses[-1] < float(gs.warmup_outputs[0])
+    gs.release()
