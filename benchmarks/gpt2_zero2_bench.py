@@ -111,7 +111,7 @@ def main():
     if rank == 0:
         n_params = sum(p.numel() for p in model.parameters())
         print(json.dumps({"metric": "GPT-2 ZeRO-%d train tokens/s" % a.stage, "model": a.model, "params": n_params, "n_gpus": world,
-                          "global_batch": a.global_batch, "seq_len": a.seq, "comm": a.comm if world > 1 else "none", "cuda_graph": bool(a.graph),
+                          "global_batch": a.global_batch, "seq_len": a.seq, "comm": a.comm if world > 1 else "none", "cuda_graph": bool(a.graph and cuda),
                           "overlap": bool(opt.overlap), "ms_per_step": round(float(t), 3),
                           "value": round(a.global_batch * a.seq / float(t) * 1e3), "unit": "tokens/s",
                           "loss": round(float(loss), 4), "dtype": "bf16" if cuda else "fp32",
