@@ -205,3 +205,47 @@ def convert_linears_to_fp8(module: torch.nn.Module, skip=("lm_head",)) -> int:
         else:
             n += convert_linears_to_fp8(child, skip)
     return n
+
+
+# ------------------------------------------------------------------------------------------ MX (block-scaled) format
+# OCP microscaling MXFP8: blocks of 32 consecutive elements along the contraction axis share one power-of-two scale
+# stored as E8M0 (a biased exponent byte, value 2^(e - 127)); the elements are e4m3. This is the operand format of
+# `tcgen05.mma.kind::mxf8f6f4.block_scale`. The quantiser, the de-quantiser and the fp32 oracle below define the format
+# for this package and are what a native block-scaled kernel has to reproduce; the GEMM entry point here runs the
+# de-quantised operands through the bf16 tensor-core kernel (exact for the scales, bf16 rounding for the products of
+# two e4m3 values is exact too: 4 + 4 significant bits), so it is a correct but not a native MX path.
+MX_BLOCK = 32
+_E4M3_EMAX = 8          # largest power of two representable in e4m3 (448 = 1.75 * 2^8)
+
+
+def quantize_mxfp8(x: torch.Tensor):
+    """``x [R, K]`` (K a multiple of 32) -> ``(q uint8 [R, K]`` e4m3 bytes, ``scale uint8 [R, K / 32]`` E8M0 bytes)``.
+    The shared exponent of a block is ``floor(log2(amax)) - 8`` as the OCP specification prescribes."""
+    R, K = x.shape
+    assert K % MX_BLOCK == 0, "the contraction length must be a multiple of 32"
+    xb = x.float().reshape(R, K // MX_BLOCK, MX_BLOCK)
+    amax = xb.abs().amax(-1)
+    e = torch.floor(torch.log2(amax.clamp_min(2.0 ** -126))) - _E4M3_EMAX
+    e = e.clamp(-127, 127)
+    scale = torch.exp2(e)
+    q = (xb / scale[..., None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8).reshape(R, K)
+    return q, (e + 127).to(torch.uint8)
+
+
+def dequantize_mxfp8(q: torch.Tensor, scale_e8m0: torch.Tensor) -> torch.Tensor:
+    """fp32 values of an MXFP8 tensor."""
+    R, K = q.shape
+    v = q.view(torch.float8_e4m3fn).float().reshape(R, K // MX_BLOCK, MX_BLOCK)
+    s = torch.exp2(scale_e8m0.float() - 127.0)
+    return (v * s[..., None]).reshape(R, K)
+
+
+def gemm_mxfp8(aq, sa, bq, sb, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``out[M, N] = dequant(aq, sa) @ dequant(bq, sb)^T`` for MXFP8 operands ``aq [M, K]``, ``bq [N, K]``.
+    CPU: fp32 oracle. CUDA: the de-quantised operands through the bf16 tensor-core GEMM (see the note above)."""
+    a, b = dequantize_mxfp8(aq, sa), dequantize_mxfp8(bq, sb)
+    if aq.is_cuda:
+        from . import gemm as _gemm
+
+        return _gemm.matmul_nt(a.to(torch.bfloat16), b.to(torch.bfloat16)).to(out_dtype)
+    return (a @ b.t()).to(out_dtype)

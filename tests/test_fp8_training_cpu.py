@@ -43,3 +43,29 @@ def test_small_network_trains_with_fp8_linears():
         first = first if first is not None else loss.item()
         last = loss.item()
     assert last < 0.35 * first, (first, last)
+
+
+def test_mxfp8_format_round_trip_and_oracle():
+    """Blocks of 32 share an E8M0 power-of-two scale: scales are exact powers of two, the largest element of a block
+    lands in e4m3's top binade, the round trip error is e4m3's (3 mantissa bits), and the block-scaled product is
+    closer to fp32 than one scale per row when the row mixes magnitudes."""
+    torch.manual_seed(0)
+    M, N, K = 48, 40, 256
+    a = torch.randn(M, K) * torch.logspace(-3, 3, K // 32).repeat_interleave(32)      # magnitudes vary along K
+    b = torch.randn(N, K)
+    aq, sa = fp8.quantize_mxfp8(a)
+    bq, sb = fp8.quantize_mxfp8(b)
+    assert aq.dtype == torch.uint8 and sa.shape == (M, K // 32) and sa.dtype == torch.uint8
+    top = fp8.dequantize_mxfp8(aq, sa).reshape(M, K // 32, 32).abs().amax(-1) / torch.exp2(sa.float() - 127)
+    assert float(top.min()) >= 256 * 0.9 and float(top.max()) <= 448          # the block maximum sits in [2^8, 448]
+    assert _rel(fp8.dequantize_mxfp8(aq, sa), a) < 0.04
+    ref = a @ b.t()
+    mx = fp8.gemm_mxfp8(aq, sa, bq, sb, out_dtype=torch.float32)
+    assert _rel(mx, ref) < 0.06
+    # what the block scales buy: every block keeps e4m3's relative accuracy, while one scale per row flushes the
+    # small-magnitude blocks of the row to zero
+    aq0, s0 = fp8.quantize_rows(a, 0)
+    blocks = lambda t: t.reshape(M, K // 32, 32)                                  # noqa: E731
+    err = lambda d: ((blocks(d) - blocks(a)).norm(dim=(0, 2)) / blocks(a).norm(dim=(0, 2)))   # noqa: E731
+    e_mx, e_row = err(fp8.dequantize_mxfp8(aq, sa)), err(fp8.dequantize(aq0, s0, 0))
+    assert float(e_mx.max()) < 0.05 and float(e_row[0]) > 0.5 and float(e_row[-1]) < 0.05, (e_mx, e_row)
