@@ -50,7 +50,7 @@ CUDA_SOURCES = [
     "runtime.cu",
 ]
 
-HOST_SOURCES = ["cabi.cpp", "formats.cpp", "cpu_ref.cpp"]
+HOST_SOURCES = ["cabi.cpp", "formats.cpp", "cpu_ref.cpp", "symm_alloc.cpp"]
 
 
 def _nvcc() -> str:
@@ -115,8 +115,10 @@ def build(force: bool = False, verbose: bool = False, checked: bool = True) -> d
         if not src.exists():
             continue
         obj = OBJ_DIR / (name + ".o")
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", str(HERE), "-c", str(src), "-o",
-               str(obj)]
+        cuda_inc = Path(nvcc).resolve().parent.parent / "include"      # headers only (ABI checks); nothing is linked
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", str(HERE),
+               *(["-I", str(cuda_inc), "-DGF_HAVE_CUDA_H"] if (cuda_inc / "cuda.h").exists() else []),
+               "-c", str(src), "-o", str(obj)]
         jobs.append((cmd, src, obj))
         host_objs.append(obj)
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
@@ -154,7 +156,7 @@ def build(force: bool = False, verbose: bool = False, checked: bool = True) -> d
         lib = LIB_DIR / "libghostflow.so"
         newest = max(o.stat().st_mtime for o in host_objs)
         if force or not lib.exists() or lib.stat().st_mtime < newest:
-            cmd = ["g++", "-shared", "-o", str(lib), *map(str, host_objs), "-lpthread"]
+            cmd = ["g++", "-shared", "-o", str(lib), *map(str, host_objs), "-lpthread", "-ldl"]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

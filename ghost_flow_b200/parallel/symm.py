@@ -109,10 +109,27 @@ class FusedComm(Comm):
         from .canary import SLACK_BYTES, CanaryLedger
 
         nbytes = (nbytes + SLACK_BYTES + 4095) // 4096 * 4096
-        self.arena = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
-        self.arena_hdl = self._symm.rendezvous(self.arena, self.group_name)
-        self.arena_ptrs = [int(p) for p in self.arena_hdl.buffer_ptrs]
-        mc = getattr(self.arena_hdl, "multicast_ptr", 0) or 0
+        if os.environ.get("GF_SYMM_ALLOC", "torch") == "own":
+            # the library's own allocator (csrc/symm_alloc.cpp: cuMemCreate / export / import / map of every rank's
+            # allocation); no in-switch multicast mapping on this path
+            from .symm_alloc import SymmetricAllocation
+
+            job = [os.urandom(4).hex() if self.rank == 0 else None]
+            dist.broadcast_object_list(job, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                                       group=self.group)
+            self._own = SymmetricAllocation(nbytes, self.rank, self.world, device=self.device.index or 0, job=job[0])
+            self.arena = self._own.tensor()[:nbytes]
+            self.arena.zero_()
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            self.arena_hdl = None
+            self.arena_ptrs = list(self._own.ptrs)
+            mc = 0
+        else:
+            self.arena = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self.arena_hdl = self._symm.rendezvous(self.arena, self.group_name)
+            self.arena_ptrs = [int(p) for p in self.arena_hdl.buffer_ptrs]
+            mc = getattr(self.arena_hdl, "multicast_ptr", 0) or 0
         self.arena_mc = int(mc) if self.use_multimem else 0
         # guard blocks in front of the first carve-out and behind every carve-out (each rank guards its own copy)
         self.canaries = CanaryLedger(self.arena, f"symmetric arena of rank {self.rank}")
