@@ -30,3 +30,15 @@ def test_mixtral_expert_parallel_example(world):
     losses = [float(line.split("loss")[1].split()[0]) for line in out.splitlines() if line.startswith("step")]
     assert len(losses) == 8 and losses[-1] < losses[0] - 0.5
     assert "experts of layer 0: (4, 256, 64)" in out
+
+
+def test_step_roofline_budget_is_consistent():
+    import json
+
+    out = _run(["benchmarks/step_roofline.py", "--gpus", "8", "--measured-ms", "188.8"])
+    b = json.loads(out.strip().splitlines()[-1])
+    assert b["model"]["params"] == 6738415616 and b["ideal_step_ms"] == max(b["ideal_compute_ms"], b["ideal_link_ms"])
+    gemm = next(r for r in b["parts"] if r["part"].startswith("GEMMs"))
+    assert 100 < gemm["ideal_ms"] < 140 and 0.5 < b["fraction_of_ideal"] < 1.0
+    one = json.loads(_run(["benchmarks/step_roofline.py", "--gpus", "1"]).strip().splitlines()[-1])
+    assert one["ideal_link_ms"] == 0 and one["ideal_compute_ms"] > b["ideal_compute_ms"]      # the whole optimizer on one GPU
