@@ -76,13 +76,53 @@ def budget(cfg: LLaMAConfig, tokens: int, world: int, persist: bool = True):
             "ideal_step_ms": round(max(compute, link), 2)}
 
 
+def budget_mixtral(tokens: int, world: int, layers: int = 32):
+    """Mixtral 8x7B shapes, expert parallelism = world, ZeRO-3 for the attention parameters."""
+    from ghost_flow_b200.models.configs import MixtralConfig
+
+    hbm, tflops, src = peaks()
+    c = MixtralConfig.mixtral_8x7b()
+    d, f, V, E, k = c.hidden_size, c.intermediate_size, c.vocab_size, c.num_local_experts, c.num_experts_per_tok
+    H, Hkv, hd = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+    T, L, bf = tokens, layers, 2
+    attn_params = d * (H + 2 * Hkv) * hd + H * hd * d
+    active = L * (attn_params + k * 3 * d * f + E * d) + V * d
+    expert_params_rank = L * (E // world if world <= E else 1) * 3 * d * f
+    rows = []
+    gemm = 6.0 * active * T
+    rows.append({"part": "GEMMs on the active parameters (attention, router, two experts per token, head)", "bound": "tensor",
+                 "ideal_ms": round(gemm / (tflops * 1e12) * 1e3, 2), "note": f"{gemm / 1e12:.0f} TFLOP"})
+    attn = L * 3.5 * 4.0 * H * T * T * hd / 2
+    rows.append({"part": "FlashAttention forward + backward", "bound": "tensor",
+                 "ideal_ms": round(attn / (tflops * 1e12) * 1e3, 2), "note": f"{attn / 1e12:.1f} TFLOP"})
+    passes = L * (2 * 5 * T * d * bf + 8 * T * k * f * bf + 2 * 2 * T * (H + Hkv) * hd * bf) + 2 * T * V * bf
+    rows.append({"part": "norms, SwiGLU over the routed rows, RoPE, cross-entropy", "bound": "HBM",
+                 "ideal_ms": round(passes / (hbm * 1e9) * 1e3, 2), "note": f"{passes / 1e9:.1f} GB"})
+    opt = expert_params_rank * 26 + (L * attn_params + 2 * V * d) / world * 28
+    rows.append({"part": "AdamW: this rank's experts (local) and its shard of the dense parameters", "bound": "HBM",
+                 "ideal_ms": round(opt / (hbm * 1e9) * 1e3, 2), "note": f"{expert_params_rank / 1e9:.2f} B expert parameters"})
+    if world > 1:
+        a2a = L * 4 * T * k * d * bf * (world - 1) / world              # dispatch + combine, forward and backward
+        rows.append({"part": "token dispatch / combine over NVLink (forward and backward)", "bound": "NVLink",
+                     "ideal_ms": round(a2a / 770e9 * 1e3, 2), "note": f"{a2a / 1e9:.1f} GB out per rank"})
+    compute = sum(r["ideal_ms"] for r in rows if r["bound"] != "NVLink")
+    link = sum(r["ideal_ms"] for r in rows if r["bound"] == "NVLink")
+    return {"peaks": {"hbm_gbs": hbm, "bf16_tflops_sustained": tflops, "nvlink_gbs_per_direction": 770.0, "source": src},
+            "model": {"active_params": active, "tokens_per_gpu": T, "gpus": world, "layers": L}, "parts": rows,
+            "ideal_compute_ms": round(compute, 2), "ideal_link_ms": round(link, 2),
+            "ideal_step_ms": round(max(compute, link), 2)}
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama-7b", choices=["llama-7b", "mixtral-8x7b"])
+    ap.add_argument("--layers", type=int, default=32, help="mixtral only")
     ap.add_argument("--gpus", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU and step")
     ap.add_argument("--measured-ms", type=float, default=None)
     a = ap.parse_args()
-    b = budget(LLaMAConfig.llama_7b(), a.tokens, a.gpus)
+    b = (budget(LLaMAConfig.llama_7b(), a.tokens, a.gpus) if a.model == "llama-7b"
+         else budget_mixtral(a.tokens, a.gpus, a.layers))
     print(f"peaks ({b['peaks']['source']}): {b['peaks']['hbm_gbs']:.0f} GB/s copy, "
           f"{b['peaks']['bf16_tflops_sustained']:.0f} TFLOP/s bf16 sustained, 770 GB/s NVLink per direction")
     print(f"{'part':<78}{'bound':>8}{'ideal ms':>10}")
